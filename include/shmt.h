@@ -1,0 +1,226 @@
+/*
+ * libshmt — C-ABI of the B200 (sm_100a) GPU-cache hot path.
+ *
+ * Every entry point is plain C: raw pointers, sizes, dtype codes and an opaque
+ * cudaStream_t passed as void*.  No torch / pybind types cross this boundary.
+ * Each function returns an int status (SHMT_OK == 0); shmt_last_error() gives
+ * the text of the last failure on the calling thread.  Nothing here ever calls
+ * exit(): the reference's CUDA_CALL (include/common.h:15-27) kills the process,
+ * this library reports.
+ *
+ * Each declaration cites the reference interface it replaces, as
+ * <file>:<line> inside the gpzlx1/ShmTensor source tree.
+ */
+#ifndef SHMT_H_
+#define SHMT_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes -------------------------------------------------------- */
+#define SHMT_OK 0
+#define SHMT_ERR_INVALID 1  /* bad argument (null, dtype code, alignment, size)   */
+#define SHMT_ERR_CUDA 2     /* a CUDA runtime call failed                         */
+#define SHMT_ERR_CAPACITY 3 /* hashmap full: a probe ran the whole table          */
+#define SHMT_ERR_TIMEOUT 4  /* a bounded device-side wait (look-back) gave up     */
+#define SHMT_ERR_OS 5       /* shm_open / mmap / file error (errno in the text)   */
+
+/* ---- integer dtype codes (ids, keys, slots, indptr, indices) -------------- */
+#define SHMT_I32 0
+#define SHMT_I64 1
+
+const char* shmt_last_error(void);
+int shmt_version(void);
+
+/* ---- context --------------------------------------------------------------
+ * Owns the per-device scratch every op needs (look-back tile states, relabel
+ * table, device/pinned result words).  Scratch grows on demand and is reused,
+ * so steady-state calls allocate nothing.  One context serves one stream at a
+ * time: two ops on the same context must not overlap on the GPU.
+ * Replaces the reference's per-call torch::empty / raw_allocate temporaries
+ * (src/cache_graph_sampling.cu:30-45,50-56; src/tensor_relabel.cu:141-177).   */
+typedef struct shmt_ctx shmt_ctx;
+int shmt_ctx_create(int device, shmt_ctx** out);
+int shmt_ctx_destroy(shmt_ctx* ctx);
+int64_t shmt_ctx_scratch_bytes(const shmt_ctx* ctx);
+
+/* ---- static hashmap --------------------------------------------------------
+ * Open addressing, linear probing over 16-byte {int64 key, int64 value} slots,
+ * probed by 4-lane tiles (one 64-byte window per step).  Empty key = -1.
+ * Replaces pycuco::CUCOHashmapWrapper / CUCOHashmap
+ * (include/cuco_hashmap.h:12-25, include/cuco_hashmap.cuh:49-93,
+ *  src/cuco_hashmap.cu:10-41).                                                */
+typedef struct shmt_map shmt_map;
+
+/* bytes of table storage a map of `capacity` requested slots needs            */
+int64_t shmt_map_table_bytes(int64_t capacity);
+
+/* Create an empty map.  `capacity` is what shmt_map_capacity() reports
+ * (the reference reports ceil(n / load_factor), include/cuco_hashmap.cuh:62,75).
+ * table_buf: device buffer of shmt_map_table_bytes(capacity) bytes, 16-byte
+ * aligned, that must outlive the map; NULL lets the map cudaMalloc its own.   */
+int shmt_map_create(int device, int64_t capacity, int key_dtype, int val_dtype,
+                    void* table_buf, void* stream, shmt_map** out);
+
+/* insert_or_assign of n (key, value) pairs, key != -1.  Synchronises `stream`
+ * and returns SHMT_ERR_CAPACITY if the table overflowed.  Bulk-insert half of
+ * include/cuco_hashmap.cuh:68-70; inserting into an existing map is new.      */
+int shmt_map_insert(shmt_map* map, const void* keys, const void* values,
+                    int64_t n, void* stream);
+
+/* out[i] = value of requests[i] or -1 (include/cuco_hashmap.cuh:81-87).
+ * Requests are first narrowed to the key dtype, as the reference's
+ * requests.to(key_type_) does (src/cuco_hashmap.cu:29).  out has the value
+ * dtype.  Asynchronous on `stream`.                                           */
+int shmt_map_query(const shmt_map* map, const void* requests, int req_dtype,
+                   int64_t n, void* out, void* stream);
+
+int64_t shmt_map_capacity(const shmt_map* map);     /* include/cuco_hashmap.h:20 */
+int64_t shmt_map_memory_usage(const shmt_map* map); /* include/cuco_hashmap.h:21 */
+int64_t shmt_map_size(const shmt_map* map);         /* distinct keys stored       */
+int shmt_map_key_dtype(const shmt_map* map);
+int shmt_map_val_dtype(const shmt_map* map);
+int shmt_map_destroy(shmt_map* map);
+
+/* ---- feature fetch ---------------------------------------------------------
+ * out[i] = hit(i) ? gpu_base[slot(i)] : host_base[idx[i]], rows of row_bytes.
+ *   map  != NULL : slot from a fused probe   -> CacheTensorFetch
+ *                                               (src/cache_feature_fetch.cu:131-185)
+ *   mask != NULL : slot = mask[i] (>= 0 hit) -> CacheTensorFetchWithMask (:226-272)
+ *   both NULL    : every row from host_base  -> UVATensorFetch (:47-87)
+ * host_base is pinned/registered host memory read through UVA (or any device-
+ * visible pointer).  Asynchronous on `stream`.                                */
+int shmt_fetch(const shmt_map* map, const void* mask, int mask_dtype,
+               const void* host_base, const void* gpu_base, const void* idx,
+               int idx_dtype, int64_t n, int64_t row_bytes, void* out,
+               void* stream);
+
+/* Partitioned cache: value = (owner << owner_shift) | slot; the row is read
+ * from bases[owner] (this GPU's buffer or a peer's, by plain NVLink loads).
+ * No counterpart in the reference (it is single-GPU).                         */
+int shmt_fetch_partitioned(const shmt_map* map, const void* const* bases,
+                           int n_bases, int owner_shift, const void* host_base,
+                           const void* idx, int idx_dtype, int64_t n,
+                           int64_t row_bytes, void* out, void* stream);
+
+/* ---- feature set -----------------------------------------------------------
+ * hit(i) ? gpu_base[slot(i)] = update[i] : host_base[idx[i]] = update[i].
+ * Same three modes: CacheTensorSet (src/cache_feature_set.cu:118-165),
+ * CacheTensorSetWithMask (:209-248), UVATensorSet (:39-75).  Duplicate ids
+ * have no defined winner, as in the reference.                                */
+int shmt_set(const shmt_map* map, const void* mask, int mask_dtype,
+             void* host_base, void* gpu_base, const void* idx, int idx_dtype,
+             int64_t n, int64_t row_bytes, const void* update, void* stream);
+
+/* Fused insert/overwrite: key[i] is inserted with value slots[i] unless it is
+ * already present (then its stored slot is kept); update[i] is written to
+ * gpu_base[slot].  Synchronises and reports SHMT_ERR_CAPACITY like
+ * shmt_map_insert.  New entry point (the reference never inserts into a live
+ * map; src/cache_feature_set.cu:93-116 only overwrites).                      */
+int shmt_insert_set(shmt_map* map, void* gpu_base, const void* keys,
+                    int key_dtype, const void* slots, int slots_dtype,
+                    int64_t n, int64_t row_bytes, const void* update,
+                    void* stream);
+
+/* ---- scan ------------------------------------------------------------------
+ * In-place prefix sum by a single-pass decoupled look-back kernel, wrapping
+ * integer arithmetic.  exclusive=0: the intended semantics of thrust_scan
+ * (src/thrust_scan.cu:9-18); exclusive=1: cub_exclusiveSum
+ * (src/cache_graph_sampling.cu:30-45, src/tensor_relabel.cu:11-26).           */
+int shmt_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
+              void* stream);
+
+/* ---- relabel ---------------------------------------------------------------
+ * Concatenation of `n_parts` id arrays -> distinct ids in first-occurrence
+ * order (out_unique, capacity = total) and, for every input element, the index
+ * of its id in out_unique (out_relabel, total elements, same dtype).  Ids must
+ * not be -1.  If n_unique_host != NULL the call synchronises and stores the
+ * number of distinct ids there.  TensorRelabel (src/tensor_relabel.cu:125-209). */
+int shmt_relabel(shmt_ctx* ctx, const void* const* parts,
+                 const int64_t* part_sizes, int n_parts, int dtype,
+                 void* out_unique, void* out_relabel, int64_t* n_unique_host,
+                 void* stream);
+
+/* ---- neighbour sampling ----------------------------------------------------
+ * One fan-out hop over a CSR, fused into one kernel (probe, degree, look-back
+ * scan, sample).  For seed i: row = seeds[i]; if a map is given and holds row,
+ * the adjacency is gpu_indices[gpu_indptr[slot] .. gpu_indptr[slot+1]), else
+ * indices[indptr[row] .. indptr[row+1]) (UVA).  Picks per seed:
+ * replace ? (deg ? k : 0) : min(deg, k); deg <= k copies the row in CSR order,
+ * otherwise k distinct uniform positions (without replacement) or k iid
+ * uniform positions (with).  out_sub_indptr: n+1 entries of indptr dtype;
+ * out_sub_indices: capacity n*k entries of indices dtype.  If nnz_host != NULL
+ * the call synchronises and stores out_sub_indptr[n] there.
+ * CSRWiseSampling / CSRWiseCacheSampling
+ * (src/cache_graph_sampling.cu:179-220, :382-426; kernels :91-177, :291-380;
+ *  GetSubIndptr(:47-89) / GetSubIndptrWithCache(:222-289)).
+ * gpu_indptr / gpu_indices / map may all be NULL (uncached).  Randomness is
+ * Philox4x32-10 keyed by rng_seed, countered by (rng_offset, seed index, lane). */
+int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
+                    const void* indices, int indices_dtype,
+                    const void* gpu_indptr, const void* gpu_indices,
+                    const shmt_map* map, const void* seeds, int seeds_dtype,
+                    int64_t n, int64_t k, int replace, uint64_t rng_seed,
+                    uint64_t rng_offset, void* out_sub_indptr,
+                    void* out_sub_indices, int64_t* nnz_host, void* stream);
+
+/* Compact CSR of the selected rows, in the given order: CreateCacheCSR
+ * (src/cache_graph_sampling.cu:455-492).  _count writes the n+1 offsets and
+ * (synchronising) the total; _fill copies the adjacency lists.               */
+int shmt_subcsr_count(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
+                      const void* seeds, int seeds_dtype, int64_t n,
+                      void* out_gpu_indptr, int64_t* nnz_host, void* stream);
+int shmt_subcsr_fill(const void* indptr, int indptr_dtype, const void* indices,
+                     int indices_dtype, const void* seeds, int seeds_dtype,
+                     int64_t n, const void* gpu_indptr, void* out_gpu_indices,
+                     void* stream);
+
+/* ---- host memory substrate -------------------------------------------------
+ * POSIX shared memory (include/shm_memory.h:6-49), existence test
+ * (include/utils.h:5-13), mmap'ed .npy (src/mmap_tensor.cc:10-55,
+ * src/cnpy.cc:18-86) and host registration (src/cache_feature_fetch.cu:6-13). */
+int shmt_shm_create(const char* name, int64_t size, int pin_memory,
+                    int64_t* out_ptr, int64_t* out_fd);
+int shmt_shm_open(const char* name, int64_t size, int pin_memory,
+                  int64_t* out_ptr, int64_t* out_fd);
+int shmt_shm_release(const char* name, int64_t size, int64_t ptr, int64_t fd,
+                     int pin_memory);
+int shmt_shm_exists(const char* name); /* 1 / 0 */
+
+typedef struct shmt_npy_info {
+  char descr[8];     /* numpy dtype string, e.g. "<f4"                        */
+  int32_t ndim;
+  int32_t fortran_order;
+  int64_t shape[8];
+  int64_t data_offset; /* bytes from the start of the file to element 0       */
+  int64_t file_size;   /* size of the mapping                                 */
+  int64_t ptr;         /* base address of the mapping                         */
+  int64_t fd;
+} shmt_npy_info;
+int shmt_npy_open(const char* path, int pin_memory, shmt_npy_info* out);
+int shmt_npy_close(int64_t size, int64_t ptr, int64_t fd, int pin_memory);
+
+int shmt_host_register(void* ptr, int64_t nbytes);
+int shmt_host_unregister(void* ptr);
+
+/* ---- device buffers shared between ranks (partitioned cache) ---------------
+ * cudaMalloc'ed so that a CUDA IPC handle maps the buffer itself.  No
+ * counterpart in the reference.                                              */
+int shmt_dev_alloc(int64_t bytes, void** out);
+int shmt_dev_free(void* ptr);
+int shmt_ipc_get_handle(void* dev_ptr, void* handle_64_bytes);
+int shmt_ipc_open_handle(const void* handle_64_bytes, void** out);
+int shmt_ipc_close_handle(void* mapped_ptr);
+
+/* Streaming-read probe used to measure the host-link / peer-link / HBM
+ * ceilings: sums `bytes` of memory at `src` (16-byte loads) into *sink.       */
+int shmt_stream_read(const void* src, int64_t bytes, void* sink_8_bytes,
+                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SHMT_H_ */

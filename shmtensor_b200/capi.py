@@ -1,0 +1,471 @@
+"""Drop-in mirror of the reference's ``ShmTensorLib`` pybind module.
+
+Same function names, keyword names, return shapes/dtypes and error behaviour as
+the reference's ``src/pybind.cc:16-65``; the work is done by ``libshmt.so``
+through its C-ABI.  PyTorch is only the tensor carrier here: this module checks
+arguments, allocates outputs with ``torch.empty`` and passes raw pointers plus
+torch's current CUDA stream.  There is no CPU implementation behind any of the
+GPU entry points — they raise if no GPU / no library is available.
+
+Differences a caller can see, all extensions:
+
+* kernels run on torch's *current* stream (the reference uses the legacy
+  default stream);
+* ``indptr`` and ``indices`` may have different integer dtypes;
+* payload rows may have any dtype (the reference rejects f16/bf16/bool);
+* sampling draws differ from call to call (``set_sampling_seed`` pins them);
+* ``CUCOStaticHashmap.insert`` / ``.empty`` and ``cache_insert_set`` exist.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import List, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import I32, I64, check, lib
+
+_INT_CODES = {torch.int32: I32, torch.int64: I64}
+_CODE_DTYPES = {I32: torch.int32, I64: torch.int64}
+
+_NPY_DTYPES = {
+    "<f2": torch.float16, "<f4": torch.float32, "<f8": torch.float64, "|u1": torch.uint8,
+    "|i1": torch.int8, "<i2": torch.int16, "<i4": torch.int32, "<i8": torch.int64,
+    "|b1": torch.bool,
+}
+
+
+# --------------------------------------------------------------------------- helpers
+def _int_code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _INT_CODES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"{what}: ID can only be int32 or int64, got {t.dtype}") from None
+
+
+def _check_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+
+
+def _check_contig(t: torch.Tensor, name: str) -> None:
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t) -> int | None:
+    if t is None:
+        return None
+    return t.data_ptr() if t.numel() else None
+
+
+_contexts: dict = {}
+
+
+def _ctx(device: torch.device) -> int:
+    """Per-device libshmt context (scratch + result words), created on first use."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    h = _contexts.get(idx)
+    if h is None:
+        out = C.c_void_p()
+        check(lib.shmt_ctx_create(idx, C.byref(out)))
+        h = _contexts[idx] = out.value
+    return h
+
+
+def _row_bytes(data: torch.Tensor) -> int:
+    n = data.element_size()
+    for s in data.shape[1:]:
+        n *= s
+    return n
+
+
+_rng = {"seed": 7777, "calls": 0}
+
+
+def set_sampling_seed(seed: int) -> None:
+    """Pin the Philox key used by the samplers and restart the per-call counter.
+
+    The reference hard-codes the seed 7777 (src/cache_graph_sampling.cu:201-204), so
+    every call returns the same sample; here the key defaults to 7777 too but
+    each call advances a counter.
+    """
+    _rng["seed"] = int(seed) & (2**64 - 1)
+    _rng["calls"] = 0
+
+
+# --------------------------------------------------------------------------- host memory
+def create_shared_mem(name: str, size: int, pin_memory: bool = False) -> Tuple[int, int]:
+    """include/shm_memory.h:6-23 — returns ``(ptr, fd)``."""
+    p, fd = C.c_int64(), C.c_int64()
+    check(lib.shmt_shm_create(name.encode(), size, int(pin_memory), C.byref(p), C.byref(fd)))
+    return p.value, fd.value
+
+
+def open_shared_mem(name: str, size: int, pin_memory: bool = False) -> Tuple[int, int]:
+    """include/shm_memory.h:25-39 — returns ``(ptr, fd)``."""
+    p, fd = C.c_int64(), C.c_int64()
+    check(lib.shmt_shm_open(name.encode(), size, int(pin_memory), C.byref(p), C.byref(fd)))
+    return p.value, fd.value
+
+
+def release_shared_mem(name: str, size: int, ptr: int, fd: int, pin_memory: bool = False) -> None:
+    """include/shm_memory.h:41-49 — unregister, unmap, close and unlink."""
+    check(lib.shmt_shm_release(name.encode(), size, ptr, fd, int(pin_memory)))
+
+
+def _tensor_from_address(ptr: int, dtype: torch.dtype, shape: Sequence[int]) -> torch.Tensor:
+    numel = 1
+    for s in shape:
+        numel *= int(s)
+    itemsize = torch.empty((), dtype=dtype).element_size()
+    if numel == 0:
+        return torch.empty(tuple(shape), dtype=dtype)
+    buf = (C.c_char * (numel * itemsize)).from_address(ptr)
+    return torch.frombuffer(buf, dtype=dtype, count=numel).reshape(tuple(shape))
+
+
+def open_shared_tensor(ptr: int, dtype: torch.dtype, shape: Sequence[int]) -> torch.Tensor:
+    """include/shm_memory.h:51-56 — zero-copy CPU tensor over the mapping."""
+    return _tensor_from_address(ptr, dtype, shape)
+
+
+def file_exist(filename: str) -> bool:
+    """include/utils.h:5-13 — does a POSIX shm segment of that name exist?"""
+    return bool(lib.shmt_shm_exists(filename.encode()))
+
+
+def open_mmap_tensor(filename: str, pin_memory: bool):
+    """src/mmap_tensor.cc:10-47 — returns ``(tensor, size, ptr, fd)``."""
+    info = _lib.NpyInfo()
+    check(lib.shmt_npy_open(filename.encode(), int(pin_memory), C.byref(info)))
+    descr = info.descr.decode()
+    try:
+        if info.fortran_order:
+            raise RuntimeError("fortran order is not supported")
+        if descr not in _NPY_DTYPES:
+            raise RuntimeError(f"parse_npy_header: failed to find dtype ({descr})")
+    except RuntimeError:
+        lib.shmt_npy_close(info.file_size, info.ptr, info.fd, int(pin_memory))
+        raise
+    shape = [info.shape[i] for i in range(info.ndim)]
+    t = _tensor_from_address(info.ptr + info.data_offset, _NPY_DTYPES[descr], shape)
+    return t, info.file_size, info.ptr, info.fd
+
+
+def close_mmap_tensor(size: int, ptr: int, fd: int, pin_memory: bool) -> None:
+    """src/mmap_tensor.cc:49-55."""
+    check(lib.shmt_npy_close(size, ptr, fd, int(pin_memory)))
+
+
+def pin_memory(data: torch.Tensor) -> None:
+    """src/cache_feature_fetch.cu:6-9 — cudaHostRegister(Portable) of a CPU tensor in place."""
+    _check_contig(data, "data")
+    check(lib.shmt_host_register(data.data_ptr(), data.numel() * data.element_size()))
+
+
+def unpin_memory(data: torch.Tensor) -> None:
+    """src/cache_feature_fetch.cu:11-13."""
+    check(lib.shmt_host_unregister(data.data_ptr()))
+
+
+# --------------------------------------------------------------------------- hashmap
+class CUCOStaticHashmap:
+    """include/cuco_hashmap.h:12-25 — static map int32/int64 keys -> int32/int64 values.
+
+    ``query`` returns the stored value or -1; ``capacity()`` is
+    ``ceil(numel / load_factor)`` exactly as the reference reports it.
+    """
+
+    def __init__(self, keys: torch.Tensor, values: torch.Tensor, load_factor: float):
+        _check_cuda(keys, "keys")
+        _check_cuda(values, "values")
+        kd = _int_code(keys, "keys")
+        vd = _int_code(values, "values")
+        if keys.numel() != values.numel():
+            raise RuntimeError("keys and values must have the same number of elements")
+        capacity = int(math.ceil(keys.numel() / load_factor))
+        self._init_empty(capacity, kd, vd, keys.device)
+        self.insert(keys, values)
+
+    def _init_empty(self, capacity: int, kd: int, vd: int, device: torch.device) -> None:
+        self._handle = None
+        self._device = device
+        self._kd, self._vd = kd, vd
+        nbytes = lib.shmt_map_table_bytes(capacity)
+        # table memory comes from torch's caching allocator, like the reference's torch_allocator
+        self._table = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        out = C.c_void_p()
+        check(lib.shmt_map_create(device.index, capacity, kd, vd, self._table.data_ptr(),
+                                  _stream(device), C.byref(out)))
+        self._handle = out.value
+
+    @classmethod
+    def empty(cls, capacity: int, key_dtype=torch.int64, value_dtype=torch.int64,
+              device="cuda") -> "CUCOStaticHashmap":
+        """Extension: an empty map with room for ``capacity`` keys (see ``insert``)."""
+        self = cls.__new__(cls)
+        device = torch.device(device)
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self._init_empty(int(capacity), _INT_CODES[key_dtype], _INT_CODES[value_dtype], device)
+        return self
+
+    def insert(self, keys: torch.Tensor, values: torch.Tensor) -> None:
+        """Extension: insert_or_assign more pairs (keys != -1).  Raises on overflow."""
+        _check_cuda(keys, "keys")
+        _check_cuda(values, "values")
+        keys = keys.contiguous().to(_CODE_DTYPES[self._kd])
+        values = values.contiguous().to(_CODE_DTYPES[self._vd])
+        check(lib.shmt_map_insert(self._handle, _ptr(keys), _ptr(values), keys.numel(),
+                                  _stream(self._device)))
+
+    def query(self, requests: torch.Tensor) -> torch.Tensor:
+        _check_cuda(requests, "requests")
+        if requests.dtype not in _INT_CODES:
+            requests = requests.to(_CODE_DTYPES[self._kd])
+        requests = requests.contiguous()
+        out = torch.empty(requests.shape, dtype=_CODE_DTYPES[self._vd], device=requests.device)
+        check(lib.shmt_map_query(self._handle, _ptr(requests), _INT_CODES[requests.dtype],
+                                 requests.numel(), _ptr(out), _stream(requests.device)))
+        return out
+
+    def capacity(self) -> int:
+        return lib.shmt_map_capacity(self._handle)
+
+    def memory_usage(self) -> int:
+        return lib.shmt_map_memory_usage(self._handle)
+
+    def size(self) -> int:
+        """Extension: number of distinct keys stored."""
+        return lib.shmt_map_size(self._handle)
+
+    @property
+    def key_dtype(self) -> torch.dtype:
+        return _CODE_DTYPES[self._kd]
+
+    @property
+    def value_dtype(self) -> torch.dtype:
+        return _CODE_DTYPES[self._vd]
+
+    def __del__(self):
+        h = getattr(self, "_handle", None)
+        if h is not None:
+            lib.shmt_map_destroy(h)
+            self._handle = None
+
+
+# --------------------------------------------------------------------------- fetch / set
+def _fetch(uva_data, gpu_data, indices, hashmap, mask, who):
+    _check_cuda(indices, "indices")
+    indices = indices.contiguous()
+    idt = _int_code(indices, who)
+    shape_src = uva_data if uva_data is not None else gpu_data
+    _check_contig(shape_src, "data")
+    if gpu_data is not None:
+        _check_cuda(gpu_data, "gpu_data")
+        _check_contig(gpu_data, "gpu_data")
+    n = indices.numel()
+    out = torch.empty((n, *shape_src.shape[1:]), dtype=shape_src.dtype, device=indices.device)
+    mdt = 0
+    if mask is not None:
+        _check_cuda(mask, "mask")
+        mask = mask.contiguous()
+        mdt = _int_code(mask, who)
+    check(lib.shmt_fetch(hashmap._handle if hashmap is not None else None, _ptr(mask), mdt,
+                         _ptr(uva_data), _ptr(gpu_data), _ptr(indices), idt, n,
+                         _row_bytes(shape_src), _ptr(out), _stream(indices.device)))
+    return out
+
+
+def uva_fetch(data: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
+    """src/cache_feature_fetch.cu:47-87 — ``data[indices]`` read over UVA, result on the GPU."""
+    return _fetch(data, None, indices, None, None, "uva_fetch")
+
+
+def cache_fetch(uva_data: torch.Tensor, gpu_data: torch.Tensor, indices: torch.Tensor,
+                hashmap: CUCOStaticHashmap) -> torch.Tensor:
+    """src/cache_feature_fetch.cu:131-185 — hit rows from ``gpu_data``, misses from ``uva_data``."""
+    return _fetch(uva_data, gpu_data, indices, hashmap, None, "cache_fetch")
+
+
+def cache_fetch_with_mask(uva_data: torch.Tensor, gpu_data: torch.Tensor, indices: torch.Tensor,
+                          mask: torch.Tensor) -> torch.Tensor:
+    """src/cache_feature_fetch.cu:226-272 — like ``cache_fetch`` with slots given by ``mask``."""
+    return _fetch(uva_data, gpu_data, indices, None, mask, "cache_fetch_with_mask")
+
+
+def _set(uva_data, gpu_data, indices, update, hashmap, mask, who):
+    _check_cuda(indices, "indices")
+    _check_cuda(update, "update")
+    indices = indices.contiguous()
+    update = update.contiguous()
+    idt = _int_code(indices, who)
+    ref = uva_data if uva_data is not None else gpu_data
+    _check_contig(ref, "data")
+    if update.dtype != ref.dtype:
+        raise RuntimeError(f"{who}: update has dtype {update.dtype}, the table {ref.dtype}")
+    if update.numel() != indices.numel() * (_row_bytes(ref) // ref.element_size()):
+        raise RuntimeError(f"{who}: update must hold one row per index")
+    mdt = 0
+    if mask is not None:
+        _check_cuda(mask, "mask")
+        mask = mask.contiguous()
+        mdt = _int_code(mask, who)
+    check(lib.shmt_set(hashmap._handle if hashmap is not None else None, _ptr(mask), mdt,
+                       _ptr(uva_data), _ptr(gpu_data), _ptr(indices), idt, indices.numel(),
+                       _row_bytes(ref), _ptr(update), _stream(indices.device)))
+
+
+def uva_set(data: torch.Tensor, indices: torch.Tensor, update: torch.Tensor) -> None:
+    """src/cache_feature_set.cu:39-75 — ``data[indices] = update`` written over UVA."""
+    _set(data, None, indices, update, None, None, "uva_set")
+
+
+def cache_set(uva_data: torch.Tensor, gpu_data: torch.Tensor, indices: torch.Tensor,
+              update: torch.Tensor, hashmap: CUCOStaticHashmap) -> None:
+    """src/cache_feature_set.cu:118-165 — hits overwrite the cached row, misses the host row."""
+    _set(uva_data, gpu_data, indices, update, hashmap, None, "cache_set")
+
+
+def cache_set_with_mask(uva_data: torch.Tensor, gpu_data: torch.Tensor, indices: torch.Tensor,
+                        update: torch.Tensor, mask: torch.Tensor) -> None:
+    """src/cache_feature_set.cu:209-248."""
+    _set(uva_data, gpu_data, indices, update, None, mask, "cache_set_with_mask")
+
+
+def cache_insert_set(gpu_data: torch.Tensor, indices: torch.Tensor, slots: torch.Tensor,
+                     update: torch.Tensor, hashmap: CUCOStaticHashmap) -> None:
+    """Extension: fused insert/overwrite.
+
+    ``indices[i]`` is inserted with value ``slots[i]`` unless already present
+    (then its stored slot is kept) and ``update[i]`` is written to that slot of
+    ``gpu_data`` in the same kernel.  Raises if the map overflows.
+    """
+    for t, nm in ((gpu_data, "gpu_data"), (indices, "indices"), (slots, "slots"), (update, "update")):
+        _check_cuda(t, nm)
+    indices, slots, update = indices.contiguous(), slots.contiguous(), update.contiguous()
+    _check_contig(gpu_data, "gpu_data")
+    if update.dtype != gpu_data.dtype:
+        raise RuntimeError("cache_insert_set: update and gpu_data dtypes differ")
+    check(lib.shmt_insert_set(hashmap._handle, _ptr(gpu_data), _ptr(indices),
+                              _int_code(indices, "cache_insert_set"), _ptr(slots),
+                              _int_code(slots, "cache_insert_set"), indices.numel(),
+                              _row_bytes(gpu_data), _ptr(update), _stream(indices.device)))
+
+
+# --------------------------------------------------------------------------- scan / relabel
+def thrust_scan(tensor: torch.Tensor) -> None:
+    """src/thrust_scan.cu:9-18 — in-place inclusive prefix sum (int32; int64 also accepted)."""
+    _check_cuda(tensor, "tensor")
+    _check_contig(tensor, "tensor")
+    check(lib.shmt_scan(_ctx(tensor.device), _ptr(tensor), _int_code(tensor, "thrust_scan"),
+                        tensor.numel(), 0, _stream(tensor.device)))
+
+
+def exclusive_scan_(tensor: torch.Tensor) -> None:
+    """In-place exclusive prefix sum (the reference's internal cub_exclusiveSum)."""
+    _check_cuda(tensor, "tensor")
+    _check_contig(tensor, "tensor")
+    check(lib.shmt_scan(_ctx(tensor.device), _ptr(tensor), _int_code(tensor, "exclusive_scan_"),
+                        tensor.numel(), 1, _stream(tensor.device)))
+
+
+def tensor_relabel(tensors: List[torch.Tensor]):
+    """src/tensor_relabel.cu:125-209 — ``(unique, [relabelled ...])``.
+
+    ``unique`` lists the distinct ids of ``cat(tensors)`` in first-occurrence
+    order; each returned tensor holds, for its input, the index into ``unique``.
+    """
+    if len(tensors) == 0:
+        raise RuntimeError("tensor_relabel: expected a non-empty list of tensors")
+    dt, dev = tensors[0].dtype, tensors[0].device
+    for t in tensors:
+        _check_cuda(t, "tensors")
+        if t.dtype != dt or t.device != dev:
+            raise RuntimeError("tensor_relabel: all tensors must share dtype and device")
+    code = _INT_CODES.get(dt)
+    if code is None:
+        raise RuntimeError(f"tensor_relabel: ID can only be int32 or int64, got {dt}")
+    sizes = [t.numel() for t in tensors]
+    parts = [t.contiguous().reshape(-1) for t in tensors]
+    if len(parts) > 8:
+        parts = [torch.cat(parts, 0)]
+    total = sum(sizes)
+    unique = torch.empty(total, dtype=dt, device=dev)
+    relabel = torch.empty(total, dtype=dt, device=dev)
+    n_parts = len(parts)
+    ptrs = (C.c_void_p * n_parts)(*[_ptr(p) for p in parts])
+    lens = (C.c_int64 * n_parts)(*[p.numel() for p in parts])
+    n_unique = C.c_int64(0)
+    check(lib.shmt_relabel(_ctx(dev), ptrs, lens, n_parts, code, _ptr(unique), _ptr(relabel),
+                           C.byref(n_unique), _stream(dev)))
+    return unique[:n_unique.value], list(relabel.split_with_sizes(sizes, 0))
+
+
+# --------------------------------------------------------------------------- sampling
+def _sample(indptr, indices, gpu_indptr, gpu_indices, hashmap, seeds, num_picks, replace, who):
+    _check_cuda(seeds, "seeds")
+    seeds = seeds.contiguous()
+    dev = seeds.device
+    for t, nm in ((indptr, "indptr"), (indices, "indices")):
+        _check_contig(t, nm)
+    pdt, xdt, sdt = _int_code(indptr, who), _int_code(indices, who), _int_code(seeds, who)
+    if hashmap is not None:
+        _check_cuda(gpu_indptr, "gpu_indptr")
+        _check_cuda(gpu_indices, "gpu_indices")
+        if gpu_indptr.dtype != indptr.dtype or gpu_indices.dtype != indices.dtype:
+            raise RuntimeError(f"{who}: the cached CSR must have the dtypes of the host CSR")
+    n, k = seeds.numel(), int(num_picks)
+    sub_indptr = torch.empty(n + 1, dtype=indptr.dtype, device=dev)
+    sub_indices = torch.empty(n * k, dtype=indices.dtype, device=dev)
+    nnz = C.c_int64(0)
+    _rng["calls"] += 1
+    check(lib.shmt_sample_hop(_ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr),
+                              _ptr(gpu_indices), hashmap._handle if hashmap is not None else None,
+                              _ptr(seeds), sdt, n, k, int(bool(replace)), _rng["seed"],
+                              _rng["calls"], sub_indptr.data_ptr(), _ptr(sub_indices),
+                              C.byref(nnz), _stream(dev)))
+    return sub_indptr, sub_indices[:nnz.value]
+
+
+def csr_sampling(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.Tensor,
+                 num_picks: int, replace: bool):
+    """src/cache_graph_sampling.cu:179-220 — ``(sub_indptr, sub_indices)`` for one hop."""
+    return _sample(indptr, indices, None, None, None, seeds, num_picks, replace, "csr_sampling")
+
+
+def csr_cache_sampling(uva_indptr: torch.Tensor, uva_indices: torch.Tensor,
+                       gpu_indptr: torch.Tensor, gpu_indices: torch.Tensor,
+                       hashmap: CUCOStaticHashmap, seeds: torch.Tensor, num_picks: int,
+                       replace: bool):
+    """src/cache_graph_sampling.cu:382-426 — cached rows from the GPU CSR, the rest over UVA."""
+    return _sample(uva_indptr, uva_indices, gpu_indptr, gpu_indices, hashmap, seeds, num_picks,
+                   replace, "csr_cache_sampling")
+
+
+def create_subcsr(uva_indptr: torch.Tensor, uva_indices: torch.Tensor, seeds: torch.Tensor):
+    """src/cache_graph_sampling.cu:455-492 — compact GPU CSR of the rows ``seeds``, in order."""
+    _check_cuda(seeds, "seeds")
+    seeds = seeds.contiguous()
+    dev = seeds.device
+    _check_contig(uva_indptr, "uva_indptr")
+    _check_contig(uva_indices, "uva_indices")
+    pdt = _int_code(uva_indptr, "create_subcsr")
+    xdt = _int_code(uva_indices, "create_subcsr")
+    sdt = _int_code(seeds, "create_subcsr")
+    n = seeds.numel()
+    gpu_indptr = torch.empty(n + 1, dtype=uva_indptr.dtype, device=dev)
+    nnz = C.c_int64(0)
+    check(lib.shmt_subcsr_count(_ctx(dev), _ptr(uva_indptr), pdt, _ptr(seeds), sdt, n,
+                                gpu_indptr.data_ptr(), C.byref(nnz), _stream(dev)))
+    gpu_indices = torch.empty(nnz.value, dtype=uva_indices.dtype, device=dev)
+    check(lib.shmt_subcsr_fill(_ptr(uva_indptr), pdt, _ptr(uva_indices), xdt, _ptr(seeds), sdt, n,
+                               gpu_indptr.data_ptr(), _ptr(gpu_indices), _stream(dev)))
+    return gpu_indptr, gpu_indices

@@ -1,0 +1,112 @@
+// Context, error text and small device utilities of libshmt.
+#include <stdarg.h>
+#include <string.h>
+
+#include "ctx.cuh"
+
+namespace shmt {
+
+static thread_local char g_error[1024] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+int ctx_reserve(shmt_ctx* ctx, size_t bytes) {
+  bytes += 256;  // result words live in front of the region
+  if (bytes <= ctx->scratch_bytes) return SHMT_OK;
+  // cudaFree waits for work that may still read the old block.
+  if (ctx->scratch) SHMT_CUDA_TRY(cudaFree(ctx->scratch));
+  ctx->scratch = nullptr;
+  ctx->scratch_bytes = 0;
+  size_t want = bytes + bytes / 2;
+  if (want < ((size_t)1 << 20)) want = (size_t)1 << 20;
+  want = (want + 255) & ~(size_t)255;
+  void* p = nullptr;
+  SHMT_CUDA_TRY(cudaMalloc(&p, want));
+  ctx->scratch = static_cast<char*>(p);
+  ctx->scratch_bytes = want;
+  return SHMT_OK;
+}
+
+int ctx_fetch_words(shmt_ctx* ctx, cudaStream_t stream, const char* what) {
+  SHMT_CUDA_TRY(cudaMemcpyAsync(ctx->h_words, ctx->d_words(), 4 * sizeof(int64_t),
+                                cudaMemcpyDeviceToHost, stream));
+  SHMT_CUDA_TRY(cudaStreamSynchronize(stream));
+  const int64_t st = ctx->h_words[W_STATUS];
+  if (st == DEV_TIMEOUT) {
+    set_error("%s: a bounded look-back wait ran out (device status %lld)", what, (long long)st);
+    return SHMT_ERR_TIMEOUT;
+  }
+  if (st == DEV_OVERFLOW) {
+    set_error("%s: table overflow (device status %lld)", what, (long long)st);
+    return SHMT_ERR_CAPACITY;
+  }
+  return SHMT_OK;
+}
+
+}  // namespace shmt
+
+using namespace shmt;
+
+extern "C" {
+
+const char* shmt_last_error(void) { return g_error; }
+
+int shmt_version(void) { return 100; }
+
+int shmt_ctx_create(int device, shmt_ctx** out) {
+  SHMT_REQUIRE(out != nullptr, "shmt_ctx_create: out is null");
+  int ndev = 0;
+  SHMT_CUDA_TRY(cudaGetDeviceCount(&ndev));
+  SHMT_REQUIRE(device >= 0 && device < ndev, "shmt_ctx_create: device %d out of range (%d devices)",
+               device, ndev);
+  DeviceGuard guard(device);
+  shmt_ctx* ctx = new shmt_ctx();
+  ctx->device = device;
+  void* h = nullptr;
+  cudaError_t e = cudaHostAlloc(&h, kCtxWords * sizeof(int64_t), cudaHostAllocDefault);
+  if (e != cudaSuccess) {
+    set_error("shmt_ctx_create: %s", cudaGetErrorString(e));
+    delete ctx;
+    return SHMT_ERR_CUDA;
+  }
+  if (int rc = ctx_reserve(ctx, 0)) {
+    cudaFreeHost(h);
+    delete ctx;
+    return rc;
+  }
+  ctx->h_words = static_cast<int64_t*>(h);
+  memset(ctx->h_words, 0, kCtxWords * sizeof(int64_t));
+  *out = ctx;
+  return SHMT_OK;
+}
+
+int shmt_ctx_destroy(shmt_ctx* ctx) {
+  if (!ctx) return SHMT_OK;
+  DeviceGuard guard(ctx->device);
+  if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->h_words) cudaFreeHost(ctx->h_words);
+  delete ctx;
+  return SHMT_OK;
+}
+
+int64_t shmt_ctx_scratch_bytes(const shmt_ctx* ctx) { return ctx ? (int64_t)ctx->scratch_bytes : 0; }
+
+}  // extern "C"

@@ -1,0 +1,41 @@
+// Per-device context: reusable scratch + result words (host side).
+#pragma once
+
+#include "common.cuh"
+
+struct shmt_ctx {
+  int device = 0;
+  char* scratch = nullptr;      // device scratch, grown geometrically; the first
+  size_t scratch_bytes = 0;     // 256 bytes are the result words (status, result, ticket ...)
+  int64_t* h_words = nullptr;   // pinned host mirror of the result words
+  int64_t* d_words() const { return reinterpret_cast<int64_t*>(scratch); }
+  char* region() const { return scratch + 256; }
+};
+
+namespace shmt {
+
+constexpr int kCtxWords = 32;
+enum : int { W_STATUS = 0, W_RESULT = 1, W_TICKET = 2, W_DONE = 3 };
+
+// Make sure ctx->region() holds at least `bytes` (256-byte aligned base).
+int ctx_reserve(shmt_ctx* ctx, size_t bytes);
+
+// Copy the first `n_words` result words to the host and wait for `stream`.
+// Returns SHMT_ERR_TIMEOUT / SHMT_ERR_CAPACITY if the kernel flagged either.
+int ctx_fetch_words(shmt_ctx* ctx, cudaStream_t stream, const char* what);
+
+// RAII device guard for entry points that are handed a context or a map.
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) == cudaSuccess && prev != device) {
+      switched = cudaSetDevice(device) == cudaSuccess;
+    }
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
+
+}  // namespace shmt

@@ -1,0 +1,253 @@
+// Host memory substrate: POSIX shared memory, mmap'ed .npy files and host
+// registration.  Host-only code; the kernels read these buffers through UVA.
+// Behaviour follows the reference's include/shm_memory.h:6-49, include/utils.h:5-13,
+// src/mmap_tensor.cc:10-55, src/cnpy.cc:18-86 and src/cache_feature_fetch.cu:6-13,
+// except that failures come back as status codes instead of aborting.
+#include <cuda_runtime.h>
+#include <errno.h>
+#include <fcntl.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <string>
+
+#include "shmt.h"
+
+namespace shmt {
+void set_error(const char* fmt, ...);
+}
+using shmt::set_error;
+
+namespace {
+
+int register_host(void* ptr, size_t size, unsigned flags, const char* who) {
+  cudaError_t e = cudaHostRegister(ptr, size, flags);
+  if (e != cudaSuccess) {
+    set_error("%s: cudaHostRegister(%zu bytes) failed: %s", who, size, cudaGetErrorString(e));
+    return SHMT_ERR_CUDA;
+  }
+  return SHMT_OK;
+}
+
+int map_shared(const char* who, const char* name, int64_t size, int pin_memory, bool create,
+               int64_t* out_ptr, int64_t* out_fd) {
+  if (!name || !out_ptr || !out_fd || size <= 0) {
+    set_error("%s: bad argument (name/size/out)", who);
+    return SHMT_ERR_INVALID;
+  }
+  const int flag = create ? (O_RDWR | O_CREAT) : O_RDWR;
+  const int fd = shm_open(name, flag, S_IRUSR | S_IWUSR);
+  if (fd == -1) {
+    set_error("%s: fail to open %s: %s", who, name, strerror(errno));
+    return SHMT_ERR_OS;
+  }
+  if (create && ftruncate(fd, (off_t)size) == -1) {
+    set_error("%s: failed to truncate %s to %lld bytes: %s", who, name, (long long)size,
+              strerror(errno));
+    close(fd);
+    shm_unlink(name);
+    return SHMT_ERR_OS;
+  }
+  void* ptr = mmap(nullptr, (size_t)size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  if (ptr == MAP_FAILED) {
+    set_error("%s: failed to map shared memory %s: %s", who, name, strerror(errno));
+    close(fd);
+    if (create) shm_unlink(name);
+    return SHMT_ERR_OS;
+  }
+  if (pin_memory) {
+    if (int rc = register_host(ptr, (size_t)size, cudaHostRegisterDefault, who)) {
+      munmap(ptr, (size_t)size);
+      close(fd);
+      if (create) shm_unlink(name);
+      return rc;
+    }
+  }
+  *out_ptr = (int64_t)(intptr_t)ptr;
+  *out_fd = fd;
+  return SHMT_OK;
+}
+
+// Value of a key in the Python-dict text of an .npy header, e.g. 'descr': '<f4'.
+bool find_after(const std::string& h, const char* key, size_t* pos) {
+  const size_t k = h.find(key);
+  if (k == std::string::npos) return false;
+  const size_t c = h.find(':', k);
+  if (c == std::string::npos) return false;
+  size_t p = c + 1;
+  while (p < h.size() && h[p] == ' ') ++p;
+  *pos = p;
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+int shmt_shm_create(const char* name, int64_t size, int pin_memory, int64_t* out_ptr,
+                    int64_t* out_fd) {
+  return map_shared("shmt_shm_create", name, size, pin_memory, true, out_ptr, out_fd);
+}
+
+int shmt_shm_open(const char* name, int64_t size, int pin_memory, int64_t* out_ptr,
+                  int64_t* out_fd) {
+  return map_shared("shmt_shm_open", name, size, pin_memory, false, out_ptr, out_fd);
+}
+
+int shmt_shm_release(const char* name, int64_t size, int64_t ptr, int64_t fd, int pin_memory) {
+  if (!name || !ptr) {
+    set_error("shmt_shm_release: bad argument");
+    return SHMT_ERR_INVALID;
+  }
+  int rc = SHMT_OK;
+  if (pin_memory) {
+    cudaError_t e = cudaHostUnregister((void*)(intptr_t)ptr);
+    if (e != cudaSuccess) {
+      set_error("shmt_shm_release: cudaHostUnregister failed: %s", cudaGetErrorString(e));
+      rc = SHMT_ERR_CUDA;
+    }
+  }
+  if (munmap((void*)(intptr_t)ptr, (size_t)size) == -1) {
+    set_error("shmt_shm_release: munmap failed: %s", strerror(errno));
+    rc = SHMT_ERR_OS;
+  }
+  close((int)fd);
+  shm_unlink(name);
+  return rc;
+}
+
+int shmt_shm_exists(const char* name) {
+  if (!name) return 0;
+  const int fd = shm_open(name, O_RDONLY, S_IRUSR | S_IWUSR);
+  if (fd >= 0) {
+    close(fd);
+    return 1;
+  }
+  return 0;
+}
+
+int shmt_npy_open(const char* path, int pin_memory, shmt_npy_info* out) {
+  if (!path || !out) {
+    set_error("shmt_npy_open: bad argument");
+    return SHMT_ERR_INVALID;
+  }
+  memset(out, 0, sizeof(*out));
+  const int fd = open(path, O_RDWR, S_IRUSR | S_IWUSR);
+  if (fd == -1) {
+    set_error("npy_load: Unable to open file %s: %s", path, strerror(errno));
+    return SHMT_ERR_OS;
+  }
+  struct stat sb;
+  if (fstat(fd, &sb) == -1 || sb.st_size < 10) {
+    set_error("shmt_npy_open: %s is not an .npy file", path);
+    close(fd);
+    return SHMT_ERR_OS;
+  }
+  const size_t file_size = (size_t)sb.st_size;
+  void* base = mmap(nullptr, file_size, PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  if (base == MAP_FAILED) {
+    set_error("shmt_npy_open: mmap of %s failed: %s", path, strerror(errno));
+    close(fd);
+    return SHMT_ERR_OS;
+  }
+  const unsigned char* b = static_cast<const unsigned char*>(base);
+  auto fail = [&](const char* why) {
+    set_error("parse_npy_header: %s (%s)", why, path);
+    munmap(base, file_size);
+    close(fd);
+    return SHMT_ERR_INVALID;
+  };
+  if (memcmp(b, "\x93NUMPY", 6) != 0) return fail("bad magic");
+  const int major = b[6];
+  size_t hlen = 0, hstart = 0;
+  if (major == 1) {
+    hlen = b[8] | (b[9] << 8);
+    hstart = 10;
+  } else if (major == 2 || major == 3) {
+    if (file_size < 12) return fail("truncated header");
+    hlen = (size_t)b[8] | ((size_t)b[9] << 8) | ((size_t)b[10] << 16) | ((size_t)b[11] << 24);
+    hstart = 12;
+  } else {
+    return fail("unsupported .npy version");
+  }
+  if (hstart + hlen > file_size) return fail("truncated header");
+  const std::string h(reinterpret_cast<const char*>(b + hstart), hlen);
+
+  size_t p = 0;
+  if (!find_after(h, "fortran_order", &p))
+    return fail("failed to find header keyword: 'fortran_order'");
+  out->fortran_order = h.compare(p, 4, "True") == 0;
+  if (!find_after(h, "descr", &p)) return fail("failed to find header keyword: 'descr'");
+  if (p >= h.size() || (h[p] != '\'' && h[p] != '"')) return fail("structured dtypes are not supported");
+  const size_t q = h.find(h[p], p + 1);
+  if (q == std::string::npos || q - p - 1 >= sizeof(out->descr)) return fail("bad descr");
+  memcpy(out->descr, h.data() + p + 1, q - p - 1);
+  if (!find_after(h, "shape", &p)) return fail("failed to find header keyword: 'shape'");
+  const size_t lp = h.find('(', p), rp = h.find(')', p);
+  if (lp == std::string::npos || rp == std::string::npos || rp < lp)
+    return fail("failed to find header keyword: '(' or ')'");
+  int ndim = 0;
+  size_t i = lp + 1;
+  while (i < rp) {
+    while (i < rp && (h[i] < '0' || h[i] > '9')) ++i;
+    if (i >= rp) break;
+    int64_t v = 0;
+    while (i < rp && h[i] >= '0' && h[i] <= '9') v = v * 10 + (h[i++] - '0');
+    if (ndim >= 8) return fail("more than 8 dimensions");
+    out->shape[ndim++] = v;
+  }
+  out->ndim = ndim;
+  out->data_offset = (int64_t)(hstart + hlen);
+  out->file_size = (int64_t)file_size;
+  out->ptr = (int64_t)(intptr_t)base;
+  out->fd = fd;
+  if (pin_memory) {
+    // like the reference, register the whole mapping (header included)
+    if (int rc = register_host(base, file_size, cudaHostRegisterDefault, "shmt_npy_open")) {
+      munmap(base, file_size);
+      close(fd);
+      return rc;
+    }
+  }
+  return SHMT_OK;
+}
+
+int shmt_npy_close(int64_t size, int64_t ptr, int64_t fd, int pin_memory) {
+  int rc = SHMT_OK;
+  if (pin_memory) {
+    cudaError_t e = cudaHostUnregister((void*)(intptr_t)ptr);
+    if (e != cudaSuccess) {
+      set_error("shmt_npy_close: cudaHostUnregister failed: %s", cudaGetErrorString(e));
+      rc = SHMT_ERR_CUDA;
+    }
+  }
+  if (munmap((void*)(intptr_t)ptr, (size_t)size) == -1) {
+    set_error("shmt_npy_close: munmap failed: %s", strerror(errno));
+    rc = SHMT_ERR_OS;
+  }
+  close((int)fd);
+  return rc;
+}
+
+int shmt_host_register(void* ptr, int64_t nbytes) {
+  if (!ptr || nbytes <= 0) {
+    set_error("shmt_host_register: bad argument");
+    return SHMT_ERR_INVALID;
+  }
+  return register_host(ptr, (size_t)nbytes, cudaHostRegisterPortable, "shmt_host_register");
+}
+
+int shmt_host_unregister(void* ptr) {
+  cudaError_t e = cudaHostUnregister(ptr);
+  if (e != cudaSuccess) {
+    set_error("shmt_host_unregister: %s", cudaGetErrorString(e));
+    return SHMT_ERR_CUDA;
+  }
+  return SHMT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,171 @@
+// Static hashmap: creation, bulk insert_or_assign, bulk query.
+// Replaces pycuco::CUCOHashmap / CUCOHashmapWrapper of the reference
+// (include/cuco_hashmap.cuh:49-93, src/cuco_hashmap.cu:10-41).
+#include "ctx.cuh"
+#include "map.cuh"
+
+namespace shmt {
+
+constexpr int kMapThreads = 256;
+
+__global__ void __launch_bounds__(kMapThreads)
+map_insert_kernel(MapView m, const void* __restrict__ keys, int keys64,
+                  const void* __restrict__ vals, int vals64, int64_t n, int64_t* meta) {
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const unsigned lane = threadIdx.x & 31;
+  const int64_t n_batches = (n + 31) >> 5;
+  int64_t total_new = 0;
+  for (int64_t b = warp; b < n_batches; b += n_warps) {
+    const int64_t i = b * 32 + lane;
+    const bool valid = i < n;
+    const int64_t k = valid ? load_int(keys, keys64, i) : kEmptyKey;
+    const int64_t v = valid ? load_int(vals, vals64, i) : -1;
+    int n_new = 0;
+    warp_insert(m, k, v, valid, /*assign=*/true, meta, &n_new);
+    total_new += n_new;
+  }
+  if (lane == 0 && total_new)
+    atomicAdd(reinterpret_cast<unsigned long long*>(meta + 1), (unsigned long long)total_new);
+}
+
+__global__ void __launch_bounds__(kMapThreads)
+map_query_kernel(MapView m, const void* __restrict__ req, int req64, int64_t n,
+                 void* __restrict__ out, int out64) {
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const unsigned lane = threadIdx.x & 31;
+  const int64_t n_batches = (n + 31) >> 5;
+  for (int64_t b = warp; b < n_batches; b += n_warps) {
+    const int64_t i = b * 32 + lane;
+    const bool valid = i < n;
+    const int64_t k = valid ? load_int(req, req64, i) : kEmptyKey;
+    const int64_t v = warp_find(m, k, valid);
+    if (valid) store_int(out, out64, i, v);
+  }
+}
+
+inline unsigned grid_for_warps(int64_t n_items_per_warp32) {
+  const int64_t batches = (n_items_per_warp32 + 31) / 32;
+  int64_t blocks = (batches + kMapThreads / 32 - 1) / (kMapThreads / 32);
+  const int64_t cap = (int64_t)sm_count() * 32;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (unsigned)blocks;
+}
+
+inline uint64_t windows_for(int64_t capacity) {
+  // 1/16 slack over the requested capacity keeps probes short even when the
+  // caller asks for load factor 1.0
+  const uint64_t slots = (uint64_t)capacity + (uint64_t)capacity / 16 + kWindow;
+  return (slots + kWindow - 1) / kWindow;
+}
+
+}  // namespace shmt
+
+using namespace shmt;
+
+extern "C" {
+
+int64_t shmt_map_table_bytes(int64_t capacity) {
+  if (capacity < 0) return 0;
+  return (int64_t)(windows_for(capacity) * kWindow * sizeof(Slot) + 256);
+}
+
+int shmt_map_create(int device, int64_t capacity, int key_dtype, int val_dtype, void* table_buf,
+                    void* stream, shmt_map** out) {
+  SHMT_REQUIRE(out != nullptr, "shmt_map_create: out is null");
+  SHMT_REQUIRE(capacity >= 0, "shmt_map_create: negative capacity");
+  SHMT_REQUIRE(valid_int_dtype(key_dtype) && valid_int_dtype(val_dtype),
+               "shmt_map_create: keys and values can only be int32 or int64");
+  SHMT_REQUIRE(((uintptr_t)table_buf & 15) == 0, "shmt_map_create: table buffer must be 16-byte aligned");
+  DeviceGuard guard(device);
+  shmt_map* m = new shmt_map();
+  m->device = device;
+  m->capacity = capacity;
+  m->key_dtype = key_dtype;
+  m->val_dtype = val_dtype;
+  m->table_bytes = (size_t)shmt_map_table_bytes(capacity);
+  void* buf = table_buf;
+  if (!buf) {
+    cudaError_t e = cudaMalloc(&buf, m->table_bytes);
+    if (e != cudaSuccess) {
+      set_error("shmt_map_create: cudaMalloc of %zu bytes failed: %s", m->table_bytes,
+                cudaGetErrorString(e));
+      delete m;
+      return SHMT_ERR_CUDA;
+    }
+    m->owns_table = true;
+  }
+  m->view.slots = static_cast<Slot*>(buf);
+  m->view.n_windows = windows_for(capacity);
+  m->view.key32 = key_dtype == SHMT_I32;
+  m->d_meta = reinterpret_cast<int64_t*>(static_cast<char*>(buf) + m->table_bytes - 256);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // every slot {-1, -1}; then the trailing status / size words to zero
+  cudaError_t e = cudaMemsetAsync(buf, 0xFF, m->table_bytes - 256, s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(m->d_meta, 0, 256, s);
+  if (e != cudaSuccess) {
+    set_error("shmt_map_create: memset failed: %s", cudaGetErrorString(e));
+    if (m->owns_table) cudaFree(buf);
+    delete m;
+    return SHMT_ERR_CUDA;
+  }
+  *out = m;
+  return SHMT_OK;
+}
+
+int shmt_map_insert(shmt_map* map, const void* keys, const void* values, int64_t n, void* stream) {
+  SHMT_REQUIRE(map != nullptr, "shmt_map_insert: map is null");
+  SHMT_REQUIRE(n >= 0, "shmt_map_insert: negative count");
+  if (n == 0) return SHMT_OK;
+  SHMT_REQUIRE(keys != nullptr && values != nullptr, "shmt_map_insert: keys/values are null");
+  DeviceGuard guard(map->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  map_insert_kernel<<<grid_for_warps(n), kMapThreads, 0, s>>>(
+      map->view, keys, map->key_dtype == SHMT_I64, values, map->val_dtype == SHMT_I64, n,
+      map->d_meta);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  int64_t meta[2] = {0, 0};
+  SHMT_CUDA_TRY(cudaMemcpyAsync(meta, map->d_meta, sizeof(meta), cudaMemcpyDeviceToHost, s));
+  SHMT_CUDA_TRY(cudaStreamSynchronize(s));
+  map->size = meta[1];
+  if (meta[0] == DEV_OVERFLOW) {
+    set_error("shmt_map_insert: table overflow (%lld keys stored, capacity %lld)",
+              (long long)meta[1], (long long)map->capacity);
+    return SHMT_ERR_CAPACITY;
+  }
+  return SHMT_OK;
+}
+
+int shmt_map_query(const shmt_map* map, const void* requests, int req_dtype, int64_t n, void* out,
+                   void* stream) {
+  SHMT_REQUIRE(map != nullptr, "shmt_map_query: map is null");
+  SHMT_REQUIRE(valid_int_dtype(req_dtype), "shmt_map_query: requests can only be int32 or int64");
+  SHMT_REQUIRE(n >= 0, "shmt_map_query: negative count");
+  if (n == 0) return SHMT_OK;
+  SHMT_REQUIRE(requests != nullptr && out != nullptr, "shmt_map_query: requests/out are null");
+  DeviceGuard guard(map->device);
+  map_query_kernel<<<grid_for_warps(n), kMapThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      map->view, requests, req_dtype == SHMT_I64, n, out, map->val_dtype == SHMT_I64);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  return SHMT_OK;
+}
+
+int64_t shmt_map_capacity(const shmt_map* map) { return map ? map->capacity : 0; }
+int64_t shmt_map_memory_usage(const shmt_map* map) { return map ? (int64_t)map->table_bytes : 0; }
+int64_t shmt_map_size(const shmt_map* map) { return map ? map->size : 0; }
+int shmt_map_key_dtype(const shmt_map* map) { return map ? map->key_dtype : -1; }
+int shmt_map_val_dtype(const shmt_map* map) { return map ? map->val_dtype : -1; }
+
+int shmt_map_destroy(shmt_map* map) {
+  if (!map) return SHMT_OK;
+  if (map->owns_table) {
+    DeviceGuard guard(map->device);
+    cudaFree(map->view.slots);
+  }
+  delete map;
+  return SHMT_OK;
+}
+
+}  // extern "C"

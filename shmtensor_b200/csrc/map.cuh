@@ -1,0 +1,207 @@
+// Static open-addressing hashmap for sm_100a: device view + cooperative probes.
+//
+// Layout: 16-byte slots {int64 key, int64 value}, grouped in windows of 4 slots
+// (64 bytes, half a cache line).  A key's home window is mulhi(mix64(key),
+// n_windows); probing is linear over windows.  A 4-lane tile inspects one
+// window per step (each lane one 16-byte load) and votes with a ballot, so a
+// warp resolves 8 keys per step and 32 keys with four independent steps in
+// flight.  Keys are never deleted, so an empty slot ends a probe.
+// Empty key = -1 (the reference's sentinel, include/cuco_hashmap.cuh:58-59);
+// int32 keys are stored sign-extended, int32 values likewise.
+#pragma once
+
+#include "common.cuh"
+
+namespace shmt {
+
+struct __align__(16) Slot {
+  long long key;
+  long long val;
+};
+
+struct MapView {
+  Slot* slots;         // nullptr: no map (every lookup misses)
+  uint64_t n_windows;  // table holds 4 * n_windows slots
+  int key32;           // narrow lookups to int32 first (map built from int32 keys)
+};
+
+constexpr int kWindow = 4;
+
+}  // namespace shmt
+
+struct shmt_map {
+  int device = 0;
+  shmt::MapView view{nullptr, 0, 0};
+  int64_t capacity = 0;  // as requested; what capacity() reports
+  int key_dtype = SHMT_I64;
+  int val_dtype = SHMT_I64;
+  bool owns_table = false;
+  size_t table_bytes = 0;
+  int64_t* d_meta = nullptr;  // device: [0] status, [1] number of keys stored
+  int64_t size = 0;
+};
+
+namespace shmt {
+
+inline MapView view_of(const shmt_map* m) {
+  return m ? m->view : MapView{nullptr, 0, 0};
+}
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ int64_t narrow_key(const MapView& m, int64_t k) {
+  return m.key32 ? (int64_t)(int32_t)k : k;
+}
+
+__device__ __forceinline__ uint64_t home_window(const MapView& m, int64_t k) {
+  return __umul64hi(mix64((uint64_t)k), m.n_windows);
+}
+
+// Look up one key per lane.  All 32 lanes of the warp must call; lanes with
+// valid == false take part in the votes only.  Returns the value or -1.
+__device__ __forceinline__ int64_t warp_find(const MapView& m, int64_t key, bool valid) {
+  const unsigned full = 0xffffffffu;
+  const unsigned lane = threadIdx.x & 31, sub = lane & 3, tile = lane >> 2;
+  key = narrow_key(m, key);
+  if (key == kEmptyKey) valid = false;
+  const longlong2* slots = reinterpret_cast<const longlong2*>(m.slots);
+
+  longlong2 s[4];
+  int64_t kr[4];
+  int vr[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int src = r * 8 + tile;
+    kr[r] = __shfl_sync(full, key, src);
+    vr[r] = __shfl_sync(full, (int)valid, src);
+    s[r] = make_longlong2(kEmptyKey, -1);
+    if (vr[r]) s[r] = __ldg(slots + home_window(m, kr[r]) * kWindow + sub);
+  }
+  int64_t result = -1;
+  int more = 0;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const bool match = vr[r] && s[r].x == kr[r];
+    const bool empty = !vr[r] || s[r].x == kEmptyKey;
+    const unsigned mb = (__ballot_sync(full, match) >> (tile * 4)) & 0xFu;
+    const unsigned eb = (__ballot_sync(full, empty) >> (tile * 4)) & 0xFu;
+    const int from = mb ? (int)(tile * 4 + __ffs(mb) - 1) : (int)lane;
+    const int64_t val = __shfl_sync(full, s[r].y, from);
+    const int64_t res = mb ? val : -1;
+    const int cont = (!mb && !eb) ? 1 : 0;
+    const int64_t rv = __shfl_sync(full, res, (lane & 7) * 4);
+    const int rc = __shfl_sync(full, cont, (lane & 7) * 4);
+    if ((int)(lane >> 3) == r) {
+      result = rv;
+      more = rc;
+    }
+  }
+  if (more) {
+    // rare: the home window was full of other keys; walk on slot by slot
+    const uint64_t n_slots = m.n_windows * kWindow;
+    uint64_t w = home_window(m, key) + 1;
+    if (w == m.n_windows) w = 0;
+    uint64_t pos = w * kWindow;
+    for (uint64_t step = kWindow; step < n_slots; ++step) {
+      const longlong2 c = __ldg(slots + pos);
+      if (c.x == key) {
+        result = c.y;
+        break;
+      }
+      if (c.x == kEmptyKey) break;
+      pos = pos + 1 == n_slots ? 0 : pos + 1;
+    }
+  }
+  return result;
+}
+
+// 16-byte compare-and-swap on one slot (atom.cas.b128, sm_90+): key and value
+// become visible together, so no reader ever sees a claimed slot without its value.
+__device__ __forceinline__ longlong2 cas_slot(Slot* p, longlong2 expect, longlong2 desired) {
+  longlong2 old;
+  asm volatile(
+      "{\n\t"
+      ".reg .b128 c, s, o;\n\t"
+      "mov.b128 c, {%2, %3};\n\t"
+      "mov.b128 s, {%4, %5};\n\t"
+      "atom.global.cas.b128 o, [%6], c, s;\n\t"
+      "mov.b128 {%0, %1}, o;\n\t"
+      "}"
+      : "=l"(old.x), "=l"(old.y)
+      : "l"(expect.x), "l"(expect.y), "l"(desired.x), "l"(desired.y), "l"(p)
+      : "memory");
+  return old;
+}
+
+// Insert one (key, value) per lane; all 32 lanes must call.  A key already in
+// the table keeps its slot; its value is replaced only if `assign`.  Returns
+// the value now stored for the key (-1 for invalid lanes or on overflow) and
+// counts newly stored keys in *n_new (warp total, same on every lane).
+__device__ __forceinline__ int64_t warp_insert(const MapView& m, int64_t key, int64_t val,
+                                               bool valid, bool assign, int64_t* status_word,
+                                               int* n_new) {
+  const unsigned full = 0xffffffffu;
+  const unsigned lane = threadIdx.x & 31, sub = lane & 3, tile = lane >> 2;
+  key = narrow_key(m, key);
+  if (key == kEmptyKey) valid = false;
+  int64_t result = -1;
+  int added = 0;
+#pragma unroll 1
+  for (int r = 0; r < 4; ++r) {
+    const int src = r * 8 + tile;
+    const int64_t k = __shfl_sync(full, key, src);
+    const int64_t v = __shfl_sync(full, val, src);
+    bool done = !__shfl_sync(full, (int)valid, src);
+    uint64_t w = done ? 0 : home_window(m, k);
+    uint64_t steps = 0;
+    int64_t res = -1;
+    bool newly = false;
+    while (__any_sync(full, !done)) {
+      Slot* p = m.slots + w * kWindow + sub;
+      longlong2 s = make_longlong2(0, 0);
+      if (!done) s = __ldcg(reinterpret_cast<const longlong2*>(p));
+      const bool match = !done && s.x == k;
+      const bool empty = !done && s.x == kEmptyKey;
+      const unsigned mb = (__ballot_sync(full, match) >> (tile * 4)) & 0xFu;
+      const unsigned eb = (__ballot_sync(full, empty) >> (tile * 4)) & 0xFu;
+      bool ok = false;
+      if (!done && !mb && eb && (int)sub == __ffs(eb) - 1) {
+        const longlong2 old =
+            cas_slot(p, make_longlong2(kEmptyKey, -1), make_longlong2(k, v));
+        ok = old.x == kEmptyKey;
+      }
+      const unsigned okb = (__ballot_sync(full, ok) >> (tile * 4)) & 0xFu;
+      const int from = mb ? (int)(tile * 4 + __ffs(mb) - 1) : (int)lane;
+      const int64_t exist = __shfl_sync(full, s.y, from);
+      if (!done) {
+        if (mb) {
+          if (assign && (int)sub == __ffs(mb) - 1) p->val = v;
+          res = assign ? v : exist;
+          done = true;
+        } else if (okb) {
+          res = v;
+          newly = true;
+          done = true;
+        } else if (!eb) {
+          w = w + 1 == m.n_windows ? 0 : w + 1;
+          if (++steps >= m.n_windows) {
+            if (sub == 0)
+              atomicMax(reinterpret_cast<unsigned long long*>(status_word),
+                        (unsigned long long)DEV_OVERFLOW);
+            done = true;
+          }
+        }
+        // else: the claimed slot went to another key first; re-read this window
+      }
+    }
+    added += __popc(__ballot_sync(full, newly && sub == 0));
+    const int64_t rv = __shfl_sync(full, res, (lane & 7) * 4);
+    if ((int)(lane >> 3) == r) result = rv;
+  }
+  *n_new = added;
+  return result;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace shmt

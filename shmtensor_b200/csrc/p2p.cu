@@ -1,0 +1,83 @@
+// Device buffers shared between ranks of a partitioned cache (CUDA IPC) and the
+// streaming-read probe used to measure HBM / host-link / peer-link ceilings.
+// The reference is single-GPU and has no counterpart for any of this.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace shmt {
+
+// Every thread folds 16-byte loads into a checksum; a few threads publish it so
+// the loads cannot be optimised away.  Plain loads only (no multicast), so the
+// source may be local HBM, pinned host memory or a peer GPU's buffer.
+__global__ void __launch_bounds__(256)
+stream_read_kernel(const uint4* __restrict__ src, int64_t n_vec, unsigned long long* sink) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  uint32_t acc = 0;
+  for (; i + 3 * stride < n_vec; i += 4 * stride) {
+    const uint4 a = ld_stream16(src + i), b = ld_stream16(src + i + stride),
+                c = ld_stream16(src + i + 2 * stride), d = ld_stream16(src + i + 3 * stride);
+    acc ^= a.x ^ a.y ^ a.z ^ a.w ^ b.x ^ b.y ^ b.z ^ b.w ^ c.x ^ c.y ^ c.z ^ c.w ^ d.x ^ d.y ^
+           d.z ^ d.w;
+  }
+  for (; i < n_vec; i += stride) {
+    const uint4 a = ld_stream16(src + i);
+    acc ^= a.x ^ a.y ^ a.z ^ a.w;
+  }
+  if (acc == 0x9E3779B9u) atomicAdd(sink, 1ULL);  // practically never; keeps the loads alive
+}
+
+}  // namespace shmt
+
+using namespace shmt;
+
+extern "C" {
+
+int shmt_dev_alloc(int64_t bytes, void** out) {
+  SHMT_REQUIRE(out != nullptr && bytes > 0, "shmt_dev_alloc: bad argument");
+  SHMT_CUDA_TRY(cudaMalloc(out, (size_t)bytes));
+  return SHMT_OK;
+}
+
+int shmt_dev_free(void* ptr) {
+  if (ptr) SHMT_CUDA_TRY(cudaFree(ptr));
+  return SHMT_OK;
+}
+
+int shmt_ipc_get_handle(void* dev_ptr, void* handle_64_bytes) {
+  SHMT_REQUIRE(dev_ptr && handle_64_bytes, "shmt_ipc_get_handle: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+  cudaIpcMemHandle_t h;
+  SHMT_CUDA_TRY(cudaIpcGetMemHandle(&h, dev_ptr));
+  memcpy(handle_64_bytes, &h, sizeof(h));
+  return SHMT_OK;
+}
+
+int shmt_ipc_open_handle(const void* handle_64_bytes, void** out) {
+  SHMT_REQUIRE(handle_64_bytes && out, "shmt_ipc_open_handle: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle_64_bytes, sizeof(h));
+  SHMT_CUDA_TRY(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+  return SHMT_OK;
+}
+
+int shmt_ipc_close_handle(void* mapped_ptr) {
+  if (mapped_ptr) SHMT_CUDA_TRY(cudaIpcCloseMemHandle(mapped_ptr));
+  return SHMT_OK;
+}
+
+int shmt_stream_read(const void* src, int64_t bytes, void* sink_8_bytes, void* stream) {
+  SHMT_REQUIRE(src && sink_8_bytes && bytes >= 16, "shmt_stream_read: bad argument");
+  SHMT_REQUIRE(((uintptr_t)src & 15) == 0, "shmt_stream_read: src must be 16-byte aligned");
+  const int64_t n_vec = bytes / 16;
+  int64_t blocks = (n_vec + 255) / 256 / 4 + 1;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  stream_read_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0,
+                       static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), n_vec, static_cast<unsigned long long*>(sink_8_bytes));
+  SHMT_CUDA_TRY(cudaGetLastError());
+  return SHMT_OK;
+}
+
+}  // extern "C"

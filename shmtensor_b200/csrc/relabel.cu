@@ -1,0 +1,186 @@
+// Unique (first-occurrence order) + dense remap of concatenated id arrays.
+// Same result as the reference's TensorRelabel (src/tensor_relabel.cu:125-209):
+// unique[j] is the j-th distinct id in order of first appearance and
+// relabel[i] is the position of input[i] in unique.
+//
+// Three kernels instead of the reference's cat + 2 fills + 4 thrust passes + CUB
+// scan: (1) claim a table slot per distinct id and take the minimum input
+// index per slot, remembering each element's slot in the output array;
+// (2) flag first occurrences, scan the flags with a decoupled look-back inside
+// the same kernel, emit unique ids and the slot -> new id table; (3) remap.
+// Every element probes the table once (the reference probes four times).
+#include "ctx.cuh"
+#include "lookback.cuh"
+
+namespace shmt {
+
+constexpr int kRelThreads = 256;
+constexpr int kRelItems = 4;
+constexpr int kRelTile = kRelThreads * kRelItems;
+constexpr int kMaxParts = 8;
+
+struct Parts {
+  const void* ptr[kMaxParts];
+  int64_t start[kMaxParts + 1];  // element offset of each part in the concatenation
+  int n;
+  int is64;
+};
+
+__device__ __forceinline__ int64_t part_elem(const Parts& ps, int64_t i) {
+  int p = 0;
+#pragma unroll
+  for (int q = 1; q < kMaxParts; ++q)
+    if (q < ps.n && i >= ps.start[q]) p = q;
+  return load_int(ps.ptr[p], ps.is64, i - ps.start[p]);
+}
+
+struct RelTable {
+  long long* keys;     // cap entries, -1 = empty
+  unsigned* first;     // cap entries, smallest input index holding the key
+  unsigned* newid;     // cap entries, dense id of the key (written by kernel 2)
+  uint32_t mask;       // cap - 1
+};
+
+__global__ void __launch_bounds__(kRelThreads)
+relabel_insert_kernel(Parts ps, int64_t numel, RelTable t, void* __restrict__ out,
+                      int64_t* words) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
+    const long long key = part_elem(ps, i);
+    uint32_t pos = (uint32_t)mix64((uint64_t)key) & t.mask;
+    uint32_t steps = 0;
+    while (true) {
+      long long cur = __ldcg(t.keys + pos);
+      if (cur == kEmptyKey)
+        cur = (long long)atomicCAS(reinterpret_cast<unsigned long long*>(t.keys + pos),
+                                   (unsigned long long)kEmptyKey, (unsigned long long)key);
+      if (cur == kEmptyKey || cur == key) break;
+      pos = (pos + 1) & t.mask;
+      if (++steps > t.mask) {  // cannot happen at load <= 0.5; bounded all the same
+        atomicMax(reinterpret_cast<unsigned long long*>(words + W_STATUS),
+                  (unsigned long long)DEV_OVERFLOW);
+        break;
+      }
+    }
+    atomicMin(t.first + pos, (unsigned)i);
+    store_int(out, ps.is64, i, (int64_t)pos);
+  }
+}
+
+__global__ void __launch_bounds__(kRelThreads)
+relabel_compact_kernel(Parts ps, int64_t numel, RelTable t, const void* __restrict__ slot_of,
+                       void* __restrict__ unique, TileStates st, int64_t n_tiles, int64_t* words) {
+  __shared__ int64_t warp_sums[32];
+  __shared__ int64_t s_total;
+  __shared__ int64_t s_prefix;
+  __shared__ int s_tile;
+  const int tile = take_tile(words + W_TICKET, &s_tile);
+  const int64_t base = (int64_t)tile * kRelTile + (int64_t)threadIdx.x * kRelItems;
+  uint32_t pos[kRelItems];
+  bool is_first[kRelItems];
+  int64_t cnt = 0;
+#pragma unroll
+  for (int j = 0; j < kRelItems; ++j) {
+    const int64_t i = base + j;
+    is_first[j] = false;
+    if (i < numel) {
+      pos[j] = (uint32_t)load_int(slot_of, ps.is64, i);
+      is_first[j] = __ldg(t.first + pos[j]) == (unsigned)i;
+    }
+    cnt += is_first[j];
+  }
+  const int64_t local = block_exclusive_scan(cnt, warp_sums, &s_total);
+  if (threadIdx.x < 32) {
+    const int64_t p = lookback_exclusive_prefix(st, tile, s_total, words + W_STATUS);
+    if (threadIdx.x == 0) {
+      s_prefix = p;
+      if (tile == n_tiles - 1) words[W_RESULT] = p + s_total;
+    }
+  }
+  __syncthreads();
+  int64_t uid = s_prefix + local;
+#pragma unroll
+  for (int j = 0; j < kRelItems; ++j) {
+    if (is_first[j]) {
+      store_int(unique, ps.is64, uid, part_elem(ps, base + j));
+      t.newid[pos[j]] = (unsigned)uid;
+      ++uid;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kRelThreads)
+relabel_remap_kernel(int64_t numel, const unsigned* __restrict__ newid, void* out, int is64) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
+    const int64_t pos = is64 ? reinterpret_cast<const long long*>(out)[i]
+                             : (int64_t) reinterpret_cast<const int*>(out)[i];
+    store_int(out, is64, i, (int64_t)__ldg(newid + pos));
+  }
+}
+
+}  // namespace shmt
+
+using namespace shmt;
+
+extern "C" int shmt_relabel(shmt_ctx* ctx, const void* const* parts, const int64_t* part_sizes,
+                            int n_parts, int dtype, void* out_unique, void* out_relabel,
+                            int64_t* n_unique_host, void* stream) {
+  SHMT_REQUIRE(ctx != nullptr, "shmt_relabel: ctx is null");
+  SHMT_REQUIRE(valid_int_dtype(dtype), "shmt_relabel: ids can only be int32 or int64");
+  SHMT_REQUIRE(n_parts >= 0 && n_parts <= kMaxParts, "shmt_relabel: 0..%d parts", kMaxParts);
+  SHMT_REQUIRE(n_parts == 0 || (parts && part_sizes), "shmt_relabel: parts/part_sizes are null");
+  Parts ps{};
+  ps.n = n_parts;
+  ps.is64 = dtype == SHMT_I64;
+  int64_t numel = 0;
+  for (int p = 0; p < n_parts; ++p) {
+    SHMT_REQUIRE(part_sizes[p] >= 0, "shmt_relabel: part %d has negative size", p);
+    SHMT_REQUIRE(part_sizes[p] == 0 || parts[p] != nullptr, "shmt_relabel: part %d is null", p);
+    ps.ptr[p] = parts[p];
+    ps.start[p] = numel;
+    numel += part_sizes[p];
+  }
+  for (int p = n_parts; p <= kMaxParts; ++p) ps.start[p] = numel;
+  SHMT_REQUIRE(numel < ((int64_t)1 << 30), "shmt_relabel: %lld ids is too many (limit 2^30)",
+               (long long)numel);
+  if (numel == 0) {
+    if (n_unique_host) *n_unique_host = 0;
+    return SHMT_OK;
+  }
+  SHMT_REQUIRE(out_unique && out_relabel, "shmt_relabel: outputs are null");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  uint64_t cap = 64;
+  while (cap < (uint64_t)numel * 2) cap <<= 1;
+  const int64_t n_tiles = (numel + kRelTile - 1) / kRelTile;
+  const size_t states = (tile_state_bytes(n_tiles) + 255) & ~(size_t)255;
+  const size_t need = states + cap * (8 + 4 + 4);
+  if (int rc = ctx_reserve(ctx, need)) return rc;
+  char* region = ctx->region();
+  TileStates st = carve_tile_states(region, n_tiles);
+  RelTable t;
+  t.keys = reinterpret_cast<long long*>(region + states);
+  t.first = reinterpret_cast<unsigned*>(region + states + cap * 8);
+  t.newid = t.first + cap;
+  t.mask = (uint32_t)(cap - 1);
+
+  // result words + tile flags to zero; table keys and first-index to all ones
+  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + (size_t)n_tiles * 4, s));
+  SHMT_CUDA_TRY(cudaMemsetAsync(t.keys, 0xFF, cap * 12, s));
+
+  int64_t blocks = (numel + kRelThreads - 1) / kRelThreads;
+  const int64_t cap_blocks = (int64_t)sm_count() * 16;
+  const unsigned grid = (unsigned)(blocks < cap_blocks ? blocks : cap_blocks);
+  relabel_insert_kernel<<<grid, kRelThreads, 0, s>>>(ps, numel, t, out_relabel, ctx->d_words());
+  relabel_compact_kernel<<<(unsigned)n_tiles, kRelThreads, 0, s>>>(
+      ps, numel, t, out_relabel, out_unique, st, n_tiles, ctx->d_words());
+  relabel_remap_kernel<<<grid, kRelThreads, 0, s>>>(numel, t.newid, out_relabel, ps.is64);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  if (n_unique_host) {
+    if (int rc = ctx_fetch_words(ctx, s, "shmt_relabel")) return rc;
+    *n_unique_host = ctx->h_words[W_RESULT];
+  }
+  return SHMT_OK;
+}

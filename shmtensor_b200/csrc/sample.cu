@@ -1,0 +1,389 @@
+// One fan-out hop of neighbour sampling over a (partly cached) CSR, as ONE kernel,
+// and the sub-CSR builder that fills the cache.
+//
+// Reference: GetSubIndptr / GetSubIndptrWithCache + CUB scan + host read of nnz +
+// CSRWise[Mask]SampleUniform[Replace]Kernel (src/cache_graph_sampling.cu:47-89,
+// 222-289, 91-177, 291-380, 179-220, 382-426); CreateCacheCSR (:428-492).
+//
+// Here a CTA takes a tile of S seeds:
+//   1. one seed per thread: cooperative map probe, row bounds from the cached
+//      indptr (hit) or the host indptr over UVA (miss), picks = min(deg, k);
+//   2. block scan of the picks, decoupled look-back for the tile's offset ->
+//      sub_indptr, so no separate scan kernel and no host round trip;
+//   3. groups of G = 8/16/32 lanes (smallest power of two >= k) sample one seed
+//      each: deg <= k copies the row; otherwise each lane p < k draws
+//      t_p ~ U[0, deg-k+p] with Philox4x32-10 and the group resolves Floyd's
+//      subset algorithm with k shuffle+ballot steps (O(k) work, exact uniform
+//      k-subset; the reference draws O(deg) numbers and uses global atomics).
+//      k > 32 falls back to the warp-parallel reservoir on the output row.
+#include "ctx.cuh"
+#include "lookback.cuh"
+#include "map.cuh"
+
+namespace shmt {
+
+constexpr int kHopThreads = 256;
+constexpr int kMaxSeedsPerTile = 1024;
+
+struct HopJob {
+  const void* indptr;
+  int indptr64;
+  const void* indices;      // host / full graph
+  const void* gpu_indptr;   // compact cached CSR (nullable)
+  const void* gpu_indices;
+  MapView map;
+  const void* seeds;
+  int seeds64;
+  int64_t n;
+  int64_t k;
+  int replace;
+  uint64_t rng_seed;
+  uint32_t off_lo, off_hi;
+  void* sub_indptr;
+  void* sub_indices;
+  TileStates st;
+  int64_t* words;
+  int seeds_per_tile;
+  int64_t n_tiles;
+};
+
+__device__ __forceinline__ uint64_t draw_below(const Philox& rng, uint32_t seed_idx, uint32_t draw,
+                                               uint32_t off_lo, uint32_t off_hi, uint64_t range) {
+  const uint4 r = rng(seed_idx, draw, off_lo, off_hi);
+  return bounded(r.x, r.y, range);
+}
+
+template <typename IxT, int G>
+__global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob job) {
+  __shared__ int64_t s_begin[kMaxSeedsPerTile];
+  __shared__ int64_t s_deg[kMaxSeedsPerTile];
+  __shared__ int64_t s_off[kMaxSeedsPerTile];
+  __shared__ uint8_t s_hit[kMaxSeedsPerTile];
+  __shared__ int64_t warp_sums[32];
+  __shared__ int64_t s_total;
+  __shared__ int64_t s_prefix;
+  __shared__ int s_tile;
+
+  const unsigned full = 0xffffffffu;
+  const unsigned tid = threadIdx.x, lane = tid & 31;
+  const int S = job.seeds_per_tile;
+  const int tile = take_tile(job.words + W_TICKET, &s_tile);
+  const int64_t first = (int64_t)tile * S;
+  const int rows = (int)min((int64_t)S, job.n - first);
+  const int64_t k = job.k;
+
+  // ---- 1. row bounds and pick counts, one seed per thread
+  for (int j0 = (int)(tid & ~31u); j0 < S; j0 += kHopThreads) {
+    const int j = j0 + (int)lane;
+    const bool valid = j < rows;
+    const int64_t row = valid ? load_int(job.seeds, job.seeds64, first + j) : kEmptyKey;
+    int64_t slot = -1;
+    if (job.map.slots) slot = warp_find(job.map, row, valid);
+    int64_t b = 0, e = 0;
+    if (valid) {
+      if (slot >= 0) {
+        b = load_int(job.gpu_indptr, job.indptr64, slot);
+        e = load_int(job.gpu_indptr, job.indptr64, slot + 1);
+      } else {
+        b = load_int(job.indptr, job.indptr64, row);
+        e = load_int(job.indptr, job.indptr64, row + 1);
+      }
+    }
+    const int64_t deg = e - b;
+    if (j < S) {
+      s_begin[j] = b;
+      s_deg[j] = deg;
+      s_hit[j] = slot >= 0;
+      s_off[j] = !valid ? 0 : (job.replace ? (deg > 0 ? k : 0) : (deg < k ? deg : k));
+    }
+  }
+  __syncthreads();
+
+  // ---- 2. offsets: scan inside the tile, look-back across tiles
+  {
+    const int ch = (S + kHopThreads - 1) / kHopThreads;  // seeds per thread, 1..4
+    int64_t c[kMaxSeedsPerTile / kHopThreads];
+    int64_t sum = 0;
+#pragma unroll
+    for (int q = 0; q < kMaxSeedsPerTile / kHopThreads; ++q) {
+      const int j = (int)tid * ch + q;
+      c[q] = (q < ch && j < S) ? s_off[j] : 0;
+      sum += c[q];
+    }
+    int64_t run = block_exclusive_scan(sum, warp_sums, &s_total);
+    if (tid < 32) {
+      const int64_t p = lookback_exclusive_prefix(job.st, tile, s_total, job.words + W_STATUS);
+      if (tid == 0) s_prefix = p;
+    }
+#pragma unroll
+    for (int q = 0; q < kMaxSeedsPerTile / kHopThreads; ++q) {
+      const int j = (int)tid * ch + q;
+      if (q < ch && j < S) s_off[j] = run;
+      run += c[q];
+    }
+    __syncthreads();
+  }
+  const int64_t prefix = s_prefix;
+  for (int j = (int)tid; j < rows; j += kHopThreads)
+    store_int(job.sub_indptr, job.indptr64, first + j, prefix + s_off[j]);
+  if (tile == job.n_tiles - 1 && tid == 0) {
+    store_int(job.sub_indptr, job.indptr64, job.n, prefix + s_total);
+    job.words[W_RESULT] = prefix + s_total;
+  }
+
+  // ---- 3. sampling, one seed per G-lane group
+  constexpr int kGroups = kHopThreads / G;
+  const unsigned gl = tid & (G - 1);
+  const unsigned gshift = lane & ~(unsigned)(G - 1);  // first lane of my group within the warp
+  const unsigned gmask = G == 32 ? full : (((1u << G) - 1u) << gshift);
+  const int group = (int)(tid / G);
+  const Philox rng(job.rng_seed);
+  IxT* out_all = static_cast<IxT*>(job.sub_indices);
+
+  for (int j0 = 0; j0 < rows; j0 += kGroups) {
+    const int j = j0 + group;
+    const bool active = j < rows;
+    const int64_t deg = active ? s_deg[j] : 0;
+    const IxT* in = nullptr;
+    IxT* out = nullptr;
+    if (active) {
+      in = static_cast<const IxT*>(s_hit[j] ? job.gpu_indices : job.indices) + s_begin[j];
+      out = out_all + prefix + s_off[j];
+    }
+    const uint32_t seed_idx = (uint32_t)(first + j);
+
+    if (job.replace) {
+      if (deg > 0)
+        for (int64_t p = gl; p < k; p += G)
+          out[p] = in[draw_below(rng, seed_idx, (uint32_t)p, job.off_lo, job.off_hi, (uint64_t)deg)];
+      continue;
+    }
+    if (active && deg <= k) {
+      for (int64_t p = gl; p < deg; p += G) out[p] = in[p];
+    }
+    const bool pick = active && deg > k;
+    if (k <= G) {
+      // Floyd: step p inserts t_p unless already chosen, then inserts deg-k+p instead
+      if (__any_sync(full, pick)) {
+        const int64_t top = deg - k + (int64_t)gl;  // largest position step gl may choose
+        int64_t t = -1;
+        if (pick && (int64_t)gl < k)
+          t = (int64_t)draw_below(rng, seed_idx, gl, job.off_lo, job.off_hi, (uint64_t)top + 1);
+        int64_t res = -1;
+        for (int p = 0; p < (int)k; ++p) {
+          const int64_t cand = __shfl_sync(full, t, p, G);
+          const bool clash = pick && (int)gl < p && res == cand;
+          const unsigned votes = __ballot_sync(full, clash) & gmask;
+          if ((int)gl == p) res = votes ? top : cand;
+        }
+        if (pick && (int64_t)gl < k) out[gl] = in[res];
+      }
+    } else {
+      // k > 32 (G == 32): reservoir on the output row, positions first, then values
+      if (pick) {
+        for (int64_t p = gl; p < k; p += 32) out[p] = (IxT)p;
+        __syncwarp();
+        for (int64_t q = k + gl; q < deg; q += 32) {
+          const uint64_t r = draw_below(rng, seed_idx, (uint32_t)q, job.off_lo, job.off_hi, (uint64_t)q + 1);
+          if (r < (uint64_t)k) atomicMax(out + r, (IxT)q);
+        }
+        __syncwarp();
+        __threadfence_block();
+        for (int64_t p = gl; p < k; p += 32) {
+          const IxT pos = *reinterpret_cast<volatile IxT*>(out + p);
+          out[p] = in[pos];
+        }
+      }
+    }
+  }
+}
+
+// ---- sub-CSR ------------------------------------------------------------------
+
+__global__ void subcsr_degree_kernel(const void* __restrict__ indptr, int indptr64,
+                                     const void* __restrict__ seeds, int seeds64, int64_t n,
+                                     void* __restrict__ out) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i <= n; i += stride) {
+    int64_t d = 0;
+    if (i < n) {
+      const int64_t row = load_int(seeds, seeds64, i);
+      d = load_int(indptr, indptr64, row + 1) - load_int(indptr, indptr64, row);
+    }
+    store_int(out, indptr64, i, d);
+  }
+}
+
+template <typename IxT>
+__global__ void __launch_bounds__(256)
+subcsr_fill_kernel(const void* __restrict__ indptr, int indptr64, const IxT* __restrict__ indices,
+                   const void* __restrict__ seeds, int seeds64, int64_t n,
+                   const void* __restrict__ gpu_indptr, IxT* __restrict__ out) {
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
+  const unsigned lane = threadIdx.x & 31;
+  for (int64_t i = warp; i < n; i += n_warps) {
+    const int64_t row = load_int(seeds, seeds64, i);
+    const int64_t b = load_int(indptr, indptr64, row);
+    const int64_t deg = load_int(indptr, indptr64, row + 1) - b;
+    const IxT* src = indices + b;
+    IxT* dst = out + load_int(gpu_indptr, indptr64, i);
+    int64_t p = lane;
+    for (; p + 96 < deg; p += 128) {  // four independent loads per lane in flight
+      const IxT a0 = src[p], a1 = src[p + 32], a2 = src[p + 64], a3 = src[p + 96];
+      dst[p] = a0;
+      dst[p + 32] = a1;
+      dst[p + 64] = a2;
+      dst[p + 96] = a3;
+    }
+    for (; p < deg; p += 32) dst[p] = src[p];
+  }
+}
+
+int launch_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
+                size_t scratch_off, cudaStream_t stream);
+size_t scan_scratch_bytes(int64_t n);
+
+static int pick_seeds_per_tile(int64_t n) {
+  int64_t s = (n + (int64_t)sm_count() * 4 - 1) / ((int64_t)sm_count() * 4);
+  s = (s + 31) / 32 * 32;
+  if (s < 32) s = 32;
+  if (s > kMaxSeedsPerTile) s = kMaxSeedsPerTile;
+  return (int)s;
+}
+
+template <typename IxT>
+static void launch_hop(const HopJob& job, cudaStream_t s) {
+  const unsigned grid = (unsigned)job.n_tiles;
+  if (job.k <= 8)
+    sample_hop_kernel<IxT, 8><<<grid, kHopThreads, 0, s>>>(job);
+  else if (job.k <= 16)
+    sample_hop_kernel<IxT, 16><<<grid, kHopThreads, 0, s>>>(job);
+  else
+    sample_hop_kernel<IxT, 32><<<grid, kHopThreads, 0, s>>>(job);
+}
+
+}  // namespace shmt
+
+using namespace shmt;
+
+extern "C" {
+
+int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                    int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
+                    const shmt_map* map, const void* seeds, int seeds_dtype, int64_t n, int64_t k,
+                    int replace, uint64_t rng_seed, uint64_t rng_offset, void* out_sub_indptr,
+                    void* out_sub_indices, int64_t* nnz_host, void* stream) {
+  SHMT_REQUIRE(ctx != nullptr, "shmt_sample_hop: ctx is null");
+  SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(indices_dtype) &&
+                   valid_int_dtype(seeds_dtype),
+               "shmt_sample_hop: ID can only be int32 or int64");
+  SHMT_REQUIRE(n >= 0 && n < ((int64_t)1 << 31), "shmt_sample_hop: seed count out of range");
+  SHMT_REQUIRE(k >= 0 && k < ((int64_t)1 << 31), "shmt_sample_hop: num_picks out of range");
+  SHMT_REQUIRE(out_sub_indptr != nullptr, "shmt_sample_hop: out_sub_indptr is null");
+  SHMT_REQUIRE(indptr != nullptr && (indices != nullptr || k == 0), "shmt_sample_hop: CSR is null");
+  SHMT_REQUIRE(n == 0 || seeds != nullptr, "shmt_sample_hop: seeds are null");
+  SHMT_REQUIRE(map == nullptr || (gpu_indptr != nullptr && gpu_indices != nullptr),
+               "shmt_sample_hop: a map needs gpu_indptr and gpu_indices");
+  SHMT_REQUIRE(n == 0 || k == 0 || out_sub_indices != nullptr,
+               "shmt_sample_hop: out_sub_indices is null");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n == 0) {
+    SHMT_CUDA_TRY(cudaMemsetAsync(out_sub_indptr, 0, int_itemsize(indptr_dtype), s));
+    if (nnz_host) {
+      SHMT_CUDA_TRY(cudaStreamSynchronize(s));
+      *nnz_host = 0;
+    }
+    return SHMT_OK;
+  }
+  HopJob job{};
+  job.indptr = indptr;
+  job.indptr64 = indptr_dtype == SHMT_I64;
+  job.indices = indices;
+  job.gpu_indptr = gpu_indptr;
+  job.gpu_indices = gpu_indices;
+  job.map = view_of(map);
+  job.seeds = seeds;
+  job.seeds64 = seeds_dtype == SHMT_I64;
+  job.n = n;
+  job.k = k;
+  job.replace = replace != 0;
+  job.rng_seed = rng_seed;
+  job.off_lo = (uint32_t)rng_offset;
+  job.off_hi = (uint32_t)(rng_offset >> 32);
+  job.sub_indptr = out_sub_indptr;
+  job.sub_indices = out_sub_indices;
+  job.seeds_per_tile = pick_seeds_per_tile(n);
+  job.n_tiles = (n + job.seeds_per_tile - 1) / job.seeds_per_tile;
+  if (int rc = ctx_reserve(ctx, tile_state_bytes(job.n_tiles))) return rc;
+  job.st = carve_tile_states(ctx->region(), job.n_tiles);
+  job.words = ctx->d_words();
+  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + (size_t)job.n_tiles * 4, s));
+  if (indices_dtype == SHMT_I64)
+    launch_hop<long long>(job, s);
+  else
+    launch_hop<int>(job, s);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  if (nnz_host) {
+    if (int rc = ctx_fetch_words(ctx, s, "shmt_sample_hop")) return rc;
+    *nnz_host = ctx->h_words[W_RESULT];
+  }
+  return SHMT_OK;
+}
+
+int shmt_subcsr_count(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* seeds,
+                      int seeds_dtype, int64_t n, void* out_gpu_indptr, int64_t* nnz_host,
+                      void* stream) {
+  SHMT_REQUIRE(ctx != nullptr, "shmt_subcsr_count: ctx is null");
+  SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(seeds_dtype),
+               "shmt_subcsr_count: ID can only be int32 or int64");
+  SHMT_REQUIRE(n >= 0, "shmt_subcsr_count: negative count");
+  SHMT_REQUIRE(indptr && out_gpu_indptr && (n == 0 || seeds), "shmt_subcsr_count: null argument");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (int rc = ctx_reserve(ctx, scan_scratch_bytes(n + 1))) return rc;
+  int64_t blocks = (n + 1 + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  subcsr_degree_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, s>>>(
+      indptr, indptr_dtype == SHMT_I64, seeds, seeds_dtype == SHMT_I64, n, out_gpu_indptr);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  if (int rc = launch_scan(ctx, out_gpu_indptr, indptr_dtype, n + 1, /*exclusive=*/1, 0, s))
+    return rc;
+  if (nnz_host) {
+    int64_t last = 0;
+    const int sz = int_itemsize(indptr_dtype);
+    SHMT_CUDA_TRY(cudaMemcpyAsync(&last, static_cast<char*>(out_gpu_indptr) + (size_t)n * sz, sz,
+                                  cudaMemcpyDeviceToHost, s));
+    if (int rc = ctx_fetch_words(ctx, s, "shmt_subcsr_count")) return rc;
+    *nnz_host = indptr_dtype == SHMT_I64 ? last : (int64_t)(int32_t)last;
+  }
+  return SHMT_OK;
+}
+
+int shmt_subcsr_fill(const void* indptr, int indptr_dtype, const void* indices, int indices_dtype,
+                     const void* seeds, int seeds_dtype, int64_t n, const void* gpu_indptr,
+                     void* out_gpu_indices, void* stream) {
+  SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(indices_dtype) &&
+                   valid_int_dtype(seeds_dtype),
+               "shmt_subcsr_fill: ID can only be int32 or int64");
+  SHMT_REQUIRE(n >= 0, "shmt_subcsr_fill: negative count");
+  if (n == 0) return SHMT_OK;
+  SHMT_REQUIRE(indptr && indices && seeds && gpu_indptr, "shmt_subcsr_fill: null argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int64_t blocks = (n + 7) / 8;
+  const int64_t cap = (int64_t)sm_count() * 32;
+  const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+  if (indices_dtype == SHMT_I64)
+    subcsr_fill_kernel<long long><<<grid, 256, 0, s>>>(
+        indptr, indptr_dtype == SHMT_I64, static_cast<const long long*>(indices), seeds,
+        seeds_dtype == SHMT_I64, n, gpu_indptr, static_cast<long long*>(out_gpu_indices));
+  else
+    subcsr_fill_kernel<int><<<grid, 256, 0, s>>>(
+        indptr, indptr_dtype == SHMT_I64, static_cast<const int*>(indices), seeds,
+        seeds_dtype == SHMT_I64, n, gpu_indptr, static_cast<int*>(out_gpu_indices));
+  SHMT_CUDA_TRY(cudaGetLastError());
+  return SHMT_OK;
+}
+
+}  // extern "C"

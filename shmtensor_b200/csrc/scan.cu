@@ -1,0 +1,93 @@
+// In-place prefix sum: one kernel, decoupled look-back between 2048-item tiles.
+// Semantics follow cub_exclusiveSum (reference src/cache_graph_sampling.cu:30-45)
+// and the intended meaning of thrust_scan (reference src/thrust_scan.cu:9-18,
+// whose own lambda races); integer arithmetic wraps.
+#include "ctx.cuh"
+#include "lookback.cuh"
+
+namespace shmt {
+
+constexpr int kScanThreads = 256;
+constexpr int kScanItems = 8;
+constexpr int kScanTile = kScanThreads * kScanItems;
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+scan_kernel(T* __restrict__ data, int64_t n, int exclusive, TileStates st, int64_t* words) {
+  __shared__ int64_t warp_sums[32];
+  __shared__ int64_t s_total;
+  __shared__ int64_t s_prefix;
+  __shared__ int s_tile;
+  const int tile = take_tile(words + W_TICKET, &s_tile);
+  const int64_t base = (int64_t)tile * kScanTile + (int64_t)threadIdx.x * kScanItems;
+
+  T v[kScanItems];
+  int64_t sum = 0;
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j) {
+    v[j] = base + j < n ? data[base + j] : T(0);
+    sum += (int64_t)v[j];
+  }
+  const int64_t local = block_exclusive_scan(sum, warp_sums, &s_total);
+  if (threadIdx.x < 32) {
+    const int64_t p = lookback_exclusive_prefix(st, tile, s_total, words + W_STATUS);
+    if (threadIdx.x == 0) s_prefix = p;
+  }
+  __syncthreads();
+  // unsigned accumulation: wrap-around is defined, and narrowing to T keeps the low bits
+  uint64_t run = (uint64_t)(s_prefix + local);
+#pragma unroll
+  for (int j = 0; j < kScanItems; ++j) {
+    if (base + j < n) {
+      if (exclusive) {
+        data[base + j] = (T)run;
+        run += (uint64_t)(int64_t)v[j];
+      } else {
+        run += (uint64_t)(int64_t)v[j];
+        data[base + j] = (T)run;
+      }
+    }
+  }
+}
+
+// Launch helper shared with relabel / sub-CSR: scans `n` items in place using
+// ctx scratch at byte offset `scratch_off` for the tile states.
+int launch_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
+                size_t scratch_off, cudaStream_t stream) {
+  if (n <= 0) return SHMT_OK;
+  const int64_t n_tiles = (n + kScanTile - 1) / kScanTile;
+  SHMT_REQUIRE(n_tiles < (int64_t)1 << 30, "scan: %lld items is too many", (long long)n);
+  TileStates st = carve_tile_states(ctx->region() + scratch_off, n_tiles);
+  // status / result / ticket words and the tile flags start at zero
+  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->d_words(), 0, 256, stream));
+  SHMT_CUDA_TRY(cudaMemsetAsync(st.flag, 0, (size_t)n_tiles * 4, stream));
+  if (dtype == SHMT_I64)
+    scan_kernel<long long><<<(unsigned)n_tiles, kScanThreads, 0, stream>>>(
+        static_cast<long long*>(data), n, exclusive, st, ctx->d_words());
+  else
+    scan_kernel<int><<<(unsigned)n_tiles, kScanThreads, 0, stream>>>(
+        static_cast<int*>(data), n, exclusive, st, ctx->d_words());
+  SHMT_CUDA_TRY(cudaGetLastError());
+  return SHMT_OK;
+}
+
+size_t scan_scratch_bytes(int64_t n) {
+  const int64_t n_tiles = (n + kScanTile - 1) / kScanTile;
+  return (tile_state_bytes(n_tiles > 0 ? n_tiles : 1) + 255) & ~(size_t)255;
+}
+
+}  // namespace shmt
+
+using namespace shmt;
+
+extern "C" int shmt_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
+                         void* stream) {
+  SHMT_REQUIRE(ctx != nullptr, "shmt_scan: ctx is null");
+  SHMT_REQUIRE(valid_int_dtype(dtype), "shmt_scan: dtype code %d is not SHMT_I32/SHMT_I64", dtype);
+  SHMT_REQUIRE(n >= 0, "shmt_scan: negative length");
+  if (n == 0) return SHMT_OK;
+  SHMT_REQUIRE(data != nullptr, "shmt_scan: data is null");
+  DeviceGuard guard(ctx->device);
+  if (int rc = ctx_reserve(ctx, scan_scratch_bytes(n))) return rc;
+  return launch_scan(ctx, data, dtype, n, exclusive, 0, static_cast<cudaStream_t>(stream));
+}
