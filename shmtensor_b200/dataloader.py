@@ -1,0 +1,176 @@
+"""``GPUSamplingDataloader`` — mini-batch neighbour sampling driven from Python.
+
+Keeps the constructor, iteration protocol and helper methods of the reference's
+python/shmtensor/sampling.py:30-237 (hops run over ``reversed(num_picks)``, the frontier of
+the next hop is the relabelled unique set, ``create_cache`` keeps the hottest rows' adjacency
+on the GPU behind a hashmap).  The DGL block the reference builds per hop is optional here:
+pass ``block_fn`` (or have ``dgl`` installed and pass ``block_fn="dgl"``); without it each hop
+yields the tuple ``(sub_indptr, relabel_indices, num_src, num_dst)``.
+"""
+from __future__ import annotations
+
+import weakref
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import capi
+
+
+def _dgl_block(sub_indptr, relabel_indices, num_src, num_dst):
+    """CSC block as python/shmtensor/sampling.py:9-20 builds it (needs dgl)."""
+    import dgl  # noqa: deferred so that the package works without dgl
+    from dgl.heterograph import DGLBlock
+    hgidx = dgl.heterograph_index.create_unitgraph_from_csr(
+        2, num_src, num_dst, sub_indptr, relabel_indices, torch.Tensor(),
+        formats=['coo', 'csr', 'csc'], transpose=True)
+    return DGLBlock(hgidx, (['_N'], ['_N']), ['_E'])
+
+
+def _plain_block(sub_indptr, relabel_indices, num_src, num_dst):
+    return sub_indptr, relabel_indices, num_src, num_dst
+
+
+class GPUSamplingDataloader:
+
+    def __init__(self, indptr, indices, seeds, batchsize, num_picks, replace=False,
+                 use_ddp=False, shuffle=True, drop_last=False,
+                 block_fn: Optional[Callable] = None):
+        self.indptr, self.indices = indptr, indices
+        self.batchsize, self.num_picks, self.replace = batchsize, num_picks, replace
+        self.use_ddp, self.shuffle, self.drop_last = use_ddp, shuffle, drop_last
+        self.block_fn = _dgl_block if block_fn == "dgl" else (block_fn or _plain_block)
+
+        self.has_cache = False
+        self.gpu_indptr = self.gpu_indices = self.hashmap = None
+
+        # host-resident CSR arrays are registered so kernels can read them in place
+        for t in (self.indptr, self.indices):
+            if not t.is_cuda:
+                capi.pin_memory(t)
+                weakref.finalize(self, capi.unpin_memory, t)
+
+        self.seeds = self._local_share(seeds)
+        if self.shuffle:
+            self._reshuffle()
+        self.seeds = self.seeds.cuda()
+        self._set_len()
+        self.curr = 0
+
+    # ------------------------------------------------------------------ seed bookkeeping
+    def _local_share(self, seeds):
+        """This rank's contiguous slice of the seeds (python/shmtensor/sampling.py:65-71)."""
+        if not self.use_ddp:
+            return seeds
+        world, rank = dist.get_world_size(), dist.get_rank()
+        part = (seeds.numel() + world - 1) // world
+        return seeds[rank * part:(rank + 1) * part]
+
+    def _reshuffle(self):
+        self.seeds = self.seeds[torch.randperm(self.seeds.numel(), device=self.seeds.device)]
+
+    def _set_len(self):
+        n = self.seeds.numel()
+        self.len = n // self.batchsize if self.drop_last else -(-n // self.batchsize)
+
+    def __len__(self):
+        return self.len
+
+    def __iter__(self):
+        if self.shuffle:
+            self._reshuffle()
+        self.curr = 0
+        return self
+
+    def update_params(self, **kwargs):
+        for k, v in kwargs.items():
+            setattr(self, k, v)
+        if "seeds" in kwargs or "use_ddp" in kwargs:
+            self.seeds = self._local_share(self.seeds).cuda()
+            self._set_len()
+
+    # ------------------------------------------------------------------ one hop / one batch
+    def _hop(self, seeds, num_pick):
+        if self.has_cache:
+            return capi.csr_cache_sampling(self.indptr, self.indices, self.gpu_indptr,
+                                           self.gpu_indices, self.hashmap, seeds, num_pick,
+                                           self.replace)
+        return capi.csr_sampling(self.indptr, self.indices, seeds, num_pick, self.replace)
+
+    def __next__(self):
+        if self.curr >= self.len:
+            raise StopIteration
+        lo = self.curr * self.batchsize
+        seeds = self.seeds[lo:lo + self.batchsize]
+        self.curr += 1
+
+        output_nodes, blocks = seeds, []
+        for num_pick in reversed(self.num_picks):
+            sub_indptr, sub_indices = self._hop(seeds, num_pick)
+            frontier, (_, relabel_indices) = capi.tensor_relabel([seeds, sub_indices])
+            blocks.insert(0, self.block_fn(sub_indptr, relabel_indices, frontier.numel(),
+                                           seeds.numel()))
+            seeds = frontier
+        return seeds, output_nodes, blocks
+
+    # ------------------------------------------------------------------ cache management
+    def create_cache(self, cache_capacity, hotness):
+        """Keep the hottest rows' adjacency on the GPU within ``cache_capacity`` bytes
+        (python/shmtensor/sampling.py:149-189; same size model: adjacency bytes + one indptr
+        entry + 1.25*2*4 bytes of map per row, map load factor 0.8, int32 keys/values)."""
+        if cache_capacity <= 0:
+            return
+        full_size = self.indptr.nbytes + self.indices.nbytes
+        if full_size <= cache_capacity:  # everything fits: plain GPU CSR, no map
+            self.has_cache = False
+            self.indices, self.indptr = self.indices.cuda(), self.indptr.cuda()
+            return
+
+        degrees = self.indptr[1:] - self.indptr[:-1]
+        candidates = torch.sort(hotness, descending=True).indices
+        cost = degrees[candidates.to(degrees.device)].cpu() * self.indices.element_size() \
+            + self.indptr.element_size() + 1.25 * 2 * 4
+        n_rows = int(torch.searchsorted(torch.cumsum(cost, dim=0), cache_capacity).item())
+        candidates = candidates[:n_rows].cuda()
+        if candidates.numel() == 0:
+            return
+        self.gpu_indptr, self.gpu_indices = capi.create_subcsr(self.indptr, self.indices,
+                                                               candidates)
+        slots = torch.arange(candidates.numel(), device='cuda', dtype=torch.int32)
+        self.hashmap = capi.CUCOStaticHashmap(candidates.int(), slots, 0.8)
+        self.has_cache = True
+
+    def clear_cache(self):
+        self.has_cache = False
+        self.gpu_indptr = self.gpu_indices = self.hashmap = None
+
+    def presampling(self):
+        """One uncached epoch that counts how often each node is a seed (sampling hotness)
+        and how often it appears in a frontier (feature hotness)
+        (python/shmtensor/sampling.py:199-227)."""
+        n_nodes = self.indptr.numel() - 1
+        sampling_hotness = torch.zeros(n_nodes, device='cuda')
+        feature_hotness = torch.zeros(n_nodes, device='cuda')
+        one = torch.ones((), device='cuda')
+        for b in range(self.len):
+            seeds = self.seeds[b * self.batchsize:(b + 1) * self.batchsize]
+            for num_pick in reversed(self.num_picks):
+                sampling_hotness.index_add_(0, seeds.long(), one.expand(seeds.numel()))
+                _, sub_indices = capi.csr_sampling(self.indptr, self.indices, seeds, num_pick,
+                                                   self.replace)
+                seeds, _ = capi.tensor_relabel([seeds, sub_indices])
+                feature_hotness.index_add_(0, seeds.long(), one.expand(seeds.numel()))
+        if self.use_ddp:
+            dist.all_reduce(sampling_hotness)
+            dist.all_reduce(feature_hotness)
+        return sampling_hotness.cpu(), feature_hotness.cpu()
+
+    def compute_weight_size(self, hotness):
+        """(bytes of the full CSR, mean hotness-weighted bytes per touched row)
+        (python/shmtensor/sampling.py:229-237)."""
+        full_size = self.indptr.nbytes + self.indices.nbytes
+        degree = (self.indptr[1:] - self.indptr[:-1]).clip(max=self.num_picks[0] * 1.3).float().cpu()
+        hot = hotness > 0
+        item = (degree[hot] * self.indices.element_size() + self.indptr.element_size()) * hotness[hot]
+        return full_size, item.mean().item()

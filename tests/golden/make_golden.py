@@ -1,0 +1,122 @@
+"""Write the golden fixtures under ``tests/golden/``.
+
+The reference cannot be imported or run where this repository is developed (its extension
+needs cuCollections, which its build downloads, and a GPU), so the known-answer vectors are
+transcribed from the asserts of the reference's own test scripts, cited per fixture, and the
+inputs the reference draws at random are replaced by seeded draws of the same shapes.
+
+    python tests/golden/make_golden.py
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+
+
+def relabel_fixture() -> dict:
+    # example/test_cache_sampling.py:129-140
+    return {
+        "source": "example/test_cache_sampling.py:129-140",
+        "inputs": [[2, 0, 4, 1, 4, 0, 4, 1, 6, 4], [3, 8, 5, 10, 10, 6, 11, 11, 9, 14]],
+        "unique": [2, 0, 4, 1, 6, 3, 8, 5, 10, 11, 9, 14],
+        "relabel": [[0, 1, 2, 3, 2, 1, 2, 3, 4, 2], [5, 6, 7, 8, 8, 4, 9, 9, 10, 11]],
+    }
+
+
+def sampling_fixture() -> dict:
+    # example/test_cache_sampling.py:23-64 (uncached) and :67-126 (cached, int64 map keys,
+    # int32 seeds).  "exact" lists output ranges whose content the reference asserts
+    # exactly; "ranged" lists [out_begin, out_end, lo, hi, must_be_distinct].
+    return {
+        "source": "example/test_cache_sampling.py:23-126",
+        "indptr": [0, 0, 4, 9, 15, 100, 101, 107],
+        "n_indices": 107,  # indices = arange(107)
+        "seeds": [5, 0, 1, 2, 3, 4, 6],
+        "num_picks": 5,
+        "replace_true": {
+            "sub_indptr": [0, 5, 5, 10, 15, 20, 25, 30],
+            "ranged": [[0, 5, 100, 101, False], [5, 10, 0, 4, False], [10, 15, 4, 9, False],
+                       [15, 20, 9, 15, False], [20, 25, 15, 100, False], [25, 30, 101, 107, False]],
+        },
+        "replace_false": {
+            "sub_indptr": [0, 1, 1, 5, 10, 15, 20, 25],
+            "exact": [[0, 1, [100]], [1, 5, [0, 1, 2, 3]], [5, 10, [4, 5, 6, 7, 8]],
+                      [10, 15, [9, 10, 11, 12, 13]]],
+            "ranged": [[15, 20, 15, 100, True], [20, 25, 101, 107, True]],
+        },
+        "cache": {
+            "cache_seeds": [5, 2, 1],  # example/test_cache_sampling.py:75
+            "gpu_indptr": [0, 1, 6, 10],
+            "gpu_indices": [100, 4, 5, 6, 7, 8, 0, 1, 2, 3],
+            "load_factor": 0.8,
+        },
+    }
+
+
+def fetch_set_fixture() -> dict:
+    # example/test_cache_fetch.py:24-105 and example/test_cache_set.py:24-147 assert only
+    # equality with data[query] / a set-then-fetch round trip on random inputs.  The shapes,
+    # dtypes and load factor are the reference's; the random draws are seeded here.
+    rng = np.random.default_rng(20240607)
+    cached = np.unique(rng.integers(0, 100, size=50))
+    return {
+        "source": "example/test_cache_fetch.py:24-105, example/test_cache_set.py:24-147",
+        "table_rows": 100,
+        "one_dim": "arange(100) float32",
+        "multi_dim_shape": [100, 100, 100],
+        "multi_dim_seed": 7,
+        "cached_ids": cached.tolist(),            # values = arange(len(cached_ids)), int64
+        "load_factor": 0.8,
+        "query": rng.integers(0, 100, size=20).tolist(),
+        "set_ids": np.unique(rng.integers(0, 100, size=10)).tolist(),
+    }
+
+
+def hashmap_fixture() -> dict:
+    # example/test_statichashmap.py:6-41 — four (key, value) dtype combinations, values = keys+1,
+    # load factor 0.5, queried with keys.long()+1.  The script only prints; the expected answers
+    # follow from the map's contract (stored value, or -1).
+    rng = np.random.default_rng(32)
+    keys = np.unique(rng.integers(0, 10000, size=100))
+    table = {int(k): int(k) + 1 for k in keys}
+    req = keys + 1
+    return {
+        "source": "example/test_statichashmap.py:6-47",
+        "keys": keys.tolist(),
+        "values": (keys + 1).tolist(),
+        "load_factor": 0.5,
+        "requests": req.tolist(),
+        "answers": [table.get(int(r), -1) for r in req],
+        "capacity": int(np.ceil(len(keys) / 0.5)),
+        "dtype_combos": [["int32", "int32"], ["int64", "int32"], ["int32", "int64"],
+                         ["int64", "int64"]],
+    }
+
+
+def npy_shm_fixture() -> dict:
+    return {
+        "source": "example/test_disk_tensor.py:6-14, example/test_shm_tensor.py:10-19",
+        "npy": {"dtype": "float64", "shape": [2, 3, 4], "seed": 11},
+        "shm": {"dtype": "int16", "shape": [2, 3, 4], "fill": 1000},
+    }
+
+
+def main() -> None:
+    fixtures = {
+        "relabel.json": relabel_fixture(),
+        "sampling.json": sampling_fixture(),
+        "fetch_set.json": fetch_set_fixture(),
+        "hashmap.json": hashmap_fixture(),
+        "npy_shm.json": npy_shm_fixture(),
+    }
+    for name, obj in fixtures.items():
+        (HERE / name).write_text(json.dumps(obj, indent=1) + "\n")
+        print("wrote", HERE / name)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,78 @@
+"""Multi-hop mini-batches through GPUSamplingDataloader (reference: python/shmtensor/sampling.py)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _graph(n_nodes=20_000, seed=0):
+    rng = np.random.default_rng(seed)
+    deg = np.minimum((rng.pareto(1.3, size=n_nodes) * 4).astype(np.int64), 2000)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, n_nodes, size=int(indptr[-1])).astype(np.int64)
+    return indptr, indices
+
+
+@pytest.mark.parametrize("cached", [False, True])
+def test_three_hop_batches_are_consistent(cached):
+    from shmtensor_b200 import GPUSamplingDataloader
+    indptr_n, indices_n = _graph()
+    indptr, indices = torch.from_numpy(indptr_n), torch.from_numpy(indices_n)
+    dl = GPUSamplingDataloader(indptr, indices, torch.arange(0, 4096), 1024, [15, 10, 5],
+                               shuffle=False)
+    if cached:
+        hotness = torch.from_numpy(np.diff(indptr_n).astype(np.float32))
+        dl.create_cache(int((indptr.nbytes + indices.nbytes) * 0.3), hotness)
+        assert dl.has_cache and dl.hashmap.key_dtype == torch.int32
+    assert len(dl) == 4
+    deg = np.diff(indptr_n)
+    n_batches = 0
+    for input_nodes, output_nodes, blocks in dl:
+        assert len(blocks) == 3 and output_nodes.numel() == 1024
+        assert torch.equal(output_nodes.cpu(), torch.arange(n_batches * 1024, (n_batches + 1) * 1024))
+        n_batches += 1
+        # hops are sampled over reversed(num_picks); blocks[-1] is the first one sampled
+        n_dst_expected = 1024
+        for (sub_indptr, rel, n_src, n_dst), k in zip(reversed(blocks), (5, 10, 15)):
+            assert n_dst == n_dst_expected and sub_indptr.numel() == n_dst + 1
+            assert rel.numel() == sub_indptr[-1].item() and n_src >= n_dst
+            assert rel.min().item() >= 0 and rel.max().item() < n_src
+            assert (np.diff(sub_indptr.cpu().numpy()) <= k).all()
+            n_dst_expected = n_src
+        assert input_nodes.numel() == n_dst_expected
+        # seeds are unique, so every frontier starts with the previous one, in order
+        assert torch.equal(input_nodes[:1024], output_nodes)
+        first_ptr = blocks[-1][0].cpu().numpy()
+        assert np.array_equal(np.diff(first_ptr), np.minimum(deg[output_nodes.cpu().numpy()], 5))
+        assert torch.unique(input_nodes).numel() == input_nodes.numel()
+    assert n_batches == 4
+
+
+def test_relabel_contract_inside_the_loader():
+    """One hop done by hand: frontier == oracle relabel of [seeds, sub_indices]."""
+    from shmtensor_b200 import capi
+    indptr_n, indices_n = _graph(seed=1)
+    indptr, indices = torch.from_numpy(indptr_n).cuda(), torch.from_numpy(indices_n).cuda()
+    seeds = torch.randperm(20_000, device="cuda")[:1024]
+    p, x = capi.csr_sampling(indptr, indices, seeds, 10, False)
+    uniq, (rs, rx) = capi.tensor_relabel([seeds, x])
+    wu, (ws, wx) = oracle.tensor_relabel([seeds.cpu().numpy(), x.cpu().numpy()])
+    assert np.array_equal(uniq.cpu().numpy(), wu)
+    assert np.array_equal(rs.cpu().numpy(), ws) and np.array_equal(rx.cpu().numpy(), wx)
+    assert torch.equal(rs, torch.arange(1024, device="cuda"))   # seeds are unique and come first
+    assert torch.equal(uniq[rx], x)
+
+
+def test_presampling_and_weight_size():
+    from shmtensor_b200 import GPUSamplingDataloader
+    indptr_n, indices_n = _graph(5000, seed=2)
+    dl = GPUSamplingDataloader(torch.from_numpy(indptr_n), torch.from_numpy(indices_n),
+                               torch.arange(2000), 500, [5, 5], shuffle=True, drop_last=True)
+    s_hot, f_hot = dl.presampling()
+    assert s_hot.shape == (5000,) and f_hot.shape == (5000,)
+    assert s_hot.sum() >= 2000 and (f_hot >= s_hot).all()
+    full, item = dl.compute_weight_size(f_hot)
+    assert full == indptr_n.nbytes + indices_n.nbytes and item > 0

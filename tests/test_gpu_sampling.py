@@ -1,0 +1,193 @@
+"""Fused sampling hop and sub-CSR builder against the oracle.
+
+Offsets and rows with deg <= k are bit-exact; sampled rows are checked for membership,
+distinct positions and (chi-square, p > 0.01) uniformity, as the reference's algorithm is only
+defined up to its random stream.
+"""
+import numpy as np
+import pytest
+import torch
+from scipy import stats
+
+from conftest import load_golden
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+DT = {torch.int32: np.int32, torch.int64: np.int64}
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from shmtensor_b200 import capi
+    capi.set_sampling_seed(1234)
+    return capi
+
+
+def _expect(exp, sub_indptr, sub_indices):
+    assert sub_indptr.cpu().tolist() == exp["sub_indptr"]
+    x = sub_indices.cpu().numpy()
+    assert x.size == exp["sub_indptr"][-1]
+    for b, e, vals in exp.get("exact", []):
+        assert x[b:e].tolist() == vals
+    for b, e, lo, hi, distinct in exp["ranged"]:
+        assert ((x[b:e] >= lo) & (x[b:e] < hi)).all()
+        if distinct:
+            assert np.unique(x[b:e]).size == e - b
+
+
+@pytest.mark.parametrize("ptr_dt,idx_dt", [(torch.int64, torch.int64), (torch.int32, torch.int32),
+                                           (torch.int64, torch.int32)])
+def test_golden_uncached(capi, ptr_dt, idx_dt):
+    g = load_golden("sampling.json")
+    indptr = torch.tensor(g["indptr"], dtype=ptr_dt, device="cuda")
+    indices = torch.arange(g["n_indices"], dtype=idx_dt, device="cuda")
+    seeds = torch.tensor(g["seeds"], dtype=torch.int32, device="cuda")
+    for replace, key in ((True, "replace_true"), (False, "replace_false")):
+        p, x = capi.csr_sampling(indptr, indices, seeds, g["num_picks"], replace)
+        assert p.dtype == ptr_dt and x.dtype == idx_dt and p.is_cuda and x.is_cuda
+        _expect(g[key], p, x)
+
+
+def test_golden_cached_with_pinned_host_csr(capi):
+    g = load_golden("sampling.json")
+    indptr = torch.tensor(g["indptr"], dtype=torch.int64)
+    indices = torch.arange(g["n_indices"], dtype=torch.int64)
+    capi.pin_memory(indptr)
+    capi.pin_memory(indices)
+    try:
+        c = g["cache"]
+        cache_seeds = torch.tensor(c["cache_seeds"], dtype=torch.int64, device="cuda")
+        gp, gi = capi.create_subcsr(indptr, indices, cache_seeds)
+        assert gp.cpu().tolist() == c["gpu_indptr"] and gi.cpu().tolist() == c["gpu_indices"]
+        m = capi.CUCOStaticHashmap(cache_seeds, torch.arange(3, device="cuda"), c["load_factor"])
+        seeds = torch.tensor(g["seeds"], dtype=torch.int32, device="cuda")  # int32 seeds, int64 keys
+        for replace, key in ((True, "replace_true"), (False, "replace_false")):
+            p, x = capi.csr_cache_sampling(indptr, indices, gp, gi, m, seeds, g["num_picks"], replace)
+            _expect(g[key], p, x)
+    finally:
+        capi.unpin_memory(indptr)
+        capi.unpin_memory(indices)
+
+
+def _random_graph(rng, n_nodes, max_deg, idx_dtype=np.int32):
+    deg = rng.integers(0, max_deg, size=n_nodes)
+    deg[rng.integers(0, n_nodes, size=n_nodes // 10)] = 0
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = np.concatenate([rng.permutation(max(n_nodes, max_deg))[:d] for d in deg] or [[]]).astype(idx_dtype)
+    return indptr, indices
+
+
+@pytest.mark.parametrize("k", [1, 5, 8, 10, 15, 16, 25, 32, 40, 100])
+@pytest.mark.parametrize("replace", [False, True])
+def test_random_graph_legal_samples(capi, k, replace):
+    rng = np.random.default_rng(k)
+    indptr_n, indices_n = _random_graph(rng, 3000, 200)
+    seeds_n = rng.integers(0, 3000, size=5000)
+    indptr, indices = torch.from_numpy(indptr_n).cuda(), torch.from_numpy(indices_n).cuda()
+    p, x = capi.csr_sampling(indptr, indices, torch.from_numpy(seeds_n).cuda(), k, replace)
+    oracle.check_sample(indptr_n, indices_n, seeds_n, k, replace, p.cpu().numpy(), x.cpu().numpy(),
+                        positional=True)
+
+
+@pytest.mark.parametrize("n_seeds", [0, 1, 31, 33, 1024, 70_000])
+def test_seed_counts_and_cached_rows(capi, n_seeds):
+    rng = np.random.default_rng(n_seeds + 7)
+    indptr_n, indices_n = _random_graph(rng, 20_000, 60)
+    hot_n = rng.choice(20_000, size=4000, replace=False)
+    indptr, indices = torch.from_numpy(indptr_n), torch.from_numpy(indices_n)
+    capi.pin_memory(indptr)
+    capi.pin_memory(indices)
+    try:
+        hot = torch.from_numpy(hot_n).cuda()
+        gp, gi = capi.create_subcsr(indptr, indices, hot)
+        wp, wi = oracle.create_subcsr(indptr_n, indices_n, hot_n)
+        assert np.array_equal(gp.cpu().numpy(), wp) and np.array_equal(gi.cpu().numpy(), wi)
+        m = capi.CUCOStaticHashmap(hot.int(), torch.arange(4000, dtype=torch.int32, device="cuda"), 0.8)
+        table = oracle.hashmap_build(hot_n, np.arange(4000))
+        seeds_n = rng.integers(0, 20_000, size=n_seeds)
+        seeds = torch.from_numpy(seeds_n).cuda()
+        for k, replace in ((10, False), (5, True)):
+            p, x = capi.csr_cache_sampling(indptr, indices, gp, gi, m, seeds, k, replace)
+            oracle.check_sample(indptr_n, indices_n, seeds_n, k, replace, p.cpu().numpy(),
+                                x.cpu().numpy(), table=table, gpu_indptr=wp, gpu_indices=wi,
+                                positional=True)
+            p2, x2 = capi.csr_sampling(indptr, indices, seeds, k, replace)   # UVA only
+            assert torch.equal(p, p2) and x2.numel() == x.numel()
+    finally:
+        capi.unpin_memory(indptr)
+        capi.unpin_memory(indices)
+
+
+@pytest.mark.parametrize("deg,k", [(20, 5), (40, 15), (17, 16), (100, 32), (300, 40), (1000, 10)])
+def test_without_replacement_is_uniform(capi, deg, k):
+    """Chi-square on how often each position of one row is picked (marginal k/deg), p > 0.01,
+    plus: every sample is k distinct positions."""
+    indptr = torch.tensor([0, deg], dtype=torch.int64, device="cuda")
+    indices = torch.arange(deg, dtype=torch.int32, device="cuda")     # value == position
+    reps = 40_000
+    seeds = torch.zeros(reps, dtype=torch.int64, device="cuda")
+    p, x = capi.csr_sampling(indptr, indices, seeds, k, False)
+    x = x.cpu().numpy().reshape(reps, k)
+    assert ((x >= 0) & (x < deg)).all()
+    assert (np.sort(x, axis=1)[:, 1:] != np.sort(x, axis=1)[:, :-1]).all(), "duplicate position"
+    counts = np.bincount(x.reshape(-1), minlength=deg)
+    chi2, pval = stats.chisquare(counts)
+    assert pval > 0.01, (chi2, pval)
+    # two calls draw different samples (the call counter advances) ...
+    _, y = capi.csr_sampling(indptr, indices, seeds, k, False)
+    assert not np.array_equal(np.sort(y.cpu().numpy().reshape(reps, k), 1), np.sort(x, 1))
+    # ... and a pinned seed reproduces them
+    capi.set_sampling_seed(99)
+    _, a = capi.csr_sampling(indptr, indices, seeds, k, False)
+    capi.set_sampling_seed(99)
+    _, b = capi.csr_sampling(indptr, indices, seeds, k, False)
+    assert torch.equal(a, b)
+
+
+def test_pairs_are_uniform_without_replacement(capi):
+    """Uniform k-subsets, not just uniform marginals: all C(6,2) pairs of a 6-row equally likely."""
+    indptr = torch.tensor([0, 6], dtype=torch.int64, device="cuda")
+    indices = torch.arange(6, dtype=torch.int64, device="cuda")
+    reps = 60_000
+    _, x = capi.csr_sampling(indptr, indices, torch.zeros(reps, dtype=torch.int32, device="cuda"), 2, False)
+    x = np.sort(x.cpu().numpy().reshape(reps, 2), axis=1)
+    counts = np.bincount(x[:, 0] * 6 + x[:, 1], minlength=36)
+    counts = counts[counts > 0]
+    assert counts.size == 15
+    assert stats.chisquare(counts)[1] > 0.01
+
+
+@pytest.mark.parametrize("deg,k", [(7, 5), (50, 20), (3, 40)])
+def test_with_replacement_is_uniform(capi, deg, k):
+    indptr = torch.tensor([0, deg], dtype=torch.int32, device="cuda")
+    indices = torch.arange(deg, dtype=torch.int32, device="cuda")
+    reps = 30_000
+    p, x = capi.csr_sampling(indptr, indices, torch.zeros(reps, dtype=torch.int64, device="cuda"), k, True)
+    assert p[-1].item() == reps * k
+    counts = np.bincount(x.cpu().numpy(), minlength=deg)
+    assert counts.size == deg and stats.chisquare(counts)[1] > 0.01
+
+
+def test_high_degree_rows_and_power_law_graph(capi):
+    """Degrees up to 10,000 (the cap of the headline workload), fan-outs 15/10/5."""
+    rng = np.random.default_rng(3)
+    deg = np.minimum((rng.pareto(1.1, size=5000) * 3).astype(np.int64), 10_000)
+    deg[:3] = [10_000, 9_999, 16]
+    indptr_n = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices_n = np.concatenate([rng.choice(2_400_000, size=d, replace=False) for d in deg]).astype(np.int32)
+    indptr, indices = torch.from_numpy(indptr_n).cuda(), torch.from_numpy(indices_n).cuda()
+    seeds_n = np.concatenate([[0, 1, 2], rng.integers(0, 5000, size=1021)])
+    for k in (15, 10, 5):
+        p, x = capi.csr_sampling(indptr, indices, torch.from_numpy(seeds_n).cuda(), k, False)
+        oracle.check_sample(indptr_n, indices_n, seeds_n, k, False, p.cpu().numpy(), x.cpu().numpy(),
+                            positional=True)
+
+
+def test_sampling_errors(capi):
+    indptr = torch.tensor([0, 2], device="cuda")
+    indices = torch.tensor([0, 1], device="cuda")
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        capi.csr_sampling(indptr, indices, torch.tensor([0]), 2, False)
+    with pytest.raises(RuntimeError, match="int32 or int64"):
+        capi.csr_sampling(indptr.float(), indices, torch.tensor([0], device="cuda"), 2, False)

@@ -1,0 +1,91 @@
+"""Decoupled look-back scan and first-occurrence relabel against the oracle (bit-exact)."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import load_golden
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def capi():
+    from shmtensor_b200 import capi
+    return capi
+
+
+@pytest.mark.parametrize("n", [1, 2, 255, 256, 2047, 2048, 2049, 100_003, 3_000_001])
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64])
+def test_scan_matches_cumsum(capi, n, dtype):
+    g = torch.Generator(device="cuda").manual_seed(n)
+    a = torch.randint(-1000, 1000, (n,), generator=g, device="cuda").to(dtype)
+    inc, exc = a.clone(), a.clone()
+    capi.thrust_scan(inc)
+    capi.exclusive_scan_(exc)
+    want = oracle.scan_inclusive(a.cpu().numpy())
+    assert np.array_equal(inc.cpu().numpy(), want)
+    assert np.array_equal(exc.cpu().numpy(), oracle.scan_exclusive(a.cpu().numpy()))
+
+
+def test_scan_int32_wraps_like_the_oracle(capi):
+    a = torch.full((5000,), 2**30, dtype=torch.int32, device="cuda")
+    want = oracle.scan_inclusive(a.cpu().numpy())
+    capi.thrust_scan(a)
+    assert np.array_equal(a.cpu().numpy(), want)
+    e = torch.empty(0, dtype=torch.int32, device="cuda")
+    capi.thrust_scan(e)  # empty input is a no-op
+    with pytest.raises(RuntimeError, match="int32 or int64"):
+        capi.thrust_scan(torch.zeros(4, device="cuda"))
+
+
+def test_relabel_golden_vector(capi):
+    g = load_golden("relabel.json")
+    for dt in (torch.int64, torch.int32):
+        ins = [torch.tensor(x, dtype=dt, device="cuda") for x in g["inputs"]]
+        uniq, rel = capi.tensor_relabel(ins)
+        assert uniq.dtype == dt and uniq.cpu().tolist() == g["unique"]
+        assert [r.cpu().tolist() for r in rel] == g["relabel"]
+        assert all(r.dtype == dt for r in rel)
+
+
+@pytest.mark.parametrize("sizes,hi", [((1,), 5), ((1000, 3000), 500), ((5, 0, 7), 4),
+                                      ((70_000, 1_200_000), 2_400_000), ((300_000,), 10),
+                                      ((2000,) * 9, 3000)])
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64])
+def test_relabel_random_matches_oracle(capi, sizes, hi, dtype):
+    rng = np.random.default_rng(sum(sizes) + hi)
+    ins_n = [rng.integers(0, hi, size=s).astype(np.int64) for s in sizes]
+    if dtype == torch.int64:
+        ins_n = [x + (1 << 35) for x in ins_n]  # ids beyond 32 bits
+    ins = [torch.from_numpy(x).to(dtype).cuda() for x in ins_n]
+    uniq, rel = capi.tensor_relabel(ins)
+    wu, wr = oracle.tensor_relabel([x.cpu().numpy() for x in ins])
+    assert np.array_equal(uniq.cpu().numpy(), wu)
+    assert len(rel) == len(sizes)
+    for a, b in zip(rel, wr):
+        assert np.array_equal(a.cpu().numpy(), b)
+
+
+def test_relabel_is_repeatable_and_idempotent(capi):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randint(0, 100_000, (500_000,), generator=g, device="cuda")
+    u1, (r1,) = capi.tensor_relabel([x])
+    u2, (r2,) = capi.tensor_relabel([x])
+    assert torch.equal(u1, u2) and torch.equal(r1, r2)
+    assert torch.equal(u1[r1], x)                       # relabel inverts through unique
+    u3, (r3,) = capi.tensor_relabel([u1])               # unique ids relabel to 0..n-1
+    assert torch.equal(u3, u1) and torch.equal(r3, torch.arange(u1.numel(), device="cuda"))
+
+
+def test_relabel_errors(capi):
+    with pytest.raises(RuntimeError):
+        capi.tensor_relabel([])
+    with pytest.raises(RuntimeError, match="share dtype"):
+        capi.tensor_relabel([torch.zeros(2, dtype=torch.int64, device="cuda"),
+                             torch.zeros(2, dtype=torch.int32, device="cuda")])
+    with pytest.raises(RuntimeError, match="int32 or int64"):
+        capi.tensor_relabel([torch.zeros(2, device="cuda")])
+    e = torch.empty(0, dtype=torch.int64, device="cuda")
+    u, (r,) = capi.tensor_relabel([e])
+    assert u.numel() == 0 and r.numel() == 0
