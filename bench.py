@@ -1,0 +1,432 @@
+#!/usr/bin/env python
+"""Benchmark of the cached feature fetch (the hot path's headline metric).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (one step = one batch through the fused probe+gather kernel): a pinned host table of
+2,400,000 x 100 float32 rows, N(0,1); the top 20 % of rows by a seeded power-law score are
+cached in HBM behind a static hashmap (int64 keys -> int32 slots, load factor 0.5); each
+batch is 500,000 int64 ids, rank-Zipf(1.1) over the score ranking mixed with uniform rows so
+that about 80 % hit the cache; misses are read from the host table through UVA.  With N > 1
+ranks (torchrun), the cached rows are hash-partitioned over the GPUs and remote hits are read
+over NVLink by the same kernel; every rank runs its own batches (weak scaling).
+
+Prints one JSON line (rank 0).  ``value`` times the kernel with ids already on the GPU;
+``e2e`` times the public call with the ids starting in pinned host memory and a read-back of
+the last fetched row.  ``--impl reference`` times the reference's CPU path for the same
+fetch (``data[q]`` = torch.index_select on the host table, example/test_cache_fetch.py:138)
+on the host cores.  Data is synthetic and seeded.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+ROWS, DIM, BATCH = 2_400_000, 100, 500_000
+CACHE_FRACTION, LOAD_FACTOR, ZIPF_ALPHA, UNIFORM_SHARE = 0.20, 0.5, 1.1, 0.21
+ROW_BYTES = DIM * 4
+N_BATCHES = 8
+METRIC, UNIT = "fetched feature GB/s", "GB/s"
+WORKLOAD = ("1-GPU cached feature fetch: pinned 2,400,000x100 f32 host table, top 20% rows cached "
+            "behind int64->int32 map (load 0.5), 500,000 int64 ids/batch Zipf(1.1), ~80% hits, misses via UVA")
+
+
+# --------------------------------------------------------------------------- synthetic data
+def make_scores(seed: int = 2024) -> np.ndarray:
+    """Seeded power-law 'degree' score per row (Pareto tail, like node degrees)."""
+    rng = np.random.default_rng(seed)
+    return rng.pareto(1.1, size=ROWS) + rng.random(ROWS) * 1e-6
+
+
+def make_batches(ranking: np.ndarray, n_batches: int, seed: int) -> list:
+    """Query batches: rank-Zipf(ZIPF_ALPHA) over the score ranking, mixed with uniform rows."""
+    rng = np.random.default_rng(seed)
+    w = 1.0 / np.arange(1, ROWS + 1, dtype=np.float64) ** ZIPF_ALPHA
+    cdf = np.cumsum(w)
+    cdf /= cdf[-1]
+    out = []
+    n_uniform = int(BATCH * UNIFORM_SHARE)
+    for _ in range(n_batches):
+        ranks = np.searchsorted(cdf, rng.random(BATCH - n_uniform))
+        ids = np.concatenate([ranking[np.minimum(ranks, ROWS - 1)], rng.integers(0, ROWS, size=n_uniform)])
+        rng.shuffle(ids)
+        out.append(torch.from_numpy(ids.astype(np.int64)))
+    return out
+
+
+def fill_table(t: torch.Tensor, seed: int = 7) -> None:
+    g = torch.Generator().manual_seed(seed)
+    chunk = 200_000
+    for lo in range(0, t.shape[0], chunk):
+        t[lo:lo + chunk].normal_(generator=g)
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.05):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+            self._thread = threading.Thread(target=self._run, args=(period_s,), daemon=True)
+        except Exception:
+            self._nv = None
+
+    def _run(self, period_s):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(period_s)
+
+    def start(self):
+        if self._thread:
+            self._thread.start()
+
+    def stop(self) -> dict:
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------- helpers
+def measured_peaks() -> tuple:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+def time_launches(fn, n: int, stream) -> float:
+    """Mean device time in ms of n calls of fn, one CUDA-event pair per call."""
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n)]
+    torch.cuda.synchronize()
+    for a, b in evs:
+        a.record(stream)
+        fn()
+        b.record(stream)
+    torch.cuda.synchronize()
+    return sum(a.elapsed_time(b) for a, b in evs) / n
+
+
+def hbm_bytes(n: int, n_hit: int) -> int:
+    """Algorithmic HBM bytes of one fetch launch: per query id 8 + probe 12 (int64 key + int32
+    slot) + the row written; hit rows are also read from HBM."""
+    return n * (8 + 12) + n_hit * ROW_BYTES + n * ROW_BYTES
+
+
+def measure_host_link(table: torch.Tensor, stream) -> dict:
+    """Host-link ceiling, measured here: pinned H2D copy and a streaming UVA read kernel."""
+    from shmtensor_b200._lib import check, lib
+    nbytes = min(table.numel() * 4, 1 << 30)
+    dst = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    src = table.view(torch.uint8).reshape(-1)[:nbytes]
+    best_copy = min(time_launches(lambda: dst.copy_(src, non_blocking=True), 1, stream) for _ in range(5))
+    sink = torch.zeros(1, dtype=torch.int64, device="cuda")
+    ptr = table.data_ptr()
+    best_read = min(time_launches(
+        lambda: check(lib.shmt_stream_read(ptr, nbytes, sink.data_ptr(), stream.cuda_stream)), 1, stream)
+        for _ in range(5))
+    copy_gbs, read_gbs = nbytes / best_copy / 1e6, nbytes / best_read / 1e6
+    return {"h2d_copy_gbs": round(copy_gbs, 2), "uva_read_kernel_gbs": round(read_gbs, 2),
+            "peak_gbs": round(max(copy_gbs, read_gbs), 2)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+# --------------------------------------------------------------------------- reference arm
+def run_reference(args) -> None:
+    """The reference's CPU path for this fetch, on the host cores: torch.index_select over the
+    host table (its ``cpu_fetch`` line).  Rank 0 only; no GPU work."""
+    rank, _, world = dist_env()
+    if rank != 0:
+        return
+    from oracle import oracle
+    table = torch.empty(ROWS, DIM)
+    fill_table(table)
+    scores = make_scores()
+    ranking = np.argsort(-scores, kind="stable")
+    batches = make_batches(ranking, N_BATCHES, seed=100)
+    for i in range(args.warmup):
+        oracle.cpu_fetch_reference(table, batches[i % N_BATCHES])
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        out = oracle.cpu_fetch_reference(table, batches[i % N_BATCHES])
+    dt = time.perf_counter() - t0
+    value = args.steps * BATCH * ROW_BYTES / dt / 1e9
+    cores = torch.get_num_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt / args.steps * 1e3, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 rows, int64 ids (byte copy)", "data": "synthetic (seeded)",
+        "config": {"workload": WORKLOAD, "rows": ROWS, "dim": DIM, "batch": BATCH},
+        "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{args.steps} full batches of 500,000 ids; torch.index_select on the host "
+                                   "table = the reference's cpu_fetch (example/test_cache_fetch.py:138), "
+                                   f"{cores} threads of {os.cpu_count()} logical cores"},
+        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    assert out.shape == (BATCH, DIM)
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------- our arm
+def run_ours(args) -> None:
+    rank, local_rank, world = dist_env()
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    import shmtensor_b200 as st
+    from shmtensor_b200 import capi
+    from shmtensor_b200.partition import PartitionedFeatureCache
+
+    stream = torch.cuda.current_stream()
+
+    # ---- data: host table shared by the ranks of the node, pinned; cache; batches
+    if world > 1:
+        name = f"shmt_bench_{os.environ.get('MASTER_PORT', '0')}"
+        if rank == 0 and capi.file_exist(name):  # stale segment of a killed run
+            p, fd = capi.open_shared_mem(name, ROWS * ROW_BYTES)
+            capi.release_shared_mem(name, ROWS * ROW_BYTES, p, fd)
+        dist.barrier()
+        shm = st.ShmTensor(name, (ROWS, DIM), rank, world, None, torch.float32, pin_memory=True)
+        table = shm.tensor_
+        if rank == 0:
+            fill_table(table)
+        dist.barrier()
+    else:
+        shm = None
+        table = torch.empty(ROWS, DIM)
+        fill_table(table)
+        capi.pin_memory(table)
+
+    scores = make_scores()
+    ranking = np.argsort(-scores, kind="stable")
+    n_cached = int(ROWS * CACHE_FRACTION)
+    cached_ids = torch.from_numpy(ranking[:n_cached].copy())
+    batches_host = [b.pin_memory() for b in make_batches(ranking, N_BATCHES, seed=100 + rank)]
+    batches = [b.to(dev) for b in batches_host]
+
+    if world == 1:
+        gpu_rows = capi.uva_fetch(table, cached_ids.to(dev))
+        hmap = capi.CUCOStaticHashmap(cached_ids.to(dev), torch.arange(n_cached, dtype=torch.int32, device=dev),
+                                      LOAD_FACTOR)
+        fetch = lambda ids: capi.cache_fetch(table, gpu_rows, ids, hmap)
+        query = hmap.query
+        pcache = None
+    else:
+        pcache = PartitionedFeatureCache(table, cached_ids, load_factor=LOAD_FACTOR)
+        fetch = pcache.fetch
+        query = pcache.directory.query
+    hit_counts = [int((query(b) >= 0).sum().item()) for b in batches]
+    hit_rate = sum(hit_counts) / (N_BATCHES * BATCH)
+
+    # ---- parity on one batch before timing anything (bit-exact vs the host table)
+    got = fetch(batches[0])
+    want = torch.index_select(table, 0, batches_host[0])
+    assert torch.equal(got.cpu().view(torch.int32), want.view(torch.int32)), "fetch is not bit-exact"
+    del got, want
+
+    # ---- warm-up, then the timed region: K launches, one CUDA-event pair each
+    for i in range(max(args.warmup, 3)):
+        fetch(batches[i % N_BATCHES])
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    sampler = ClockSampler(local_rank)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    region[0].record(stream)
+    for i, (a, b) in enumerate(evs):
+        a.record(stream)
+        out = fetch(batches[i % N_BATCHES])
+        b.record(stream)
+    region[1].record(stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop()
+    region_ms = region[0].elapsed_time(region[1])
+    kernel_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    if world > 1:
+        t = torch.tensor([region_ms, kernel_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        region_ms, kernel_ms = t.tolist()
+    ms_per_step = region_ms / args.steps
+    value = world * BATCH * ROW_BYTES / (ms_per_step * 1e6)
+
+    # ---- end to end through the public call: ids from pinned host memory each step, the last
+    #      fetched row read back to pinned host memory
+    ids_dev = torch.empty(BATCH, dtype=torch.int64, device=dev)
+    tail = torch.empty(DIM, dtype=torch.float32).pin_memory()
+    e2e_steps = args.steps
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    region[0].record(stream)
+    for i in range(e2e_steps):
+        ids_dev.copy_(batches_host[i % N_BATCHES], non_blocking=True)
+        out = fetch(ids_dev)
+        tail.copy_(out[-1], non_blocking=True)
+        stream.synchronize()
+    region[1].record(stream)
+    torch.cuda.synchronize()
+    e2e_ms = region[0].elapsed_time(region[1]) / e2e_steps
+    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = t.item()
+    e2e_value = world * BATCH * ROW_BYTES / (e2e_ms * 1e6)
+
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 rows, int64 ids (byte copy)",
+        "data": "synthetic (seeded)",
+        "config": {"workload": WORKLOAD, "rows": ROWS, "dim": DIM, "batch": BATCH, "cached_rows": n_cached,
+                   "hit_rate": round(hit_rate, 4),
+                   "l2": "inputs larger than L2: 192 MB cached rows + 200 MB output per launch, "
+                         f"{N_BATCHES} distinct query batches rotated",
+                   "partition": "single GPU" if world == 1 else f"hash-partitioned over {world} GPUs, NVLink P2P loads"},
+        "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": BATCH * 8,
+                "d2h_bytes_per_step": DIM * 4, "ms_per_step": round(e2e_ms, 5),
+                "wall_ms_per_step": round(e2e_wall_ms, 5)},
+        "gpu_launches": args.steps,
+        "clocks": clocks,
+    }
+
+    # ---- rank 0, one GPU: roofline of the fetch kernel and the CPU baseline beside it
+    if rank == 0 and world == 1:
+        peak, peak_src = measured_peaks()
+        link = measure_host_link(table, stream)
+        n_hit = sum(hit_counts[i % N_BATCHES] for i in range(args.steps)) / args.steps
+        alg = hbm_bytes(BATCH, int(n_hit))
+        link_bytes = (BATCH - n_hit) * ROW_BYTES
+        t_roof_ms = max(alg / (peak * 1e6), link_bytes / (link["peak_gbs"] * 1e6))
+        line["roofline"] = {
+            "bound": "hbm", "kernel": "row_copy_kernel<16,false,8> (fused probe+gather)",
+            "achieved": round(alg / (kernel_ms * 1e6), 1), "peak": peak, "unit": "GB/s",
+            "frac": round(alg / (kernel_ms * 1e6) / peak, 4), "peak_source": peak_src,
+            "traffic": None, "kernel_ms": round(kernel_ms, 5),
+            "note": "the 80%-hit batch is bound by the host link, not HBM: see roofline_link and "
+                    "frac_of_bound (time at the binding ceiling / measured time)",
+            "frac_of_bound": round(t_roof_ms / kernel_ms, 4),
+        }
+        line["roofline_link"] = {
+            "bound": "host_link", "achieved": round(link_bytes / (kernel_ms * 1e6), 2), "peak": link["peak_gbs"],
+            "unit": "GB/s", "frac": round(link_bytes / (kernel_ms * 1e6) / link["peak_gbs"], 4),
+            "peak_source": "measured in this run", **link}
+        # same kernel, all ids cached (HBM-bound regime) and no cache at all (link-bound regime)
+        hot_batches = [cached_ids[torch.randint(0, n_cached, (BATCH,), generator=torch.Generator().manual_seed(s))].to(dev)
+                       for s in range(4)]
+        ms_hit = time_launches(lambda c=[0]: (fetch(hot_batches[c[0] % 4]), c.__setitem__(0, c[0] + 1)), 40, stream)
+        alg_hit = hbm_bytes(BATCH, BATCH)
+        line["roofline_all_hit"] = {"bound": "hbm", "achieved": round(alg_hit / (ms_hit * 1e6), 1), "peak": peak,
+                                    "unit": "GB/s", "frac": round(alg_hit / (ms_hit * 1e6) / peak, 4),
+                                    "frac_of_nominal_8TBs": round(alg_hit / (ms_hit * 1e6) / 8000, 4),
+                                    "kernel_ms": round(ms_hit, 5), "peak_source": peak_src}
+        ms_miss = time_launches(lambda c=[0]: (capi.uva_fetch(table, batches[c[0] % N_BATCHES]), c.__setitem__(0, c[0] + 1)),
+                                10, stream)
+        line["roofline_all_miss"] = {"bound": "host_link", "achieved": round(BATCH * ROW_BYTES / (ms_miss * 1e6), 2),
+                                     "peak": link["peak_gbs"], "unit": "GB/s",
+                                     "frac": round(BATCH * ROW_BYTES / (ms_miss * 1e6) / link["peak_gbs"], 4),
+                                     "kernel_ms": round(ms_miss, 5)}
+        # CPU baseline: the reference's cpu_fetch line on this box's cores, bounded sample
+        from oracle import oracle
+        n_cpu = 20
+        for i in range(3):
+            oracle.cpu_fetch_reference(table, batches_host[i])
+        t0 = time.perf_counter()
+        for i in range(n_cpu):
+            oracle.cpu_fetch_reference(table, batches_host[i % N_BATCHES])
+        cpu_s = (time.perf_counter() - t0) / n_cpu
+        cores = torch.get_num_threads()
+        line["cpu_baseline"] = {
+            "value": round(BATCH * ROW_BYTES / cpu_s / 1e9, 3), "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{n_cpu} full batches of 500,000 ids after 3 warm-ups; torch.index_select on the pinned host "
+                      f"table (the reference's cpu_fetch, example/test_cache_fetch.py:138); {cores} threads of "
+                      f"{os.cpu_count()} logical cores"}
+
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+    # ---- orderly teardown: nothing in flight, peers unmapped before any shard is freed
+    torch.cuda.synchronize()
+    if pcache is not None:
+        pcache.close()
+    if world == 1:
+        capi.unpin_memory(table)
+    else:
+        dist.barrier()
+        del table, pcache
+        shm = None
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

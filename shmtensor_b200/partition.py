@@ -1,0 +1,141 @@
+"""Feature cache hash-partitioned over the GPUs of one node.
+
+The reference is single-GPU; this is the multi-GPU form of its cached fetch.  Each of the
+``world`` ranks (one process per GPU) keeps the rows of the cached ids it owns in one device
+buffer.  Every rank holds the whole directory — a static hashmap id -> (owner << 40 | slot)
+— so a probe never leaves local HBM; only row payloads cross NVLink, read by plain 16-byte
+loads inside the same fused gather kernel that serves local hits and host misses
+(``shmt_fetch_partitioned``).  Peer buffers are mapped with CUDA IPC, handles exchanged through
+``torch.distributed``.  There is no collective on the data path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import capi
+from ._lib import check, lib
+
+OWNER_SHIFT = 40
+
+
+def owner_of(ids: torch.Tensor, world: int) -> torch.Tensor:
+    """Owner rank of each id: a multiplicative hash, so that consecutive (or degree-sorted)
+    ids spread evenly.  Pure tensor arithmetic: identical on every rank, CPU or GPU."""
+    h = (ids.to(torch.int64) * 0x9E3779B1) & 0xFFFFFFFF
+    return (h >> 8) % world
+
+
+def plan_partition(cached_ids: torch.Tensor, world: int):
+    """(owner, slot) of every cached id: ``slot`` counts the ids of the same owner that
+    come earlier in ``cached_ids``; also the number of rows each rank holds."""
+    owner = owner_of(cached_ids, world)
+    slot = torch.empty_like(owner)
+    counts = []
+    for r in range(world):
+        mine = owner == r
+        n = int(mine.sum().item())
+        slot[mine] = torch.arange(n, dtype=torch.int64, device=owner.device)
+        counts.append(n)
+    return owner, slot, counts
+
+
+class _DeviceBuffer:
+    """A cudaMalloc'ed block owned by libshmt, exposed to torch without a copy."""
+
+    def __init__(self, nbytes: int, ptr: Optional[int] = None):
+        self.nbytes = nbytes
+        self.owned = ptr is None
+        if ptr is None:
+            out = C.c_void_p()
+            check(lib.shmt_dev_alloc(max(nbytes, 16), C.byref(out)))
+            ptr = out.value
+        self.ptr = ptr
+        self.__cuda_array_interface__ = {"shape": (max(nbytes, 1),), "typestr": "|u1",
+                                         "data": (ptr, False), "version": 2}
+
+    def tensor(self, dtype: torch.dtype, shape) -> torch.Tensor:
+        flat = torch.as_tensor(self, device="cuda")[: self.nbytes]
+        return flat.view(dtype).reshape(shape)
+
+
+class PartitionedFeatureCache:
+    """``fetch(ids)`` returns ``host_table[ids]`` on this rank's GPU, bit-exact, reading each
+    row from the local shard, a peer's shard over NVLink, or pinned host memory."""
+
+    def __init__(self, host_table: torch.Tensor, cached_ids: torch.Tensor, group=None,
+                 load_factor: float = 0.5):
+        self.group = group
+        distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if distributed else 1
+        self.rank = dist.get_rank(group) if distributed else 0
+        self.host_table = host_table
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        row_shape = tuple(host_table.shape[1:])
+        self.row_bytes = capi._row_bytes(host_table)
+
+        cached_ids = cached_ids.to(torch.int64).cpu()
+        owner, slot, counts = plan_partition(cached_ids, self.world)
+        mine = cached_ids[owner == self.rank]
+
+        # this rank's shard, filled straight from the host table by the UVA gather kernel
+        self._buf = _DeviceBuffer(counts[self.rank] * self.row_bytes)
+        self.shard = self._buf.tensor(host_table.dtype, (counts[self.rank], *row_shape))
+        if mine.numel():
+            self.shard.copy_(capi.uva_fetch(host_table, mine.to(self.device)))
+        torch.cuda.synchronize()
+
+        # peers' shards through CUDA IPC
+        self._peer_ptrs: List[int] = [0] * self.world
+        self._peer_ptrs[self.rank] = self._buf.ptr
+        self._opened: List[int] = []
+        if self.world > 1:
+            handle = (C.c_char * 64)()
+            check(lib.shmt_ipc_get_handle(self._buf.ptr, handle))
+            handles: List[bytes] = [b""] * self.world
+            dist.all_gather_object(handles, bytes(handle.raw), group=group)
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    continue
+                out = C.c_void_p()
+                check(lib.shmt_ipc_open_handle(h, C.byref(out)))
+                self._peer_ptrs[r] = out.value
+                self._opened.append(out.value)
+            dist.barrier(group)
+        self._bases = (C.c_void_p * self.world)(*self._peer_ptrs)
+
+        # replicated directory: id -> owner << 40 | slot
+        values = (owner << OWNER_SHIFT) | slot
+        self.directory = capi.CUCOStaticHashmap(cached_ids.to(self.device),
+                                                values.to(self.device), load_factor)
+        self.counts = counts
+
+    def fetch(self, ids: torch.Tensor) -> torch.Tensor:
+        capi._check_cuda(ids, "ids")
+        ids = ids.contiguous()
+        out = torch.empty((ids.numel(), *self.host_table.shape[1:]), dtype=self.host_table.dtype,
+                          device=ids.device)
+        check(lib.shmt_fetch_partitioned(self.directory._handle, self._bases, self.world,
+                                         OWNER_SHIFT, capi._ptr(self.host_table), capi._ptr(ids),
+                                         capi._int_code(ids, "fetch"), ids.numel(), self.row_bytes,
+                                         capi._ptr(out), capi._stream(ids.device)))
+        return out
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's shard.  Call on every rank, between
+        steps, with no fetch in flight; the ranks meet at a barrier before any memory goes."""
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(self.group)
+        for p in self._opened:
+            lib.shmt_ipc_close_handle(p)
+        self._opened = []
+        if self.world > 1:
+            dist.barrier(self.group)
+        if self._buf is not None and self._buf.owned:
+            self.shard = None
+            lib.shmt_dev_free(self._buf.ptr)
+            self._buf = None
