@@ -98,6 +98,11 @@ int shmt_fetch(const shmt_map* map, const void* mask, int mask_dtype,
                int idx_dtype, int64_t n, int64_t row_bytes, void* out,
                void* stream);
 
+/* Fetch kernels bound every device-side wait; one that gives up records a code
+ * here instead of hanging.  Synchronises the device, returns the code of the
+ * current device (0 = none) and clears it.  No counterpart in the reference.   */
+int shmt_device_fault(int* out_code);
+
 /* Partitioned cache: value = (owner << owner_shift) | slot; the row is read
  * from bases[owner] (this GPU's buffer or a peer's, by plain NVLink loads).
  * No counterpart in the reference (it is single-GPU).                         */

@@ -56,6 +56,7 @@ SIGNATURES = {
     "shmt_map_val_dtype": (_i, [_vp]),
     "shmt_map_destroy": (_i, [_vp]),
     "shmt_fetch": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i64, _i64, _vp, _vp]),
+    "shmt_device_fault": (_i, [C.POINTER(C.c_int)]),
     "shmt_fetch_partitioned": (_i, [_vp, _pvp, _i, _i, _vp, _vp, _i, _i64, _i64, _vp, _vp]),
     "shmt_set": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _i, _i64, _i64, _vp, _vp]),
     "shmt_insert_set": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i64, _i64, _vp, _vp]),

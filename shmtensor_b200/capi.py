@@ -254,11 +254,11 @@ class CUCOStaticHashmap:
     def value_dtype(self) -> torch.dtype:
         return _CODE_DTYPES[self._vd]
 
-    def __del__(self):
+    def __del__(self, _destroy=lib.shmt_map_destroy):
         h = getattr(self, "_handle", None)
         if h is not None:
-            lib.shmt_map_destroy(h)
             self._handle = None
+            _destroy(h)  # bound at definition: module globals may be gone at interpreter exit
 
 
 # --------------------------------------------------------------------------- fetch / set
@@ -282,6 +282,13 @@ def _fetch(uva_data, gpu_data, indices, hashmap, mask, who):
                          _ptr(uva_data), _ptr(gpu_data), _ptr(indices), idt, n,
                          _row_bytes(shape_src), _ptr(out), _stream(indices.device)))
     return out
+
+
+def device_fault() -> int:
+    """Extension: code left by a kernel whose bounded wait ran out (0 = none); synchronises."""
+    code = C.c_int(0)
+    check(lib.shmt_device_fault(C.byref(code)))
+    return code.value
 
 
 def uva_fetch(data: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:

@@ -15,6 +15,9 @@
 // (src/cache_feature_fetch.cu:15-45,89-129,188-224;
 //  src/cache_feature_set.cu:6-37,77-116,167-207), which walk 32 rows per warp one
 // after another with 4-byte accesses and probe the map redundantly on 32 lanes.
+#include <stdlib.h>
+
+#include "bulk.cuh"
 #include "ctx.cuh"
 #include "map.cuh"
 
@@ -66,6 +69,115 @@ __device__ __forceinline__ void store_chunk<16>(char* p, uint4 v) {
   st_stream16(p, v);
 }
 
+// Row address of request `first + lane` of a tile (nullptr: nothing to copy).
+// All 32 lanes must call: the map probe is cooperative.
+__device__ __forceinline__ char* resolve_row(const RowJob& job, int64_t first, int rows,
+                                             unsigned lane, int64_t slot_mask) {
+  const bool valid = (int)lane < rows;
+  const int64_t id = valid ? load_int(job.idx, job.idx64, first + lane) : kEmptyKey;
+  int64_t v = -1;
+  if (job.mode == MODE_MAP)
+    v = warp_find(job.map, id, valid);
+  else if (job.mode == MODE_MASK)
+    v = valid ? load_int(job.mask, job.mask64, first + lane) : -1;
+  char* p = nullptr;
+  if (valid) {
+    if (v >= 0) {
+      char* base = job.bases[v >> job.owner_shift];
+      if (base) p = base + (v & slot_mask) * job.row_bytes;
+    } else if (job.host) {
+      p = job.host + id * job.row_bytes;
+    }
+  }
+  return p;
+}
+
+// Set by a kernel whose bounded wait ran out; read (and cleared) by shmt_device_fault().
+__device__ int g_device_fault = 0;
+
+// Fetch through the TMA unit: rows never pass through registers.  Per warp, a ring
+// of STAGES shared-memory buffers of R rows each (about 2 KB): every lane of a tile
+// issues one bulk copy (row -> its slot of the buffer) that completes on the stage's
+// mbarrier; the whole buffer then leaves with ONE bulk store, because the tile's
+// rows are contiguous in the output.  While a stage's loads are in flight the warp
+// already probes the map for the tile after it and issues those loads.  Tiles are
+// dealt round-robin over a persistent grid, so neighbouring warps write
+// neighbouring pieces of the output at about the same time.
+template <int STAGES>
+__global__ void __launch_bounds__(kRowThreads)
+row_gather_bulk_kernel(const RowJob job) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t s_bar[kRowWarps][STAGES];
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int R = job.rows_per_tile;
+  const uint32_t rb = (uint32_t)job.row_bytes;
+  const uint32_t stage_bytes = (uint32_t)R * rb;
+  unsigned char* wbase = smem_raw + (size_t)warp * STAGES * stage_bytes;
+  const int64_t n_tiles = (job.n + R - 1) / R;
+  const int64_t stride = (int64_t)gridDim.x * kRowWarps;
+  const int64_t slot_mask = ((int64_t)1 << job.owner_shift) - 1;
+
+  if (lane == 0)
+    for (int s = 0; s < STAGES; ++s) mbar_init(&s_bar[warp][s], 1);
+  mbar_init_fence();
+  __syncwarp();
+
+  unsigned vmask[STAGES];  // lanes whose row is being loaded into the stage
+  int nrows[STAGES];
+  uint32_t parity = 0;     // bit s: phase of stage s to wait for next
+
+  auto issue = [&](int64_t tile, int s) {
+    const int64_t first = tile * R;
+    const int rows = (int)min((int64_t)R, job.n - first);
+    char* p = resolve_row(job, first, rows, lane, slot_mask);
+    const unsigned vm = __ballot_sync(0xffffffffu, p != nullptr);
+    if (lane == 0) mbar_arrive_expect_tx(&s_bar[warp][s], (uint32_t)__popc(vm) * rb);
+    if (p) bulk_load(wbase + (size_t)s * stage_bytes + (size_t)lane * rb, p, rb, &s_bar[warp][s]);
+    vmask[s] = vm;
+    nrows[s] = rows;
+  };
+
+  // D = STAGES - 1 tiles of loads are in flight while the oldest stage drains its store
+  constexpr int D = STAGES - 1;
+  int64_t tile = (int64_t)blockIdx.x * kRowWarps + warp;
+  bool ok = true;
+#pragma unroll
+  for (int j = 0; j < D; ++j)
+    if (tile + j * stride < n_tiles) issue(tile + j * stride, j);
+  while (tile < n_tiles && ok) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      if (tile >= n_tiles || !ok) break;
+      const int64_t ahead = tile + D * stride;
+      if (ahead < n_tiles) {
+        bulk_wait_read<0>();  // the store that last used that stage no longer reads it
+        __syncwarp();
+        issue(ahead, (s + D) % STAGES);
+      }
+      if (!mbar_wait_bounded(&s_bar[warp][s], (parity >> s) & 1u)) {
+        atomicExch(&g_device_fault, 1);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      parity ^= 1u << s;
+      if (ok) {
+        unsigned char* buf = wbase + (size_t)s * stage_bytes;
+        char* dst = job.flat + tile * R * job.row_bytes;
+        const unsigned vm = vmask[s];
+        async_proxy_fence();
+        if (__popc(vm) == nrows[s]) {
+          if (lane == 0 && vm) bulk_store(dst, buf, (uint32_t)nrows[s] * rb);
+        } else if ((vm >> lane) & 1u) {
+          bulk_store(dst + (size_t)lane * rb, buf + (size_t)lane * rb, rb);
+        }
+        bulk_commit();
+      }
+      tile += stride;
+    }
+  }
+  bulk_wait_read<0>();  // shared memory must outlive the stores that read it
+}
+
 // SET == false: table row -> flat (fetch).  SET == true: flat -> table row.
 template <int VEC, bool SET, int U>
 __global__ void __launch_bounds__(kRowThreads) row_copy_kernel(const RowJob job) {
@@ -85,21 +197,7 @@ __global__ void __launch_bounds__(kRowThreads) row_copy_kernel(const RowJob job)
 
     // ---- phase A: one request per lane -> row address
     {
-      const bool valid = (int)lane < rows;
-      const int64_t id = valid ? load_int(job.idx, job.idx64, first + lane) : kEmptyKey;
-      int64_t v = -1;
-      if (job.mode == MODE_MAP)
-        v = warp_find(job.map, id, valid);
-      else if (job.mode == MODE_MASK)
-        v = valid ? load_int(job.mask, job.mask64, first + lane) : -1;
-      char* p = nullptr;
-      if (valid) {
-        if (v >= 0) {
-          char* base = job.bases[v >> job.owner_shift];
-          if (base) p = base + (v & slot_mask) * job.row_bytes;
-        } else if (job.host)
-          p = job.host + id * job.row_bytes;
-      }
+      char* p = resolve_row(job, first, rows, lane, slot_mask);
       __syncwarp();  // previous tile's readers are done with s_row
       s_row[warp][lane] = p;
       __syncwarp();
@@ -219,26 +317,82 @@ static int pick_rows_per_tile(int64_t n) {
   return r;
 }
 
-static unsigned grid_for_tiles(int64_t n, int R) {
+// Persistent grid: never more CTAs than are resident at once (tiles are dealt round-robin
+// inside the kernels), so there is no partly filled last wave.
+template <typename Kernel>
+static unsigned grid_for_tiles(Kernel kernel, int64_t n, int R, size_t smem = 0) {
   const int64_t tiles = (n + R - 1) / R;
   int64_t blocks = (tiles + kRowWarps - 1) / kRowWarps;
-  const int64_t cap = (int64_t)sm_count() * 256;
-  if (blocks > cap) blocks = cap;
+  int occ = 1;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, kRowThreads, smem) != cudaSuccess ||
+      occ < 1)
+    occ = 1;
+  const int64_t resident = (int64_t)sm_count() * occ;
+  if (blocks > resident) blocks = resident;
   return (unsigned)(blocks < 1 ? 1 : blocks);
+}
+
+template <int VEC, bool SET>
+static int launch_lsu(const RowJob& job, cudaStream_t s) {
+  const unsigned grid = grid_for_tiles(row_copy_kernel<VEC, SET, 8>, job.n, job.rows_per_tile);
+  row_copy_kernel<VEC, SET, 8><<<grid, kRowThreads, 0, s>>>(job);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  return SHMT_OK;
+}
+
+// Ring geometry of the bulk path: two buffers per warp of about 2 KB each (5 rows of
+// 400 bytes, 4 of 512): measured best on B200 among 0.5 .. 12 KB buffers and 2 .. 4 stages.
+constexpr int kBulkStages = 2;
+constexpr int64_t kBulkStageBytes = 2048;
+constexpr size_t kBulkSmemMax = 200 * 1024;
+
+// Rows per ring buffer, 0 if the rows are not 16-byte units or do not fit.
+static int bulk_rows_per_stage(int64_t row_bytes, int vec, int R_small) {
+  if (vec != 16) return 0;
+  static const int forced = [] {
+    const char* e = getenv("SHMT_BULK_ROWS");
+    return e ? atoi(e) : 0;
+  }();
+  int64_t r = forced > 0 ? forced : kBulkStageBytes / row_bytes;
+  if (r < 1) r = 1;
+  if (r > 32) r = 32;
+  if (r > R_small) r = R_small;
+  if ((size_t)kRowWarps * kBulkStages * r * row_bytes > kBulkSmemMax) return 0;
+  return (int)r;
+}
+
+static int launch_gather_bulk(RowJob job, int R, cudaStream_t s) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  SHMT_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    SHMT_CUDA_TRY(cudaFuncSetAttribute(row_gather_bulk_kernel<kBulkStages>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)kBulkSmemMax));
+    configured[dev] = true;
+  }
+  job.rows_per_tile = R;
+  const size_t smem = (size_t)kRowWarps * kBulkStages * R * job.row_bytes;
+  const unsigned blocks = grid_for_tiles(row_gather_bulk_kernel<kBulkStages>, job.n, R, smem);
+  row_gather_bulk_kernel<kBulkStages><<<blocks, kRowThreads, smem, s>>>(job);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  return SHMT_OK;
 }
 
 template <bool SET>
 static int launch_row_copy(const RowJob& job, int vec, cudaStream_t s) {
-  const unsigned grid = grid_for_tiles(job.n, job.rows_per_tile);
-  switch (vec) {
-    case 16: row_copy_kernel<16, SET, 8><<<grid, kRowThreads, 0, s>>>(job); break;
-    case 8: row_copy_kernel<8, SET, 8><<<grid, kRowThreads, 0, s>>>(job); break;
-    case 4: row_copy_kernel<4, SET, 8><<<grid, kRowThreads, 0, s>>>(job); break;
-    case 2: row_copy_kernel<2, SET, 8><<<grid, kRowThreads, 0, s>>>(job); break;
-    default: row_copy_kernel<1, SET, 8><<<grid, kRowThreads, 0, s>>>(job); break;
+  if (!SET) {
+    static const bool no_bulk = getenv("SHMT_NO_BULK") != nullptr;
+    const int R = no_bulk ? 0 : bulk_rows_per_stage(job.row_bytes, vec, job.rows_per_tile);
+    if (R >= 1) return launch_gather_bulk(job, R, s);
   }
-  SHMT_CUDA_TRY(cudaGetLastError());
-  return SHMT_OK;
+  switch (vec) {
+    case 16: return launch_lsu<16, SET>(job, s);
+    case 8: return launch_lsu<8, SET>(job, s);
+    case 4: return launch_lsu<4, SET>(job, s);
+    case 2: return launch_lsu<2, SET>(job, s);
+    default: return launch_lsu<1, SET>(job, s);
+  }
 }
 
 static int check_common(const char* who, const void* idx, int idx_dtype, int64_t n,
@@ -273,6 +427,15 @@ static int fill_mode(const char* who, RowJob& job, const shmt_map* map, const vo
 using namespace shmt;
 
 extern "C" {
+
+int shmt_device_fault(int* out_code) {
+  SHMT_REQUIRE(out_code != nullptr, "shmt_device_fault: out_code is null");
+  int code = 0, zero = 0;
+  SHMT_CUDA_TRY(cudaMemcpyFromSymbol(&code, g_device_fault, sizeof(int)));
+  if (code) SHMT_CUDA_TRY(cudaMemcpyToSymbol(g_device_fault, &zero, sizeof(int)));
+  *out_code = code;
+  return SHMT_OK;
+}
 
 int shmt_fetch(const shmt_map* map, const void* mask, int mask_dtype, const void* host_base,
                const void* gpu_base, const void* idx, int idx_dtype, int64_t n, int64_t row_bytes,
@@ -364,7 +527,7 @@ int shmt_insert_set(shmt_map* map, void* gpu_base, const void* keys, int key_dty
   DeviceGuard guard(map->device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int R = pick_rows_per_tile(n);
-  const unsigned grid = grid_for_tiles(n, R);
+  const unsigned grid = grid_for_tiles(insert_set_kernel<16, 8>, n, R);
   const int vec = pick_vec(row_bytes, {gpu_base, update});
   char* g = static_cast<char*>(gpu_base);
   const char* u = static_cast<const char*>(update);
