@@ -8,7 +8,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libshmt.so"
+import os
+
+# SHMT_LIBRARY points at another build of the same library (a tuning variant); default: in-tree
+LIB_PATH = Path(os.environ.get("SHMT_LIBRARY") or Path(__file__).resolve().parent / "libshmt.so")
 
 OK, ERR_INVALID, ERR_CUDA, ERR_CAPACITY, ERR_TIMEOUT, ERR_OS = range(6)
 I32, I64 = 0, 1

@@ -41,10 +41,17 @@ def _newest_header() -> float:
     return max(h.stat().st_mtime for h in hdrs)
 
 
-def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None) -> Path:
-    """Compile every source for sm_100a and link ``libshmt.so``; returns its path."""
+def build(force: bool = False, verbose: bool = False, extra_flags: list[str] | None = None,
+          out: Path | None = None) -> Path:
+    """Compile every source for sm_100a and link ``libshmt.so``; returns its path.
+
+    ``out`` names another output library (with its own object directory), for building a
+    variant with ``extra_flags`` next to the installed one.
+    """
     nvcc = _nvcc()
-    BUILD_DIR.mkdir(exist_ok=True)
+    LIB_PATH = Path(out) if out else globals()["LIB_PATH"]
+    BUILD_DIR = LIB_PATH.parent / ("build_" + LIB_PATH.stem) if out else globals()["BUILD_DIR"]
+    BUILD_DIR.mkdir(exist_ok=True, parents=True)
     hdr_time = _newest_header()
     flags = NVCC_FLAGS + ["-I", str(INCLUDE), "-I", str(CSRC)] + (extra_flags or [])
     if verbose:

@@ -71,10 +71,14 @@ __device__ __forceinline__ void store_chunk<16>(char* p, uint4 v) {
 
 // Row address of request `first + lane` of a tile (nullptr: nothing to copy).
 // All 32 lanes must call: the map probe is cooperative.
+__device__ __forceinline__ int64_t load_id(const RowJob& job, int64_t first, int rows,
+                                            unsigned lane) {
+  return (int)lane < rows ? load_int(job.idx, job.idx64, first + lane) : kEmptyKey;
+}
+
 __device__ __forceinline__ char* resolve_row(const RowJob& job, int64_t first, int rows,
-                                             unsigned lane, int64_t slot_mask) {
+                                             unsigned lane, int64_t slot_mask, int64_t id) {
   const bool valid = (int)lane < rows;
-  const int64_t id = valid ? load_int(job.idx, job.idx64, first + lane) : kEmptyKey;
   int64_t v = -1;
   if (job.mode == MODE_MAP)
     v = warp_find(job.map, id, valid);
@@ -129,7 +133,8 @@ row_gather_bulk_kernel(const RowJob job) {
   auto issue = [&](int64_t tile, int s) {
     const int64_t first = tile * R;
     const int rows = (int)min((int64_t)R, job.n - first);
-    char* p = resolve_row(job, first, rows, lane, slot_mask);
+    const int64_t id = load_id(job, first, rows, lane);
+    char* p = resolve_row(job, first, rows, lane, slot_mask, id);
     const unsigned vm = __ballot_sync(0xffffffffu, p != nullptr);
     if (lane == 0) mbar_arrive_expect_tx(&s_bar[warp][s], (uint32_t)__popc(vm) * rb);
     if (p) bulk_load(wbase + (size_t)s * stage_bytes + (size_t)lane * rb, p, rb, &s_bar[warp][s]);
@@ -154,6 +159,8 @@ row_gather_bulk_kernel(const RowJob job) {
         __syncwarp();
         issue(ahead, (s + D) % STAGES);
       }
+      // every lane polls: measured faster than one polling lane plus a vote, and fetching
+      // the ids a tile ahead of their probe measured slower than loading them here
       if (!mbar_wait_bounded(&s_bar[warp][s], (parity >> s) & 1u)) {
         atomicExch(&g_device_fault, 1);
         ok = false;
@@ -197,7 +204,7 @@ __global__ void __launch_bounds__(kRowThreads) row_copy_kernel(const RowJob job)
 
     // ---- phase A: one request per lane -> row address
     {
-      char* p = resolve_row(job, first, rows, lane, slot_mask);
+      char* p = resolve_row(job, first, rows, lane, slot_mask, load_id(job, first, rows, lane));
       __syncwarp();  // previous tile's readers are done with s_row
       s_row[warp][lane] = p;
       __syncwarp();
