@@ -138,6 +138,24 @@ int shmt_insert_set(shmt_map* map, void* gpu_base, const void* keys,
 int shmt_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
               void* stream);
 
+/* The same scan for callers that must not allocate device memory at the point of
+ * the call: a plugin inside a host application that owns and pre-plans every byte of
+ * device memory, a serving loop with a hard latency bound (cudaMalloc and cudaFree
+ * stall the whole device, and a context's scratch may have to grow), or any code
+ * that runs where the CUDA allocator may not be entered.  The look-back state lives
+ * in a fixed array inside the library (about 160 KB per GPU, held from library load
+ * to process exit), so the call needs no context and never calls cudaMalloc or
+ * cudaFree: it is one memset of that state plus one kernel on `stream`.
+ * Limit: n <= 16,777,216 items; larger inputs are refused with SHMT_ERR_INVALID.
+ * Run it with the device that owns `data` current.  The first call on a device also
+ * looks up the array's device address (a runtime query, not an allocation); let
+ * that first call happen before any stream capture is started.  All calls on a
+ * device share the one array, which keeps what the last call left in it (each call
+ * clears the part it uses first): two calls that overlap on the GPU — different
+ * streams with no dependency between them — corrupt each other, calls ordered on
+ * one stream do not.  This entry point has no counterpart in the reference.        */
+int shmt_scan_static(void* data, int dtype, int64_t n, int exclusive, void* stream);
+
 /* ---- relabel ---------------------------------------------------------------
  * Concatenation of `n_parts` id arrays -> distinct ids in first-occurrence
  * order (out_unique, capacity = total) and, for every input element, the index

@@ -384,6 +384,22 @@ def exclusive_scan_(tensor: torch.Tensor) -> None:
                         tensor.numel(), 1, _stream(tensor.device)))
 
 
+def scan_static_(tensor: torch.Tensor, exclusive: bool = False) -> None:
+    """Extension: in-place prefix sum that allocates nothing (``shmt_scan_static``).
+
+    For callers that cannot allocate device memory where they need the scan: a component
+    living inside an application that owns all device memory, or a loop with a latency
+    bound that must never reach ``cudaMalloc``.  The scratch is a fixed array inside the
+    library: at most 16,777,216 elements, and two calls that overlap on the same GPU
+    corrupt each other.  Let the first call on a device happen before any stream capture.
+    """
+    _check_cuda(tensor, "tensor")
+    _check_contig(tensor, "tensor")
+    with torch.cuda.device(tensor.device):
+        check(lib.shmt_scan_static(_ptr(tensor), _int_code(tensor, "scan_static_"), tensor.numel(),
+                                   int(bool(exclusive)), _stream(tensor.device)))
+
+
 def tensor_relabel(tensors: List[torch.Tensor]):
     """src/tensor_relabel.cu:125-209 — ``(unique, [relabelled ...])``.
 

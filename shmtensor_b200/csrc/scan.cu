@@ -76,9 +76,63 @@ size_t scan_scratch_bytes(int64_t n) {
   return (tile_state_bytes(n_tiles > 0 ? n_tiles : 1) + 255) & ~(size_t)255;
 }
 
+// ---- scan without any allocation ----------------------------------------------------
+// Look-back state for shmt_scan_static lives in this fixed array instead of context
+// scratch.  Every GPU that loads the library carries it (about 160 KB) until exit.
+constexpr int64_t kStaticScanMaxItems = (int64_t)1 << 24;
+constexpr int64_t kStaticScanMaxTiles = kStaticScanMaxItems / kScanTile;
+constexpr size_t kStaticScanBytes = 256 + ((tile_state_bytes(kStaticScanMaxTiles) + 255) & ~(size_t)255);
+static __device__ __align__(256) unsigned char g_static_scan_scratch[kStaticScanBytes];
+
+// Device address of the array on the current device.  In host code the array's name is
+// only a handle for the runtime, never an address a kernel may be given, so it is resolved
+// once per device with cudaGetSymbolAddress and the result is what kernels receive.
+static int static_scan_scratch(unsigned char** out) {
+  static unsigned char* resolved[64] = {nullptr};
+  int dev = 0;
+  SHMT_CUDA_TRY(cudaGetDevice(&dev));
+  SHMT_REQUIRE(dev >= 0 && dev < 64, "shmt_scan_static: device index %d not supported", dev);
+  if (!resolved[dev]) {
+    unsigned char* p = nullptr;
+    SHMT_CUDA_TRY(cudaGetSymbolAddress((void**)&p, g_static_scan_scratch));
+    SHMT_REQUIRE(p != nullptr, "shmt_scan_static: the scratch array has no device address");
+    resolved[dev] = p;
+  }
+  *out = resolved[dev];
+  return SHMT_OK;
+}
+
 }  // namespace shmt
 
 using namespace shmt;
+
+extern "C" int shmt_scan_static(void* data, int dtype, int64_t n, int exclusive, void* stream) {
+  SHMT_REQUIRE(valid_int_dtype(dtype), "shmt_scan_static: dtype code %d is not SHMT_I32/SHMT_I64",
+               dtype);
+  SHMT_REQUIRE(n >= 0, "shmt_scan_static: negative length");
+  SHMT_REQUIRE(n <= kStaticScanMaxItems,
+               "shmt_scan_static: %lld items exceed the fixed scratch (limit %lld); use shmt_scan",
+               (long long)n, (long long)kStaticScanMaxItems);
+  if (n == 0) return SHMT_OK;
+  SHMT_REQUIRE(data != nullptr, "shmt_scan_static: data is null");
+  unsigned char* base = nullptr;
+  if (int rc = static_scan_scratch(&base)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t n_tiles = (n + kScanTile - 1) / kScanTile;
+  int64_t* words = reinterpret_cast<int64_t*>(base);
+  TileStates st = carve_tile_states(reinterpret_cast<char*>(base) + 256, n_tiles);
+  // the array still holds the previous call's ticket, status and tile flags: zero the
+  // words and the flags this call will use (flags sit right behind the 256-byte header)
+  SHMT_CUDA_TRY(cudaMemsetAsync(base, 0, 256 + (size_t)n_tiles * 4, s));
+  if (dtype == SHMT_I64)
+    scan_kernel<long long><<<(unsigned)n_tiles, kScanThreads, 0, s>>>(
+        static_cast<long long*>(data), n, exclusive, st, words);
+  else
+    scan_kernel<int><<<(unsigned)n_tiles, kScanThreads, 0, s>>>(static_cast<int*>(data), n,
+                                                                exclusive, st, words);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  return SHMT_OK;
+}
 
 extern "C" int shmt_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
                          void* stream) {
