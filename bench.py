@@ -423,14 +423,237 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- sampling workload
+G_NODES, G_EDGES, G_CAP, G_ALPHA = 2_400_000, 62_000_000, 10_000, 2.1
+FANOUT = [15, 10, 5]
+N_SEEDS = 1024
+SAMPLING_WORKLOAD = ("1-GPU cached neighbour sampling + relabel: power-law CSR 2,400,000 nodes / 62,000,000 edges "
+                     "(degree Zipf(2.1) capped at 10,000), int64 indptr, int32 indices, top 20% nodes by degree "
+                     "cached in HBM, rest pinned host; 1,024 seeds, 3 hops fan-out [15,10,5], unique+relabel per hop")
+
+
+def make_graph(seed: int = 3):
+    """Seeded power-law CSR: capped Zipf degrees rescaled to the edge total; the neighbours of a
+    row are an arithmetic progression modulo the node count (distinct within the row, spread
+    uniformly over the nodes)."""
+    rng = np.random.default_rng(seed)
+    raw = np.minimum(rng.zipf(G_ALPHA, size=G_NODES), G_CAP).astype(np.float64)
+    lo, hi = 0.1, 50.0
+    for _ in range(60):  # bisection on the scale factor
+        mid = 0.5 * (lo + hi)
+        if np.minimum(np.floor(raw * mid), G_CAP).sum() > G_EDGES:
+            hi = mid
+        else:
+            lo = mid
+    deg = np.minimum(np.floor(raw * lo), G_CAP).astype(np.int64)
+    short = G_EDGES - int(deg.sum())
+    bump = rng.permutation(np.flatnonzero(deg < G_CAP))[:short]
+    deg[bump] += 1
+    indptr = np.zeros(G_NODES + 1, dtype=np.int64)
+    np.cumsum(deg, out=indptr[1:])
+    steps = np.array([7, 11, 13, 17, 19, 23, 29, 31, 37, 41, 43, 47, 53, 59, 61, 67], dtype=np.int64)  # coprime to 2.4M
+    base = rng.integers(0, G_NODES, size=G_NODES)
+    step = steps[rng.integers(0, steps.size, size=G_NODES)]
+    row = np.repeat(np.arange(G_NODES, dtype=np.int64), deg)
+    j = np.arange(indptr[-1], dtype=np.int64) - indptr[row]
+    indices = ((base[row] + j * step[row]) % G_NODES).astype(np.int32)
+    return indptr, indices, deg
+
+
+def minibatch(capi, indptr, indices, gp, gi, hmap, seeds):
+    """The reference's per-batch loop (python/shmtensor/sampling.py:124-143): hops over
+    reversed(fan-out), relabel [seeds, neighbours], next frontier = unique."""
+    edges = 0
+    for k in reversed(FANOUT):
+        if hmap is None:
+            sub_indptr, sub_indices = capi.csr_sampling(indptr, indices, seeds, k, False)
+        else:
+            sub_indptr, sub_indices = capi.csr_cache_sampling(indptr, indices, gp, gi, hmap, seeds, k, False)
+        seeds, _ = capi.tensor_relabel([seeds, sub_indices])
+        edges += sub_indices.numel()
+    return edges, seeds
+
+
+def run_sampling(args) -> None:
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return
+    indptr_n, indices_n, deg = make_graph()
+    rng = np.random.default_rng(11)
+    seed_batches = [rng.integers(0, G_NODES, size=N_SEEDS).astype(np.int32) for _ in range(32)]
+    cores = torch.get_num_threads()
+    line = {"metric": "sampled edges/s", "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int64 indptr, int32 indices (integer / byte work)", "data": "synthetic (seeded)",
+            "config": {"workload": SAMPLING_WORKLOAD, "nodes": G_NODES, "edges": int(indptr_n[-1]),
+                       "fanout": FANOUT, "seeds": N_SEEDS, "hop_order": "reversed(fan-out), as the reference"}}
+
+    if args.impl == "reference":
+        # the reference has no CPU sampler (it compares against DGL): time the threaded CPU
+        # restatement of its CUDA algorithm
+        from oracle import build_oracle
+        lib = build_oracle.load_cpu()
+        def cpu_batch(seeds32):
+            seeds = seeds32.astype(np.int64)
+            edges = 0
+            for k in reversed(FANOUT):
+                sp = np.empty(seeds.size + 1, np.int64)
+                so = np.empty(seeds.size * k, np.int32)
+                nnz = lib.oracle_sample_hop(indptr_n.ctypes.data, indices_n.ctypes.data, 0, seeds.ctypes.data,
+                                            seeds.size, k, 0, 7777, sp.ctypes.data, so.ctypes.data)
+                cat = np.concatenate([seeds, so[:nnz].astype(np.int64)])
+                uniq, rel = np.empty(cat.size, np.int64), np.empty(cat.size, np.int64)
+                nu = lib.oracle_relabel(cat.ctypes.data, cat.size, uniq.ctypes.data, rel.ctypes.data)
+                seeds = uniq[:nu].copy()
+                edges += int(nnz)
+            return edges
+        for i in range(max(args.warmup, 1)):
+            cpu_batch(seed_batches[i % 32])
+        t0 = time.perf_counter()
+        edges = sum(cpu_batch(seed_batches[i % 32]) for i in range(args.steps))
+        dt = time.perf_counter() - t0
+        v = edges / dt
+        line.update({"impl": "reference", "value": round(v, 1), "ms_per_step": round(dt / args.steps * 1e3, 4),
+                     "cpu_baseline": {"value": round(v, 1), "unit": "edges/s", "cores": lib.oracle_num_threads(),
+                                      "kind": "port", "sample": f"{args.steps} full 3-hop mini-batches; threaded C++ "
+                                      "restatement of the reference's sampler (seeds split over threads) + serial relabel"},
+                     "e2e": {"value": round(v, 1), "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        print(json.dumps(line), flush=True)
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    from shmtensor_b200 import capi
+    indptr, indices = torch.from_numpy(indptr_n), torch.from_numpy(indices_n)
+    capi.pin_memory(indptr)
+    capi.pin_memory(indices)
+    n_cached = G_NODES // 5
+    hot = torch.from_numpy(np.argsort(-deg, kind="stable")[:n_cached].copy()).to(dev)
+    gp, gi = capi.create_subcsr(indptr, indices, hot)
+    hmap = capi.CUCOStaticHashmap(hot.int(), torch.arange(n_cached, dtype=torch.int32, device=dev), 0.8)
+    seeds_host = [torch.from_numpy(b).pin_memory() for b in seed_batches]
+    seeds_dev = [b.to(dev) for b in seeds_host]
+    stream = torch.cuda.current_stream()
+    capi.set_sampling_seed(7777)
+    for i in range(max(args.warmup, 3)):
+        minibatch(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
+    sampler = ClockSampler(local_rank)
+    region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    torch.cuda.synchronize()
+    sampler.start()
+    region[0].record(stream)
+    edges = 0
+    for i in range(args.steps):
+        e, frontier = minibatch(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
+        edges += e
+    region[1].record(stream)
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    ms = region[0].elapsed_time(region[1]) / args.steps
+    value = edges / args.steps / (ms * 1e-3)
+    # end to end: seeds start in pinned host memory, the frontier size is read back
+    seeds_buf = torch.empty(N_SEEDS, dtype=torch.int32, device=dev)
+    torch.cuda.synchronize()
+    region[0].record(stream)
+    e2e_edges = 0
+    for i in range(args.steps):
+        seeds_buf.copy_(seeds_host[i % 32], non_blocking=True)
+        e, frontier = minibatch(capi, indptr, indices, gp, gi, hmap, seeds_buf)
+        e2e_edges += e
+        _ = frontier[-1].item()
+    region[1].record(stream)
+    torch.cuda.synchronize()
+    e2e_ms = region[0].elapsed_time(region[1]) / args.steps
+    # uncached (every row over UVA) and fully GPU-resident graph, for the cache's effect
+    extra = {}
+    for name, (ip, ix, m) in {"uva_only": (indptr, indices, None),
+                              "all_in_hbm": (indptr.to(dev), indices.to(dev), None)}.items():
+        for i in range(3):
+            minibatch(capi, ip, ix, None, None, m, seeds_dev[i])
+        torch.cuda.synchronize()
+        region[0].record(stream)
+        ee = sum(minibatch(capi, ip, ix, None, None, m, seeds_dev[i % 32])[0] for i in range(50))
+        region[1].record(stream)
+        torch.cuda.synchronize()
+        extra[name] = round(ee / (region[0].elapsed_time(region[1]) * 1e-3), 1)
+    # same-box numbers of the reference's own CUDA kernels, when oracle/_ref was built
+    ref_line = None
+    try:
+        from oracle import build_ref
+        ref = build_ref.load_reference()
+    except Exception as exc:  # noqa: BLE001
+        ref, ref_line = None, {"unavailable": f"reference build not loadable: {exc}"}
+    if ref is not None:
+        indices64 = torch.from_numpy(indices_n.astype(np.int64))
+        ref.pin_memory(indices64)
+        rgp, rgi = ref.create_subcsr(indptr, indices64, hot)
+        rmap = ref.CUCOStaticHashmap(hot.int(), torch.arange(n_cached, dtype=torch.int32, device=dev), 0.8)
+        def ref_batch(seeds):
+            ed = 0
+            for k in reversed(FANOUT):
+                sp, so = ref.csr_cache_sampling(indptr, indices64, rgp, rgi, rmap, seeds, k, False)
+                seeds, _ = ref.tensor_relabel([seeds.long(), so])
+                ed += so.numel()
+            return ed
+        for i in range(3):
+            ref_batch(seeds_dev[i])
+        torch.cuda.synchronize()
+        region[0].record(stream)
+        ee = sum(ref_batch(seeds_dev[i % 32]) for i in range(50))
+        region[1].record(stream)
+        torch.cuda.synchronize()
+        ref_ms = region[0].elapsed_time(region[1]) / 50
+        ref_line = {"edges_per_s": round(ee / 50 / (ref_ms * 1e-3), 1), "ms_per_step": round(ref_ms, 4),
+                    "what": "the reference's own sampling + relabel kernels (compiled unmodified, int64 indices as it "
+                            "requires equal dtypes) over a stand-in for its cuCollections map"}
+        ref.unpin_memory(indices64)
+    # CPU baseline beside it (bounded sample)
+    from oracle import build_oracle
+    lib = build_oracle.load_cpu()
+    def cpu_batch(seeds32):
+        seeds = seeds32.astype(np.int64)
+        ed = 0
+        for k in reversed(FANOUT):
+            sp = np.empty(seeds.size + 1, np.int64)
+            so = np.empty(seeds.size * k, np.int32)
+            nnz = lib.oracle_sample_hop(indptr_n.ctypes.data, indices_n.ctypes.data, 0, seeds.ctypes.data,
+                                        seeds.size, k, 0, 7777, sp.ctypes.data, so.ctypes.data)
+            cat = np.concatenate([seeds, so[:nnz].astype(np.int64)])
+            uniq, rel = np.empty(cat.size, np.int64), np.empty(cat.size, np.int64)
+            nu = lib.oracle_relabel(cat.ctypes.data, cat.size, uniq.ctypes.data, rel.ctypes.data)
+            seeds = uniq[:nu].copy()
+            ed += int(nnz)
+        return ed
+    cpu_batch(seed_batches[0])
+    t0 = time.perf_counter()
+    ce = sum(cpu_batch(seed_batches[i]) for i in range(10))
+    cpu_dt = time.perf_counter() - t0
+    line.update({"value": round(value, 1), "ms_per_step": round(ms, 5), "edges_per_step": edges // args.steps,
+                 "e2e": {"value": round(e2e_edges / args.steps / (e2e_ms * 1e-3), 1), "unit": "edges/s",
+                         "h2d_bytes_per_step": N_SEEDS * 4, "d2h_bytes_per_step": 6 * 8 + 4, "ms_per_step": round(e2e_ms, 5)},
+                 "gpu_launches": args.steps * 3 * 4, "clocks": clocks, "variants_edges_per_s": extra,
+                 "reference_cuda": ref_line,
+                 "cpu_baseline": {"value": round(ce / cpu_dt, 1), "unit": "edges/s", "cores": lib.oracle_num_threads(),
+                                  "kind": "port", "sample": "10 full 3-hop mini-batches; threaded C++ restatement of the "
+                                  "reference's sampler + serial relabel (the reference has no CPU sampler)"}})
+    print(json.dumps(line), flush=True)
+    capi.unpin_memory(indptr)
+    capi.unpin_memory(indices)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="fetch", choices=["fetch", "sampling"],
+                    help="fetch: the headline cached feature fetch; sampling: cached 3-hop sampling + relabel")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "sampling":
+        run_sampling(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
