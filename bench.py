@@ -474,6 +474,12 @@ def minibatch(capi, indptr, indices, gp, gi, hmap, seeds):
     return edges, seeds
 
 
+def minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds):
+    """The same mini-batch through the fused native call (what GPUSamplingDataloader uses)."""
+    frontier, hops = capi.sample_minibatch(indptr, indices, seeds, list(reversed(FANOUT)), False, gp, gi, hmap)
+    return sum(h[1].numel() for h in hops), frontier
+
+
 def run_sampling(args) -> None:
     rank, local_rank, world = dist_env()
     if rank != 0:
@@ -537,7 +543,7 @@ def run_sampling(args) -> None:
     stream = torch.cuda.current_stream()
     capi.set_sampling_seed(7777)
     for i in range(max(args.warmup, 3)):
-        minibatch(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
+        minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
     sampler = ClockSampler(local_rank)
     region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
     torch.cuda.synchronize()
@@ -545,7 +551,7 @@ def run_sampling(args) -> None:
     region[0].record(stream)
     edges = 0
     for i in range(args.steps):
-        e, frontier = minibatch(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
+        e, frontier = minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
         edges += e
     region[1].record(stream)
     torch.cuda.synchronize()
@@ -559,7 +565,7 @@ def run_sampling(args) -> None:
     e2e_edges = 0
     for i in range(args.steps):
         seeds_buf.copy_(seeds_host[i % 32], non_blocking=True)
-        e, frontier = minibatch(capi, indptr, indices, gp, gi, hmap, seeds_buf)
+        e, frontier = minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_buf)
         e2e_edges += e
         _ = frontier[-1].item()
     region[1].record(stream)
@@ -567,13 +573,15 @@ def run_sampling(args) -> None:
     e2e_ms = region[0].elapsed_time(region[1]) / args.steps
     # uncached (every row over UVA) and fully GPU-resident graph, for the cache's effect
     extra = {}
-    for name, (ip, ix, m) in {"uva_only": (indptr, indices, None),
-                              "all_in_hbm": (indptr.to(dev), indices.to(dev), None)}.items():
+    variants = {"uva_only": (minibatch_fused, indptr, indices, None, None, None),
+                "all_in_hbm": (minibatch_fused, indptr.to(dev), indices.to(dev), None, None, None),
+                "call_per_hop_cached": (minibatch, indptr, indices, gp, gi, hmap)}
+    for name, (fn, ip, ix, a, b, m) in variants.items():
         for i in range(3):
-            minibatch(capi, ip, ix, None, None, m, seeds_dev[i])
+            fn(capi, ip, ix, a, b, m, seeds_dev[i])
         torch.cuda.synchronize()
         region[0].record(stream)
-        ee = sum(minibatch(capi, ip, ix, None, None, m, seeds_dev[i % 32])[0] for i in range(50))
+        ee = sum(fn(capi, ip, ix, a, b, m, seeds_dev[i % 32])[0] for i in range(50))
         region[1].record(stream)
         torch.cuda.synchronize()
         extra[name] = round(ee / (region[0].elapsed_time(region[1]) * 1e-3), 1)
@@ -632,7 +640,7 @@ def run_sampling(args) -> None:
     line.update({"value": round(value, 1), "ms_per_step": round(ms, 5), "edges_per_step": edges // args.steps,
                  "e2e": {"value": round(e2e_edges / args.steps / (e2e_ms * 1e-3), 1), "unit": "edges/s",
                          "h2d_bytes_per_step": N_SEEDS * 4, "d2h_bytes_per_step": 6 * 8 + 4, "ms_per_step": round(e2e_ms, 5)},
-                 "gpu_launches": args.steps * 3 * 4, "clocks": clocks, "variants_edges_per_s": extra,
+                 "gpu_launches": args.steps * 3 * 4, "api": "capi.sample_minibatch (all hops in one native call)", "clocks": clocks, "variants_edges_per_s": extra,
                  "reference_cuda": ref_line,
                  "cpu_baseline": {"value": round(ce / cpu_dt, 1), "unit": "edges/s", "cores": lib.oracle_num_threads(),
                                   "kind": "port", "sample": "10 full 3-hop mini-batches; threaded C++ restatement of the "

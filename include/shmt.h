@@ -190,6 +190,30 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
                     uint64_t rng_offset, void* out_sub_indptr,
                     void* out_sub_indices, int64_t* nnz_host, void* stream);
 
+/* A whole multi-hop mini-batch in one call: for hop h (fan-out fanouts[h]) sample the
+ * current frontier, relabel [frontier, sampled neighbours] and make the distinct ids the
+ * next frontier -- the loop of GPUSamplingDataloader.__next__
+ * (python/shmtensor/sampling.py:124-143) with csr_(cache_)sampling + tensor_relabel inside.
+ * Nothing returns to the host between hops: every kernel reads its input size from the
+ * device word the stage before it wrote, with grids sized for the largest frontier the
+ * fan-outs allow, and the host waits once at the end.  `seeds` and every id output have
+ * the indices dtype.  With c_0 = n_seeds and c_{h+1} = c_h * (1 + fanouts[h]) the caller
+ * provides per hop: out_sub_indptr[h] (c_h + 1 entries, indptr dtype), out_sub_indices[h]
+ * (c_h * fanouts[h]), out_relabel[h] (c_{h+1}: relabelled seeds, then relabelled
+ * neighbours, contiguous over the real sizes) and out_frontier[h] (c_{h+1}).
+ * sizes_host receives 3 numbers per hop: seeds in, edges sampled, distinct ids out.
+ * Draws equal those of n_hops successive shmt_sample_hop calls with rng_offset,
+ * rng_offset + 1, ...                                                              */
+int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
+                          const void* indices, int indices_dtype,
+                          const void* gpu_indptr, const void* gpu_indices,
+                          const shmt_map* map, const void* seeds, int64_t n_seeds,
+                          const int64_t* fanouts, int n_hops, int replace,
+                          uint64_t rng_seed, uint64_t rng_offset,
+                          void* const* out_sub_indptr, void* const* out_sub_indices,
+                          void* const* out_relabel, void* const* out_frontier,
+                          int64_t* sizes_host, void* stream);
+
 /* Compact CSR of the selected rows, in the given order: CreateCacheCSR
  * (src/cache_graph_sampling.cu:455-492).  _count writes the n+1 offsets and
  * (synchronising) the total; _fill copies the adjacency lists.               */

@@ -408,16 +408,18 @@ def tensor_relabel(tensors: List[torch.Tensor]):
     """
     if len(tensors) == 0:
         raise RuntimeError("tensor_relabel: expected a non-empty list of tensors")
-    dt, dev = tensors[0].dtype, tensors[0].device
+    dev = tensors[0].device
+    dt = tensors[0].dtype
     for t in tensors:
         _check_cuda(t, "tensors")
-        if t.dtype != dt or t.device != dev:
-            raise RuntimeError("tensor_relabel: all tensors must share dtype and device")
+        if t.device != dev:
+            raise RuntimeError("tensor_relabel: all tensors must share a device")
+        dt = torch.promote_types(dt, t.dtype)  # what the reference's torch::cat does
     code = _INT_CODES.get(dt)
     if code is None:
         raise RuntimeError(f"tensor_relabel: ID can only be int32 or int64, got {dt}")
     sizes = [t.numel() for t in tensors]
-    parts = [t.contiguous().reshape(-1) for t in tensors]
+    parts = [t.contiguous().reshape(-1).to(dt) for t in tensors]
     if len(parts) > 8:
         parts = [torch.cat(parts, 0)]
     total = sum(sizes)
@@ -471,6 +473,52 @@ def csr_cache_sampling(uva_indptr: torch.Tensor, uva_indices: torch.Tensor,
     """src/cache_graph_sampling.cu:382-426 — cached rows from the GPU CSR, the rest over UVA."""
     return _sample(uva_indptr, uva_indices, gpu_indptr, gpu_indices, hashmap, seeds, num_picks,
                    replace, "csr_cache_sampling")
+
+
+def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.Tensor,
+                     fanouts: Sequence[int], replace: bool = False, gpu_indptr=None,
+                     gpu_indices=None, hashmap: "CUCOStaticHashmap | None" = None):
+    """Extension: all hops of a mini-batch in one native call (``shmt_sample_minibatch``).
+
+    Equivalent to, for each ``k`` in ``fanouts`` in the given order::
+
+        sub_indptr, sub_indices = csr_(cache_)sampling(..., seeds, k, replace)
+        seeds, (_, relabel_indices) = tensor_relabel([seeds, sub_indices])
+
+    but nothing is read back between hops; the host waits once.  Returns
+    ``(frontier, hops)`` where ``hops[h] = (sub_indptr, sub_indices, relabel_indices,
+    frontier_after_hop)``.  Seeds are converted to the dtype of ``indices``.
+    """
+    _check_cuda(seeds, "seeds")
+    dev = seeds.device
+    for t, nm in ((indptr, "indptr"), (indices, "indices")):
+        _check_contig(t, nm)
+    pdt, xdt = _int_code(indptr, "sample_minibatch"), _int_code(indices, "sample_minibatch")
+    seeds = seeds.contiguous().to(indices.dtype)
+    n_hops = len(fanouts)
+    caps = [seeds.numel()]
+    for k in fanouts:
+        caps.append(caps[-1] * (1 + int(k)))
+    sub_indptr = [torch.empty(caps[h] + 1, dtype=indptr.dtype, device=dev) for h in range(n_hops)]
+    sub_indices = [torch.empty(caps[h] * int(fanouts[h]), dtype=indices.dtype, device=dev) for h in range(n_hops)]
+    relabel = [torch.empty(caps[h + 1], dtype=indices.dtype, device=dev) for h in range(n_hops)]
+    frontier = [torch.empty(caps[h + 1], dtype=indices.dtype, device=dev) for h in range(n_hops)]
+    arr = lambda ts: (C.c_void_p * n_hops)(*[t.data_ptr() for t in ts])
+    sizes = (C.c_int64 * (3 * n_hops))()
+    fan = (C.c_int64 * n_hops)(*[int(k) for k in fanouts])
+    offset = _rng["calls"] + 1
+    _rng["calls"] += n_hops
+    check(lib.shmt_sample_minibatch(_ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr),
+                                    _ptr(gpu_indices), hashmap._handle if hashmap is not None else None,
+                                    _ptr(seeds), seeds.numel(), fan, n_hops, int(bool(replace)),
+                                    _rng["seed"], offset, arr(sub_indptr), arr(sub_indices), arr(relabel),
+                                    arr(frontier), sizes, _stream(dev)))
+    hops = []
+    for h in range(n_hops):
+        n_in, nnz, n_out = sizes[3 * h], sizes[3 * h + 1], sizes[3 * h + 2]
+        hops.append((sub_indptr[h][: n_in + 1], sub_indices[h][:nnz], relabel[h][n_in:n_in + nnz],
+                     frontier[h][:n_out]))
+    return hops[-1][3], hops
 
 
 def create_subcsr(uva_indptr: torch.Tensor, uva_indices: torch.Tensor, seeds: torch.Tensor):

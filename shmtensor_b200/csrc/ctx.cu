@@ -45,11 +45,33 @@ int ctx_reserve(shmt_ctx* ctx, size_t bytes) {
   return SHMT_OK;
 }
 
+int ctx_reserve_table(shmt_ctx* ctx, size_t bytes, cudaStream_t stream) {
+  if (bytes > ctx->table_bytes) {
+    if (ctx->table) SHMT_CUDA_TRY(cudaFree(ctx->table));
+    ctx->table = nullptr;
+    ctx->table_bytes = 0;
+    size_t want = bytes + bytes / 2;
+    if (want < ((size_t)4 << 20)) want = (size_t)4 << 20;
+    want = (want + 255) & ~(size_t)255;
+    void* p = nullptr;
+    SHMT_CUDA_TRY(cudaMalloc(&p, want));
+    ctx->table = static_cast<char*>(p);
+    ctx->table_bytes = want;
+    ctx->table_dirty = true;
+  }
+  if (ctx->table_dirty) {
+    SHMT_CUDA_TRY(cudaMemsetAsync(ctx->table, 0xFF, ctx->table_bytes, stream));
+    ctx->table_dirty = false;
+  }
+  return SHMT_OK;
+}
+
 int ctx_fetch_words(shmt_ctx* ctx, cudaStream_t stream, const char* what) {
   SHMT_CUDA_TRY(cudaMemcpyAsync(ctx->h_words, ctx->d_words(), 4 * sizeof(int64_t),
                                 cudaMemcpyDeviceToHost, stream));
   SHMT_CUDA_TRY(cudaStreamSynchronize(stream));
   const int64_t st = ctx->h_words[W_STATUS];
+  if (st != DEV_OK) ctx->table_dirty = true;
   if (st == DEV_TIMEOUT) {
     set_error("%s: a bounded look-back wait ran out (device status %lld)", what, (long long)st);
     return SHMT_ERR_TIMEOUT;
@@ -102,11 +124,14 @@ int shmt_ctx_destroy(shmt_ctx* ctx) {
   if (!ctx) return SHMT_OK;
   DeviceGuard guard(ctx->device);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->table) cudaFree(ctx->table);
   if (ctx->h_words) cudaFreeHost(ctx->h_words);
   delete ctx;
   return SHMT_OK;
 }
 
-int64_t shmt_ctx_scratch_bytes(const shmt_ctx* ctx) { return ctx ? (int64_t)ctx->scratch_bytes : 0; }
+int64_t shmt_ctx_scratch_bytes(const shmt_ctx* ctx) {
+  return ctx ? (int64_t)(ctx->scratch_bytes + ctx->table_bytes) : 0;
+}
 
 }  // extern "C"

@@ -7,24 +7,24 @@
 // scan: (1) claim a table slot per distinct id and take the minimum input
 // index per slot, remembering each element's slot in the output array;
 // (2) flag first occurrences, scan the flags with a decoupled look-back inside
-// the same kernel, emit unique ids and the slot -> new id table; (3) remap.
-// Every element probes the table once (the reference probes four times).
-#include "ctx.cuh"
-#include "lookback.cuh"
+// the same kernel, emit unique ids and the slot -> new id table; (3) remap, and
+// put every slot that was used back to "empty", so the table needs no memset
+// between calls.  Every element probes the table once (the reference four times).
+// The element counts may live on the device (written by an earlier kernel), so a
+// chain of hops can be queued without the host knowing any size.
+#include "relabel.cuh"
 
 namespace shmt {
 
-constexpr int kRelThreads = 256;
-constexpr int kRelItems = 4;
-constexpr int kRelTile = kRelThreads * kRelItems;
-constexpr int kMaxParts = 8;
-
-struct Parts {
-  const void* ptr[kMaxParts];
-  int64_t start[kMaxParts + 1];  // element offset of each part in the concatenation
-  int n;
-  int is64;
-};
+__device__ __forceinline__ void resolve_sizes(Parts& ps, int64_t* numel) {
+  if (ps.dev_n1) {  // |part 0| from the device if given there, else the host's start[1]
+    const int64_t a = ps.dev_n0 ? *ps.dev_n0 : ps.start[1], b = *ps.dev_n1;
+    ps.start[0] = 0;
+#pragma unroll
+    for (int q = 1; q <= kMaxParts; ++q) ps.start[q] = q == 1 ? a : a + b;
+  }
+  *numel = ps.start[kMaxParts];
+}
 
 __device__ __forceinline__ int64_t part_elem(const Parts& ps, int64_t i) {
   int p = 0;
@@ -34,16 +34,10 @@ __device__ __forceinline__ int64_t part_elem(const Parts& ps, int64_t i) {
   return load_int(ps.ptr[p], ps.is64, i - ps.start[p]);
 }
 
-struct RelTable {
-  long long* keys;     // cap entries, -1 = empty
-  unsigned* first;     // cap entries, smallest input index holding the key
-  unsigned* newid;     // cap entries, dense id of the key (written by kernel 2)
-  uint32_t mask;       // cap - 1
-};
-
 __global__ void __launch_bounds__(kRelThreads)
-relabel_insert_kernel(Parts ps, int64_t numel, RelTable t, void* __restrict__ out,
-                      int64_t* words) {
+relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* status) {
+  int64_t numel;
+  resolve_sizes(ps, &numel);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
     const long long key = part_elem(ps, i);
@@ -57,8 +51,7 @@ relabel_insert_kernel(Parts ps, int64_t numel, RelTable t, void* __restrict__ ou
       if (cur == kEmptyKey || cur == key) break;
       pos = (pos + 1) & t.mask;
       if (++steps > t.mask) {  // cannot happen at load <= 0.5; bounded all the same
-        atomicMax(reinterpret_cast<unsigned long long*>(words + W_STATUS),
-                  (unsigned long long)DEV_OVERFLOW);
+        atomicMax(reinterpret_cast<unsigned long long*>(status), (unsigned long long)DEV_OVERFLOW);
         break;
       }
     }
@@ -68,13 +61,21 @@ relabel_insert_kernel(Parts ps, int64_t numel, RelTable t, void* __restrict__ ou
 }
 
 __global__ void __launch_bounds__(kRelThreads)
-relabel_compact_kernel(Parts ps, int64_t numel, RelTable t, const void* __restrict__ slot_of,
-                       void* __restrict__ unique, TileStates st, int64_t n_tiles, int64_t* words) {
+relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
+                       void* __restrict__ unique, TileStates st, int64_t* ticket, int64_t* status,
+                       int64_t* result) {
   __shared__ int64_t warp_sums[32];
   __shared__ int64_t s_total;
   __shared__ int64_t s_prefix;
   __shared__ int s_tile;
-  const int tile = take_tile(words + W_TICKET, &s_tile);
+  int64_t numel;
+  resolve_sizes(ps, &numel);
+  const int64_t n_tiles = (numel + kRelTile - 1) / kRelTile;
+  const int tile = take_tile(ticket, &s_tile);
+  if (tile >= n_tiles) {  // the grid is sized for the largest input the caller allows
+    if (numel == 0 && tile == 0 && threadIdx.x == 0) *result = 0;
+    return;
+  }
   const int64_t base = (int64_t)tile * kRelTile + (int64_t)threadIdx.x * kRelItems;
   uint32_t pos[kRelItems];
   bool is_first[kRelItems];
@@ -85,16 +86,16 @@ relabel_compact_kernel(Parts ps, int64_t numel, RelTable t, const void* __restri
     is_first[j] = false;
     if (i < numel) {
       pos[j] = (uint32_t)load_int(slot_of, ps.is64, i);
-      is_first[j] = __ldg(t.first + pos[j]) == (unsigned)i;
+      is_first[j] = __ldcg(t.first + pos[j]) == (unsigned)i;
     }
     cnt += is_first[j];
   }
   const int64_t local = block_exclusive_scan(cnt, warp_sums, &s_total);
   if (threadIdx.x < 32) {
-    const int64_t p = lookback_exclusive_prefix(st, tile, s_total, words + W_STATUS);
+    const int64_t p = lookback_exclusive_prefix(st, tile, s_total, status);
     if (threadIdx.x == 0) {
       s_prefix = p;
-      if (tile == n_tiles - 1) words[W_RESULT] = p + s_total;
+      if (tile == n_tiles - 1) *result = p + s_total;
     }
   }
   __syncthreads();
@@ -110,13 +111,50 @@ relabel_compact_kernel(Parts ps, int64_t numel, RelTable t, const void* __restri
 }
 
 __global__ void __launch_bounds__(kRelThreads)
-relabel_remap_kernel(int64_t numel, const unsigned* __restrict__ newid, void* out, int is64) {
+relabel_remap_kernel(Parts ps, RelTable t, void* out) {
+  int64_t numel;
+  resolve_sizes(ps, &numel);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
-    const int64_t pos = is64 ? reinterpret_cast<const long long*>(out)[i]
-                             : (int64_t) reinterpret_cast<const int*>(out)[i];
-    store_int(out, is64, i, (int64_t)__ldg(newid + pos));
+    const int64_t pos = ps.is64 ? reinterpret_cast<const long long*>(out)[i]
+                                : (int64_t) reinterpret_cast<const int*>(out)[i];
+    store_int(out, ps.is64, i, (int64_t)__ldcg(t.newid + pos));
+    // leave the slot empty for the next call (every duplicate writes the same values)
+    t.keys[pos] = kEmptyKey;
+    t.first[pos] = 0xFFFFFFFFu;
   }
+}
+
+// Table for up to `numel_bound` ids at load <= 0.5.  Keys and first-index words live in the
+// context's all-ones block (whatever the capacity, the block is all ones between calls, so
+// regions of different capacities may overlap freely); the slot -> new-id words need no
+// initial value and come from ordinary scratch (`newid`, 4 * relabel_capacity bytes).
+uint64_t relabel_capacity(int64_t numel_bound) {
+  uint64_t cap = 64;
+  while (cap < (uint64_t)numel_bound * 2) cap <<= 1;
+  return cap;
+}
+
+int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
+                   void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
+                   int64_t* status, int64_t* result, cudaStream_t s) {
+  const uint64_t cap = relabel_capacity(numel_bound);
+  if (int rc = ctx_reserve_table(ctx, cap * 12, s)) return rc;
+  RelTable t;
+  t.keys = reinterpret_cast<long long*>(ctx->table);
+  t.first = reinterpret_cast<unsigned*>(ctx->table + cap * 8);
+  t.newid = newid;
+  t.mask = (uint32_t)(cap - 1);
+  const int64_t n_tiles = (numel_bound + kRelTile - 1) / kRelTile;
+  int64_t blocks = (numel_bound + kRelThreads - 1) / kRelThreads;
+  const int64_t cap_blocks = (int64_t)sm_count() * 16;
+  const unsigned grid = (unsigned)(blocks < cap_blocks ? blocks : cap_blocks);
+  relabel_insert_kernel<<<grid, kRelThreads, 0, s>>>(ps, t, out_relabel, status);
+  relabel_compact_kernel<<<(unsigned)n_tiles, kRelThreads, 0, s>>>(ps, t, out_relabel, out_unique,
+                                                                   st, ticket, status, result);
+  relabel_remap_kernel<<<grid, kRelThreads, 0, s>>>(ps, t, out_relabel);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  return SHMT_OK;
 }
 
 }  // namespace shmt
@@ -151,33 +189,17 @@ extern "C" int shmt_relabel(shmt_ctx* ctx, const void* const* parts, const int64
   SHMT_REQUIRE(out_unique && out_relabel, "shmt_relabel: outputs are null");
   DeviceGuard guard(ctx->device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-
-  uint64_t cap = 64;
-  while (cap < (uint64_t)numel * 2) cap <<= 1;
   const int64_t n_tiles = (numel + kRelTile - 1) / kRelTile;
   const size_t states = (tile_state_bytes(n_tiles) + 255) & ~(size_t)255;
-  const size_t need = states + cap * (8 + 4 + 4);
-  if (int rc = ctx_reserve(ctx, need)) return rc;
-  char* region = ctx->region();
-  TileStates st = carve_tile_states(region, n_tiles);
-  RelTable t;
-  t.keys = reinterpret_cast<long long*>(region + states);
-  t.first = reinterpret_cast<unsigned*>(region + states + cap * 8);
-  t.newid = t.first + cap;
-  t.mask = (uint32_t)(cap - 1);
-
-  // result words + tile flags to zero; table keys and first-index to all ones
+  if (int rc = ctx_reserve(ctx, states + relabel_capacity(numel) * 4)) return rc;
+  TileStates st = carve_tile_states(ctx->region(), n_tiles);
+  unsigned* newid = reinterpret_cast<unsigned*>(ctx->region() + states);
+  // result words + tile flags to zero
   SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + (size_t)n_tiles * 4, s));
-  SHMT_CUDA_TRY(cudaMemsetAsync(t.keys, 0xFF, cap * 12, s));
-
-  int64_t blocks = (numel + kRelThreads - 1) / kRelThreads;
-  const int64_t cap_blocks = (int64_t)sm_count() * 16;
-  const unsigned grid = (unsigned)(blocks < cap_blocks ? blocks : cap_blocks);
-  relabel_insert_kernel<<<grid, kRelThreads, 0, s>>>(ps, numel, t, out_relabel, ctx->d_words());
-  relabel_compact_kernel<<<(unsigned)n_tiles, kRelThreads, 0, s>>>(
-      ps, numel, t, out_relabel, out_unique, st, n_tiles, ctx->d_words());
-  relabel_remap_kernel<<<grid, kRelThreads, 0, s>>>(numel, t.newid, out_relabel, ps.is64);
-  SHMT_CUDA_TRY(cudaGetLastError());
+  int64_t* w = ctx->d_words();
+  if (int rc = launch_relabel(ctx, ps, numel, newid, out_unique, out_relabel, st, w + W_TICKET,
+                              w + W_STATUS, w + W_RESULT, s))
+    return rc;
   if (n_unique_host) {
     if (int rc = ctx_fetch_words(ctx, s, "shmt_relabel")) return rc;
     *n_unique_host = ctx->h_words[W_RESULT];

@@ -19,6 +19,7 @@
 #include "ctx.cuh"
 #include "lookback.cuh"
 #include "map.cuh"
+#include "relabel.cuh"
 
 namespace shmt {
 
@@ -42,9 +43,11 @@ struct HopJob {
   void* sub_indptr;
   void* sub_indices;
   TileStates st;
-  int64_t* words;
+  int64_t* ticket;        // tile ticket counter (starts at 0)
+  int64_t* status;        // device status word
+  int64_t* result;        // receives nnz
+  const int64_t* n_dev;   // if set, the seed count is read here (it was produced on the device)
   int seeds_per_tile;
-  int64_t n_tiles;
 };
 
 __device__ __forceinline__ uint64_t draw_below(const Philox& rng, uint32_t seed_idx, uint32_t draw,
@@ -67,9 +70,18 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
   const unsigned full = 0xffffffffu;
   const unsigned tid = threadIdx.x, lane = tid & 31;
   const int S = job.seeds_per_tile;
-  const int tile = take_tile(job.words + W_TICKET, &s_tile);
+  const int64_t n = job.n_dev ? *job.n_dev : job.n;
+  const int64_t n_tiles = (n + S - 1) / S;
+  const int tile = take_tile(job.ticket, &s_tile);
+  if (tile >= n_tiles) {  // the grid is sized for the largest n the caller allows
+    if (n == 0 && tile == 0 && tid == 0) {
+      store_int(job.sub_indptr, job.indptr64, 0, 0);
+      *job.result = 0;
+    }
+    return;
+  }
   const int64_t first = (int64_t)tile * S;
-  const int rows = (int)min((int64_t)S, job.n - first);
+  const int rows = (int)min((int64_t)S, n - first);
   const int64_t k = job.k;
 
   // ---- 1. row bounds and pick counts, one seed per thread
@@ -112,7 +124,7 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
     }
     int64_t run = block_exclusive_scan(sum, warp_sums, &s_total);
     if (tid < 32) {
-      const int64_t p = lookback_exclusive_prefix(job.st, tile, s_total, job.words + W_STATUS);
+      const int64_t p = lookback_exclusive_prefix(job.st, tile, s_total, job.status);
       if (tid == 0) s_prefix = p;
     }
 #pragma unroll
@@ -126,9 +138,9 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
   const int64_t prefix = s_prefix;
   for (int j = (int)tid; j < rows; j += kHopThreads)
     store_int(job.sub_indptr, job.indptr64, first + j, prefix + s_off[j]);
-  if (tile == job.n_tiles - 1 && tid == 0) {
-    store_int(job.sub_indptr, job.indptr64, job.n, prefix + s_total);
-    job.words[W_RESULT] = prefix + s_total;
+  if (tile == n_tiles - 1 && tid == 0) {
+    store_int(job.sub_indptr, job.indptr64, n, prefix + s_total);
+    *job.result = prefix + s_total;
   }
 
   // ---- 3. sampling, one seed per G-lane group
@@ -253,8 +265,8 @@ static int pick_seeds_per_tile(int64_t n) {
 }
 
 template <typename IxT>
-static void launch_hop(const HopJob& job, cudaStream_t s) {
-  const unsigned grid = (unsigned)job.n_tiles;
+static void launch_hop(const HopJob& job, int64_t n_tiles, cudaStream_t s) {
+  const unsigned grid = (unsigned)n_tiles;
   if (job.k <= 8)
     sample_hop_kernel<IxT, 8><<<grid, kHopThreads, 0, s>>>(job);
   else if (job.k <= 16)
@@ -315,19 +327,146 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const v
   job.sub_indptr = out_sub_indptr;
   job.sub_indices = out_sub_indices;
   job.seeds_per_tile = pick_seeds_per_tile(n);
-  job.n_tiles = (n + job.seeds_per_tile - 1) / job.seeds_per_tile;
-  if (int rc = ctx_reserve(ctx, tile_state_bytes(job.n_tiles))) return rc;
-  job.st = carve_tile_states(ctx->region(), job.n_tiles);
-  job.words = ctx->d_words();
-  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + (size_t)job.n_tiles * 4, s));
+  const int64_t n_tiles = (n + job.seeds_per_tile - 1) / job.seeds_per_tile;
+  if (int rc = ctx_reserve(ctx, tile_state_bytes(n_tiles))) return rc;
+  job.st = carve_tile_states(ctx->region(), n_tiles);
+  job.ticket = ctx->d_words() + W_TICKET;
+  job.status = ctx->d_words() + W_STATUS;
+  job.result = ctx->d_words() + W_RESULT;
+  job.n_dev = nullptr;
+  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + (size_t)n_tiles * 4, s));
   if (indices_dtype == SHMT_I64)
-    launch_hop<long long>(job, s);
+    launch_hop<long long>(job, n_tiles, s);
   else
-    launch_hop<int>(job, s);
+    launch_hop<int>(job, n_tiles, s);
   SHMT_CUDA_TRY(cudaGetLastError());
   if (nnz_host) {
     if (int rc = ctx_fetch_words(ctx, s, "shmt_sample_hop")) return rc;
     *nnz_host = ctx->h_words[W_RESULT];
+  }
+  return SHMT_OK;
+}
+
+// Multi-hop mini-batch: every hop's sampling kernel and relabel kernels are queued back
+// to back; each reads the size of its input from the device word the previous stage
+// wrote, with grids sized for the largest frontier the fan-outs allow.  The host waits
+// once, at the end, for all the sizes.
+int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                          int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
+                          const shmt_map* map, const void* seeds, int64_t n_seeds,
+                          const int64_t* fanouts, int n_hops, int replace, uint64_t rng_seed,
+                          uint64_t rng_offset, void* const* out_sub_indptr,
+                          void* const* out_sub_indices, void* const* out_relabel,
+                          void* const* out_frontier, int64_t* sizes_host, void* stream) {
+  constexpr int kMaxHops = 8;
+  SHMT_REQUIRE(ctx != nullptr, "shmt_sample_minibatch: ctx is null");
+  SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(indices_dtype),
+               "shmt_sample_minibatch: ID can only be int32 or int64");
+  SHMT_REQUIRE(n_hops >= 1 && n_hops <= kMaxHops, "shmt_sample_minibatch: 1..%d hops", kMaxHops);
+  SHMT_REQUIRE(n_seeds >= 1 && n_seeds < ((int64_t)1 << 31), "shmt_sample_minibatch: seed count out of range");
+  SHMT_REQUIRE(indptr && indices && seeds && fanouts && out_sub_indptr && out_sub_indices &&
+                   out_relabel && out_frontier && sizes_host,
+               "shmt_sample_minibatch: null argument");
+  SHMT_REQUIRE(map == nullptr || (gpu_indptr != nullptr && gpu_indices != nullptr),
+               "shmt_sample_minibatch: a map needs gpu_indptr and gpu_indices");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+  // worst-case frontier sizes and the scratch plan: [words][per hop: sample tiles | relabel tiles][new-id]
+  int64_t cap[kMaxHops + 1], hop_tiles[kMaxHops], rel_tiles[kMaxHops];
+  int spt[kMaxHops];
+  size_t off_hop[kMaxHops], off_rel[kMaxHops];
+  cap[0] = n_seeds;
+  size_t cursor = ((size_t)(n_hops * 8 + 8) * 8 + 255) & ~(size_t)255;
+  const size_t words_bytes = cursor;
+  uint64_t newid_slots = 0;
+  for (int h = 0; h < n_hops; ++h) {
+    SHMT_REQUIRE(fanouts[h] >= 1 && fanouts[h] < ((int64_t)1 << 20), "shmt_sample_minibatch: fan-out out of range");
+    SHMT_REQUIRE(out_sub_indptr[h] && out_sub_indices[h] && out_relabel[h] && out_frontier[h],
+                 "shmt_sample_minibatch: output buffer of hop %d is null", h);
+    cap[h + 1] = cap[h] * (1 + fanouts[h]);
+    SHMT_REQUIRE(cap[h + 1] < ((int64_t)1 << 30), "shmt_sample_minibatch: worst-case frontier too large");
+    spt[h] = pick_seeds_per_tile(cap[h]);
+    hop_tiles[h] = (cap[h] + spt[h] - 1) / spt[h];
+    rel_tiles[h] = (cap[h + 1] + kRelTile - 1) / kRelTile;
+    off_hop[h] = cursor;
+    cursor += (tile_state_bytes(hop_tiles[h]) + 255) & ~(size_t)255;
+    off_rel[h] = cursor;
+    cursor += (tile_state_bytes(rel_tiles[h]) + 255) & ~(size_t)255;
+    const uint64_t c = relabel_capacity(cap[h + 1]);
+    if (c > newid_slots) newid_slots = c;
+  }
+  const size_t zero_bytes = cursor;
+  if (int rc = ctx_reserve(ctx, cursor + newid_slots * 4)) return rc;
+  char* base = ctx->region();
+  int64_t* words = reinterpret_cast<int64_t*>(base);
+  unsigned* newid = reinterpret_cast<unsigned*>(base + cursor);
+  (void)words_bytes;
+  SHMT_CUDA_TRY(cudaMemsetAsync(base, 0, zero_bytes, s));  // words, tickets and every tile flag
+  int64_t* status = words + n_hops * 8;
+
+  const void* cur_seeds = seeds;
+  for (int h = 0; h < n_hops; ++h) {
+    int64_t* w = words + h * 8;  // [0] hop ticket, [1] nnz, [2] relabel ticket, [3] n_unique
+    HopJob job{};
+    job.indptr = indptr;
+    job.indptr64 = indptr_dtype == SHMT_I64;
+    job.indices = indices;
+    job.gpu_indptr = gpu_indptr;
+    job.gpu_indices = gpu_indices;
+    job.map = view_of(map);
+    job.seeds = cur_seeds;
+    job.seeds64 = indices_dtype == SHMT_I64;
+    job.n = h == 0 ? n_seeds : 0;
+    job.n_dev = h == 0 ? nullptr : words + (h - 1) * 8 + 3;
+    job.k = fanouts[h];
+    job.replace = replace != 0;
+    job.rng_seed = rng_seed;
+    job.off_lo = (uint32_t)(rng_offset + h);
+    job.off_hi = (uint32_t)((rng_offset + h) >> 32);
+    job.sub_indptr = out_sub_indptr[h];
+    job.sub_indices = out_sub_indices[h];
+    job.seeds_per_tile = spt[h];
+    job.st = carve_tile_states(base + off_hop[h], hop_tiles[h]);
+    job.ticket = w + 0;
+    job.status = status;
+    job.result = w + 1;
+    if (indices_dtype == SHMT_I64)
+      launch_hop<long long>(job, hop_tiles[h], s);
+    else
+      launch_hop<int>(job, hop_tiles[h], s);
+    SHMT_CUDA_TRY(cudaGetLastError());
+
+    Parts ps{};
+    ps.n = 2;
+    ps.is64 = indices_dtype == SHMT_I64;
+    ps.ptr[0] = cur_seeds;
+    ps.ptr[1] = out_sub_indices[h];
+    ps.start[1] = n_seeds;  // used for hop 0 only, whose seed count the host knows
+    ps.dev_n0 = h == 0 ? nullptr : words + (h - 1) * 8 + 3;
+    ps.dev_n1 = w + 1;
+    if (int rc = launch_relabel(ctx, ps, cap[h + 1], newid, out_frontier[h], out_relabel[h],
+                                carve_tile_states(base + off_rel[h], rel_tiles[h]), w + 2, status,
+                                w + 3, s))
+      return rc;
+    cur_seeds = out_frontier[h];
+  }
+  const size_t n_words = (size_t)n_hops * 8 + 8;
+  SHMT_CUDA_TRY(cudaMemcpyAsync(ctx->h_words, words, n_words * sizeof(int64_t), cudaMemcpyDeviceToHost, s));
+  SHMT_CUDA_TRY(cudaStreamSynchronize(s));
+  const int64_t st = ctx->h_words[n_hops * 8];
+  if (st != DEV_OK) {
+    ctx->table_dirty = true;
+    set_error("shmt_sample_minibatch: device status %lld (%s)", (long long)st,
+              st == DEV_TIMEOUT ? "a bounded look-back wait ran out" : "relabel table overflow");
+    return st == DEV_TIMEOUT ? SHMT_ERR_TIMEOUT : SHMT_ERR_CAPACITY;
+  }
+  int64_t n_in = n_seeds;
+  for (int h = 0; h < n_hops; ++h) {
+    sizes_host[3 * h + 0] = n_in;
+    sizes_host[3 * h + 1] = ctx->h_words[h * 8 + 1];
+    sizes_host[3 * h + 2] = ctx->h_words[h * 8 + 3];
+    n_in = sizes_host[3 * h + 2];
   }
   return SHMT_OK;
 }

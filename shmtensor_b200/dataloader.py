@@ -36,12 +36,14 @@ class GPUSamplingDataloader:
 
     def __init__(self, indptr, indices, seeds, batchsize, num_picks, replace=False,
                  use_ddp=False, shuffle=True, drop_last=False,
-                 block_fn: Optional[Callable] = None):
+                 block_fn: Optional[Callable] = None, fused: bool = True):
         self.indptr, self.indices = indptr, indices
         self.batchsize, self.num_picks, self.replace = batchsize, num_picks, replace
         self.use_ddp, self.shuffle, self.drop_last = use_ddp, shuffle, drop_last
         self.block_fn = _dgl_block if block_fn == "dgl" else (block_fn or _plain_block)
 
+        # fused: one native call per mini-batch; False keeps the reference's call-per-hop loop
+        self.fused = fused
         self.has_cache = False
         self.gpu_indptr = self.gpu_indices = self.hashmap = None
 
@@ -106,6 +108,18 @@ class GPUSamplingDataloader:
         self.curr += 1
 
         output_nodes, blocks = seeds, []
+        if self.fused:
+            # all hops in one native call: no host round trip between hops
+            _, hops = capi.sample_minibatch(self.indptr, self.indices, seeds,
+                                            list(reversed(self.num_picks)), self.replace,
+                                            self.gpu_indptr if self.has_cache else None,
+                                            self.gpu_indices if self.has_cache else None,
+                                            self.hashmap if self.has_cache else None)
+            n_dst = seeds.numel()
+            for sub_indptr, _, relabel_indices, frontier in hops:
+                blocks.insert(0, self.block_fn(sub_indptr, relabel_indices, frontier.numel(), n_dst))
+                n_dst = frontier.numel()
+            return hops[-1][3].to(seeds.dtype), output_nodes, blocks
         for num_pick in reversed(self.num_picks):
             sub_indptr, sub_indices = self._hop(seeds, num_pick)
             frontier, (_, relabel_indices) = capi.tensor_relabel([seeds, sub_indices])

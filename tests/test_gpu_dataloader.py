@@ -76,3 +76,47 @@ def test_presampling_and_weight_size():
     assert s_hot.sum() >= 2000 and (f_hot >= s_hot).all()
     full, item = dl.compute_weight_size(f_hot)
     assert full == indptr_n.nbytes + indices_n.nbytes and item > 0
+
+
+@pytest.mark.parametrize("cached", [False, True])
+@pytest.mark.parametrize("idx_dtype", [torch.int32, torch.int64])
+def test_fused_minibatch_equals_hop_by_hop(cached, idx_dtype):
+    """shmt_sample_minibatch queues all hops without a host round trip; with the same Philox key
+    and call counter it must return exactly what the per-hop calls return."""
+    from shmtensor_b200 import capi
+    indptr_n, indices_n = _graph(30_000, seed=3)
+    indptr = torch.from_numpy(indptr_n)
+    indices = torch.from_numpy(indices_n).to(idx_dtype)
+    capi.pin_memory(indptr)
+    capi.pin_memory(indices)
+    try:
+        gp = gi = hmap = None
+        if cached:
+            hot = torch.from_numpy(np.argsort(-np.diff(indptr_n))[:6000].copy()).cuda()
+            gp, gi = capi.create_subcsr(indptr, indices, hot)
+            hmap = capi.CUCOStaticHashmap(hot.int(), torch.arange(6000, dtype=torch.int32, device="cuda"), 0.8)
+        for n_seeds, fanouts in ((1024, [5, 10, 15]), (1, [3]), (333, [40, 2])):
+            seeds = torch.randperm(30_000, device="cuda")[:n_seeds].to(idx_dtype)
+            capi.set_sampling_seed(4242)
+            want, cur = [], seeds
+            for k in fanouts:
+                if cached:
+                    p, x = capi.csr_cache_sampling(indptr, indices, gp, gi, hmap, cur, k, False)
+                else:
+                    p, x = capi.csr_sampling(indptr, indices, cur, k, False)
+                nxt, (_, rx) = capi.tensor_relabel([cur, x])
+                want.append((p, x, rx, nxt))
+                cur = nxt
+            capi.set_sampling_seed(4242)
+            frontier, hops = capi.sample_minibatch(indptr, indices, seeds, fanouts, False, gp, gi, hmap)
+            assert torch.equal(frontier, cur) and len(hops) == len(fanouts)
+            for (p, x, rx, nxt), (p2, x2, rx2, nxt2) in zip(want, hops):
+                assert torch.equal(p, p2) and torch.equal(x, x2)
+                assert torch.equal(rx, rx2) and torch.equal(nxt, nxt2)
+            # twice in a row: the relabel table must come back clean
+            capi.set_sampling_seed(4242)
+            frontier2, _ = capi.sample_minibatch(indptr, indices, seeds, fanouts, False, gp, gi, hmap)
+            assert torch.equal(frontier2, frontier)
+    finally:
+        capi.unpin_memory(indptr)
+        capi.unpin_memory(indices)

@@ -81,9 +81,11 @@ def test_relabel_is_repeatable_and_idempotent(capi):
 def test_relabel_errors(capi):
     with pytest.raises(RuntimeError):
         capi.tensor_relabel([])
-    with pytest.raises(RuntimeError, match="share dtype"):
-        capi.tensor_relabel([torch.zeros(2, dtype=torch.int64, device="cuda"),
-                             torch.zeros(2, dtype=torch.int32, device="cuda")])
+    # mixed integer widths are promoted, as the reference's torch::cat does
+    u, (a, b) = capi.tensor_relabel([torch.tensor([5, 7], dtype=torch.int64, device="cuda"),
+                                     torch.tensor([7, 9], dtype=torch.int32, device="cuda")])
+    assert u.dtype == torch.int64 and u.cpu().tolist() == [5, 7, 9]
+    assert a.cpu().tolist() == [0, 1] and b.cpu().tolist() == [1, 2]
     with pytest.raises(RuntimeError, match="int32 or int64"):
         capi.tensor_relabel([torch.zeros(2, device="cuda")])
     e = torch.empty(0, dtype=torch.int64, device="cuda")
