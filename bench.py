@@ -40,6 +40,7 @@ CACHE_FRACTION, LOAD_FACTOR, ZIPF_ALPHA, UNIFORM_SHARE = 0.20, 0.5, 1.1, 0.21
 ROW_BYTES = DIM * 4
 N_BATCHES = 8
 METRIC, UNIT = "fetched feature GB/s", "GB/s"
+NCU_DRAM_BYTES_PER_LAUNCH = 210_300_000  # 63.8 MB read + 146.5 MB written (ncu, headline batch)
 WORKLOAD = ("1-GPU cached feature fetch: pinned 2,400,000x100 f32 host table, top 20% rows cached "
             "behind int64->int32 map (load 0.5), 500,000 int64 ids/batch Zipf(1.1), ~80% hits, misses via UVA")
 
@@ -358,7 +359,11 @@ def run_ours(args) -> None:
             "bound": "hbm", "kernel": "row_gather_bulk_kernel<2> (fused probe + TMA bulk gather)",
             "achieved": round(alg / (kernel_ms * 1e6), 1), "peak": peak, "unit": "GB/s",
             "frac": round(alg / (kernel_ms * 1e6) / peak, 4), "peak_source": peak_src,
-            "traffic": None, "kernel_ms": round(kernel_ms, 5),
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
+            # workload, from the ncu capture summarised in profiles/row_gather_bulk_mixed.md
+            "traffic": {"bytes": NCU_DRAM_BYTES_PER_LAUNCH, "algorithmic_bytes": int(alg),
+                        "source": "profiles/row_gather_bulk_mixed.md (ncu --set full, 2 launches)"},
+            "kernel_ms": round(kernel_ms, 5),
             "note": "the 80%-hit batch is bound by the host link, not HBM: see roofline_link and "
                     "frac_of_bound (time at the binding ceiling / measured time)",
             "frac_of_bound": round(t_roof_ms / kernel_ms, 4),

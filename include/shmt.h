@@ -55,15 +55,20 @@ int64_t shmt_ctx_scratch_bytes(const shmt_ctx* ctx);
  *  src/cuco_hashmap.cu:10-41).                                                */
 typedef struct shmt_map shmt_map;
 
-/* bytes of table storage a map of `capacity` requested slots needs            */
-int64_t shmt_map_table_bytes(int64_t capacity);
+/* bytes of table storage for a map of `capacity` requested slots that will hold
+ * about `expected_keys` keys (0 = unknown).  The table is provisioned for load
+ * <= 0.5 on the expected keys, and never below capacity + 1/16: short probes matter
+ * more to the kernels than table bytes.                                           */
+int64_t shmt_map_table_bytes(int64_t capacity, int64_t expected_keys);
 
 /* Create an empty map.  `capacity` is what shmt_map_capacity() reports
  * (the reference reports ceil(n / load_factor), include/cuco_hashmap.cuh:62,75).
- * table_buf: device buffer of shmt_map_table_bytes(capacity) bytes, 16-byte
- * aligned, that must outlive the map; NULL lets the map cudaMalloc its own.   */
-int shmt_map_create(int device, int64_t capacity, int key_dtype, int val_dtype,
-                    void* table_buf, void* stream, shmt_map** out);
+ * table_buf: device buffer of shmt_map_table_bytes(capacity, expected_keys)
+ * bytes, 16-byte aligned, that must outlive the map; NULL lets the map cudaMalloc
+ * its own.                                                                      */
+int shmt_map_create(int device, int64_t capacity, int64_t expected_keys,
+                    int key_dtype, int val_dtype, void* table_buf, void* stream,
+                    shmt_map** out);
 
 /* insert_or_assign of n (key, value) pairs, key != -1.  Synchronises `stream`
  * and returns SHMT_ERR_CAPACITY if the table overflowed.  Bulk-insert half of

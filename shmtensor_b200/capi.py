@@ -191,18 +191,19 @@ class CUCOStaticHashmap:
         if keys.numel() != values.numel():
             raise RuntimeError("keys and values must have the same number of elements")
         capacity = int(math.ceil(keys.numel() / load_factor))
-        self._init_empty(capacity, kd, vd, keys.device)
+        self._init_empty(capacity, kd, vd, keys.device, expected_keys=keys.numel())
         self.insert(keys, values)
 
-    def _init_empty(self, capacity: int, kd: int, vd: int, device: torch.device) -> None:
+    def _init_empty(self, capacity: int, kd: int, vd: int, device: torch.device,
+                    expected_keys: int = 0) -> None:
         self._handle = None
         self._device = device
         self._kd, self._vd = kd, vd
-        nbytes = lib.shmt_map_table_bytes(capacity)
+        nbytes = lib.shmt_map_table_bytes(capacity, expected_keys)
         # table memory comes from torch's caching allocator, like the reference's torch_allocator
         self._table = torch.empty(nbytes, dtype=torch.uint8, device=device)
         out = C.c_void_p()
-        check(lib.shmt_map_create(device.index, capacity, kd, vd, self._table.data_ptr(),
+        check(lib.shmt_map_create(device.index, capacity, expected_keys, kd, vd, self._table.data_ptr(),
                                   _stream(device), C.byref(out)))
         self._handle = out.value
 

@@ -54,10 +54,13 @@ inline unsigned grid_for_warps(int64_t n_items_per_warp32) {
   return (unsigned)blocks;
 }
 
-inline uint64_t windows_for(int64_t capacity) {
-  // 1/16 slack over the requested capacity keeps probes short even when the
-  // caller asks for load factor 1.0
-  const uint64_t slots = (uint64_t)capacity + (uint64_t)capacity / 16 + kWindow;
+inline uint64_t windows_for(int64_t capacity, int64_t expected_keys) {
+  // Probe length, not memory, is what the kernels pay for: provision at least two slots
+  // per expected key (load <= 0.5: a lookup ends in its home window almost always, whatever
+  // load factor the caller asked for), and never less than the requested capacity + 1/16.
+  uint64_t slots = (uint64_t)capacity + (uint64_t)capacity / 16;
+  if (expected_keys > 0 && (uint64_t)expected_keys * 2 > slots) slots = (uint64_t)expected_keys * 2;
+  slots += kWindow;
   return (slots + kWindow - 1) / kWindow;
 }
 
@@ -67,12 +70,13 @@ using namespace shmt;
 
 extern "C" {
 
-int64_t shmt_map_table_bytes(int64_t capacity) {
+int64_t shmt_map_table_bytes(int64_t capacity, int64_t expected_keys) {
   if (capacity < 0) return 0;
-  return (int64_t)(windows_for(capacity) * kWindow * sizeof(Slot) + 256);
+  return (int64_t)(windows_for(capacity, expected_keys) * kWindow * sizeof(Slot) + 256);
 }
 
-int shmt_map_create(int device, int64_t capacity, int key_dtype, int val_dtype, void* table_buf,
+int shmt_map_create(int device, int64_t capacity, int64_t expected_keys, int key_dtype,
+                    int val_dtype, void* table_buf,
                     void* stream, shmt_map** out) {
   SHMT_REQUIRE(out != nullptr, "shmt_map_create: out is null");
   SHMT_REQUIRE(capacity >= 0, "shmt_map_create: negative capacity");
@@ -85,7 +89,7 @@ int shmt_map_create(int device, int64_t capacity, int key_dtype, int val_dtype, 
   m->capacity = capacity;
   m->key_dtype = key_dtype;
   m->val_dtype = val_dtype;
-  m->table_bytes = (size_t)shmt_map_table_bytes(capacity);
+  m->table_bytes = (size_t)shmt_map_table_bytes(capacity, expected_keys);
   void* buf = table_buf;
   if (!buf) {
     cudaError_t e = cudaMalloc(&buf, m->table_bytes);
@@ -98,7 +102,7 @@ int shmt_map_create(int device, int64_t capacity, int key_dtype, int val_dtype, 
     m->owns_table = true;
   }
   m->view.slots = static_cast<Slot*>(buf);
-  m->view.n_windows = windows_for(capacity);
+  m->view.n_windows = windows_for(capacity, expected_keys);
   m->view.key32 = key_dtype == SHMT_I32;
   m->d_meta = reinterpret_cast<int64_t*>(static_cast<char*>(buf) + m->table_bytes - 256);
   cudaStream_t s = static_cast<cudaStream_t>(stream);

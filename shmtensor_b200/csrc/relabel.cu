@@ -38,6 +38,15 @@ __global__ void __launch_bounds__(kRelThreads)
 relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* status) {
   int64_t numel;
   resolve_sizes(ps, &numel);
+  // The table is provisioned for the largest input the caller allows; hash into only as
+  // much of it as this input needs (load <= 0.5), so a small input stays in a small,
+  // cache-resident part.  Only this kernel hashes; the others follow the recorded slots.
+  uint32_t mask = t.mask;
+  if (numel > 0) {
+    const uint32_t want = numel * 2 <= 64 ? 63u : (0xFFFFFFFFu >> __clz((uint32_t)(numel * 2 - 1)));
+    if (want < mask) mask = want;
+  }
+  t.mask = mask;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
     const long long key = part_elem(ps, i);

@@ -50,6 +50,26 @@ struct HopJob {
   int seeds_per_tile;
 };
 
+// indptr[i] and indptr[i+1] with one load when the pair is naturally aligned (one request on
+// the host link instead of two for a row that lives in host memory).
+__device__ __forceinline__ void load_bounds(const void* indptr, int is64, int64_t i, int64_t* b,
+                                            int64_t* e) {
+  if ((i & 1) == 0) {
+    if (is64) {
+      const longlong2 v = __ldg(reinterpret_cast<const longlong2*>(indptr) + (i >> 1));
+      *b = v.x;
+      *e = v.y;
+    } else {
+      const int2 v = __ldg(reinterpret_cast<const int2*>(indptr) + (i >> 1));
+      *b = v.x;
+      *e = v.y;
+    }
+  } else {
+    *b = load_int(indptr, is64, i);
+    *e = load_int(indptr, is64, i + 1);
+  }
+}
+
 __device__ __forceinline__ uint64_t draw_below(const Philox& rng, uint32_t seed_idx, uint32_t draw,
                                                uint32_t off_lo, uint32_t off_hi, uint64_t range) {
   const uint4 r = rng(seed_idx, draw, off_lo, off_hi);
@@ -93,13 +113,10 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
     if (job.map.slots) slot = warp_find(job.map, row, valid);
     int64_t b = 0, e = 0;
     if (valid) {
-      if (slot >= 0) {
-        b = load_int(job.gpu_indptr, job.indptr64, slot);
-        e = load_int(job.gpu_indptr, job.indptr64, slot + 1);
-      } else {
-        b = load_int(job.indptr, job.indptr64, row);
-        e = load_int(job.indptr, job.indptr64, row + 1);
-      }
+      if (slot >= 0)
+        load_bounds(job.gpu_indptr, job.indptr64, slot, &b, &e);
+      else
+        load_bounds(job.indptr, job.indptr64, row, &b, &e);
     }
     const int64_t deg = e - b;
     if (j < S) {
@@ -111,7 +128,62 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
   }
   __syncthreads();
 
-  // ---- 2. offsets: scan inside the tile, look-back across tiles
+  constexpr int kGroups = kHopThreads / G;
+  constexpr int U = 8;  // seeds per group; a tile never holds more than kGroups * U when k <= G
+  const unsigned gl = tid & (G - 1);
+  const unsigned gshift = lane & ~(unsigned)(G - 1);  // first lane of my group within the warp
+  const unsigned gmask = G == 32 ? full : (((1u << G) - 1u) << gshift);
+  const int group = (int)(tid / G);
+  const Philox rng(job.rng_seed);
+  IxT* out_all = static_cast<IxT*>(job.sub_indices);
+
+  // ---- 2. (k <= G) pick positions and LOAD the neighbours now, before the tile's output
+  // offset is known: the loads (often over the host link) then overlap the look-back wait
+  // and the other tiles' row-bound reads.  One element per lane and seed; the U seeds of a
+  // group are resolved first (arithmetic and shuffles only), then their loads go out back
+  // to back.
+  const IxT* src[U];
+  IxT v[U];
+  if (k <= G) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = u * kGroups + group;
+      const bool active = j < rows;
+      const int64_t deg = active ? s_deg[j] : 0;
+      const uint32_t seed_idx = (uint32_t)(first + j);
+      int64_t pos = -1;
+      if (job.replace) {
+        if (deg > 0 && (int64_t)gl < k)
+          pos = (int64_t)draw_below(rng, seed_idx, gl, job.off_lo, job.off_hi, (uint64_t)deg);
+      } else {
+        if (active && deg <= k && (int64_t)gl < deg) pos = gl;
+        const bool pick = active && deg > k;
+        // Floyd: step p inserts t_p unless already chosen, then inserts deg-k+p instead
+        if (__any_sync(full, pick)) {
+          const int64_t top = deg - k + (int64_t)gl;  // largest position step gl may choose
+          int64_t t = -1;
+          if (pick && (int64_t)gl < k)
+            t = (int64_t)draw_below(rng, seed_idx, gl, job.off_lo, job.off_hi, (uint64_t)top + 1);
+          int64_t res = -1;
+          for (int p = 0; p < (int)k; ++p) {
+            const int64_t cand = __shfl_sync(full, t, p, G);
+            const bool clash = pick && (int)gl < p && res == cand;
+            const unsigned votes = __ballot_sync(full, clash) & gmask;
+            if ((int)gl == p) res = votes ? top : cand;
+          }
+          if (pick && (int64_t)gl < k) pos = res;
+        }
+      }
+      src[u] = nullptr;
+      if (pos >= 0)
+        src[u] = static_cast<const IxT*>(s_hit[j] ? job.gpu_indices : job.indices) + s_begin[j] + pos;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (src[u]) v[u] = __ldg(src[u]);
+  }
+
+  // ---- 3. offsets: scan inside the tile, look-back across tiles
   {
     const int ch = (S + kHopThreads - 1) / kHopThreads;  // seeds per thread, 1..4
     int64_t c[kMaxSeedsPerTile / kHopThreads];
@@ -143,15 +215,17 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
     *job.result = prefix + s_total;
   }
 
-  // ---- 3. sampling, one seed per G-lane group
-  constexpr int kGroups = kHopThreads / G;
-  const unsigned gl = tid & (G - 1);
-  const unsigned gshift = lane & ~(unsigned)(G - 1);  // first lane of my group within the warp
-  const unsigned gmask = G == 32 ? full : (((1u << G) - 1u) << gshift);
-  const int group = (int)(tid / G);
-  const Philox rng(job.rng_seed);
-  IxT* out_all = static_cast<IxT*>(job.sub_indices);
+  // ---- 4. output
+  if (k <= G) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = u * kGroups + group;
+      if (src[u]) out_all[prefix + s_off[j] + gl] = v[u];
+    }
+    return;
+  }
 
+  // k > 32 (G == 32, one warp per seed): rows are walked k lanes at a time
   for (int j0 = 0; j0 < rows; j0 += kGroups) {
     const int j = j0 + group;
     const bool active = j < rows;
@@ -163,7 +237,6 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
       out = out_all + prefix + s_off[j];
     }
     const uint32_t seed_idx = (uint32_t)(first + j);
-
     if (job.replace) {
       if (deg > 0)
         for (int64_t p = gl; p < k; p += G)
@@ -173,38 +246,19 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
     if (active && deg <= k) {
       for (int64_t p = gl; p < deg; p += G) out[p] = in[p];
     }
-    const bool pick = active && deg > k;
-    if (k <= G) {
-      // Floyd: step p inserts t_p unless already chosen, then inserts deg-k+p instead
-      if (__any_sync(full, pick)) {
-        const int64_t top = deg - k + (int64_t)gl;  // largest position step gl may choose
-        int64_t t = -1;
-        if (pick && (int64_t)gl < k)
-          t = (int64_t)draw_below(rng, seed_idx, gl, job.off_lo, job.off_hi, (uint64_t)top + 1);
-        int64_t res = -1;
-        for (int p = 0; p < (int)k; ++p) {
-          const int64_t cand = __shfl_sync(full, t, p, G);
-          const bool clash = pick && (int)gl < p && res == cand;
-          const unsigned votes = __ballot_sync(full, clash) & gmask;
-          if ((int)gl == p) res = votes ? top : cand;
-        }
-        if (pick && (int64_t)gl < k) out[gl] = in[res];
+    // reservoir on the output row: positions first, then values
+    if (active && deg > k) {
+      for (int64_t p = gl; p < k; p += 32) out[p] = (IxT)p;
+      __syncwarp();
+      for (int64_t q = k + gl; q < deg; q += 32) {
+        const uint64_t r = draw_below(rng, seed_idx, (uint32_t)q, job.off_lo, job.off_hi, (uint64_t)q + 1);
+        if (r < (uint64_t)k) atomicMax(out + r, (IxT)q);
       }
-    } else {
-      // k > 32 (G == 32): reservoir on the output row, positions first, then values
-      if (pick) {
-        for (int64_t p = gl; p < k; p += 32) out[p] = (IxT)p;
-        __syncwarp();
-        for (int64_t q = k + gl; q < deg; q += 32) {
-          const uint64_t r = draw_below(rng, seed_idx, (uint32_t)q, job.off_lo, job.off_hi, (uint64_t)q + 1);
-          if (r < (uint64_t)k) atomicMax(out + r, (IxT)q);
-        }
-        __syncwarp();
-        __threadfence_block();
-        for (int64_t p = gl; p < k; p += 32) {
-          const IxT pos = *reinterpret_cast<volatile IxT*>(out + p);
-          out[p] = in[pos];
-        }
+      __syncwarp();
+      __threadfence_block();
+      for (int64_t p = gl; p < k; p += 32) {
+        const IxT pos = *reinterpret_cast<volatile IxT*>(out + p);
+        out[p] = in[pos];
       }
     }
   }
@@ -256,11 +310,14 @@ int launch_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
                 size_t scratch_off, cudaStream_t stream);
 size_t scan_scratch_bytes(int64_t n);
 
-static int pick_seeds_per_tile(int64_t n) {
+static int pick_seeds_per_tile(int64_t n, int64_t k) {
   int64_t s = (n + (int64_t)sm_count() * 4 - 1) / ((int64_t)sm_count() * 4);
   s = (s + 31) / 32 * 32;
   if (s < 32) s = 32;
   if (s > kMaxSeedsPerTile) s = kMaxSeedsPerTile;
+  // with k <= 32 a tile is sampled in one pass of 8 seeds per lane group (see the kernel)
+  const int64_t one_pass = k <= 8 ? 256 : (k <= 16 ? 128 : (k <= 32 ? 64 : kMaxSeedsPerTile));
+  if (s > one_pass) s = one_pass;
   return (int)s;
 }
 
@@ -326,7 +383,7 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const v
   job.off_hi = (uint32_t)(rng_offset >> 32);
   job.sub_indptr = out_sub_indptr;
   job.sub_indices = out_sub_indices;
-  job.seeds_per_tile = pick_seeds_per_tile(n);
+  job.seeds_per_tile = pick_seeds_per_tile(n, k);
   const int64_t n_tiles = (n + job.seeds_per_tile - 1) / job.seeds_per_tile;
   if (int rc = ctx_reserve(ctx, tile_state_bytes(n_tiles))) return rc;
   job.st = carve_tile_states(ctx->region(), n_tiles);
@@ -386,7 +443,7 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
                  "shmt_sample_minibatch: output buffer of hop %d is null", h);
     cap[h + 1] = cap[h] * (1 + fanouts[h]);
     SHMT_REQUIRE(cap[h + 1] < ((int64_t)1 << 30), "shmt_sample_minibatch: worst-case frontier too large");
-    spt[h] = pick_seeds_per_tile(cap[h]);
+    spt[h] = pick_seeds_per_tile(cap[h], fanouts[h]);
     hop_tiles[h] = (cap[h] + spt[h] - 1) / spt[h];
     rel_tiles[h] = (cap[h + 1] + kRelTile - 1) / kRelTile;
     off_hop[h] = cursor;

@@ -41,7 +41,8 @@ def test_invalid_arguments_return_status_not_crash():
     assert lib.shmt_fetch(None, None, 0, None, None, None, 1, 0, 16, None, None) == _lib.OK  # n == 0
     assert lib.shmt_fetch(None, None, 0, None, None, None, 1, 4, 0, None, None) == _lib.ERR_INVALID
     assert lib.shmt_map_query(None, None, 0, 1, None, None) == _lib.ERR_INVALID
-    assert lib.shmt_map_table_bytes(1000) >= 1000 * 16
+    assert lib.shmt_map_table_bytes(1000, 0) >= 1000 * 16
+    assert lib.shmt_map_table_bytes(1000, 800) >= 1600 * 16
     p, fd = C.c_int64(), C.c_int64()
     assert lib.shmt_shm_open(b"/shmt_does_not_exist", 64, 0, C.byref(p), C.byref(fd)) == _lib.ERR_OS
     assert "fail to open" in _lib.last_error()
