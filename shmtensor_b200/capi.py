@@ -500,11 +500,22 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
     caps = [seeds.numel()]
     for k in fanouts:
         caps.append(caps[-1] * (1 + int(k)))
-    sub_indptr = [torch.empty(caps[h] + 1, dtype=indptr.dtype, device=dev) for h in range(n_hops)]
-    sub_indices = [torch.empty(caps[h] * int(fanouts[h]), dtype=indices.dtype, device=dev) for h in range(n_hops)]
-    relabel = [torch.empty(caps[h + 1], dtype=indices.dtype, device=dev) for h in range(n_hops)]
-    frontier = [torch.empty(caps[h + 1], dtype=indices.dtype, device=dev) for h in range(n_hops)]
-    arr = lambda ts: (C.c_void_p * n_hops)(*[t.data_ptr() for t in ts])
+    # two allocations (one per dtype); the per-hop outputs are 16-byte aligned pieces of them,
+    # handed to the library as raw addresses and turned into views only once sizes are known
+    def plan(dtype, counts):
+        item = torch.empty((), dtype=dtype).element_size()
+        step = 16 // item
+        offs, lo = [], 0
+        for c in counts:
+            offs.append(lo)
+            lo += -(-c // step) * step
+        pool = torch.empty(lo, dtype=dtype, device=dev)
+        base = pool.data_ptr()
+        return pool, offs, [base + o * item for o in offs]
+    p_pool, p_off, p_ptr = plan(indptr.dtype, [caps[h] + 1 for h in range(n_hops)])
+    i_pool, i_off, i_ptr = plan(indices.dtype, [caps[h] * int(fanouts[h]) for h in range(n_hops)]
+                                + [caps[h + 1] for h in range(n_hops)] * 2)
+    arr = lambda ptrs: (C.c_void_p * n_hops)(*ptrs)
     sizes = (C.c_int64 * (3 * n_hops))()
     fan = (C.c_int64 * n_hops)(*[int(k) for k in fanouts])
     offset = _rng["calls"] + 1
@@ -512,13 +523,15 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
     check(lib.shmt_sample_minibatch(_ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr),
                                     _ptr(gpu_indices), hashmap._handle if hashmap is not None else None,
                                     _ptr(seeds), seeds.numel(), fan, n_hops, int(bool(replace)),
-                                    _rng["seed"], offset, arr(sub_indptr), arr(sub_indices), arr(relabel),
-                                    arr(frontier), sizes, _stream(dev)))
+                                    _rng["seed"], offset, arr(p_ptr), arr(i_ptr[:n_hops]),
+                                    arr(i_ptr[n_hops:2 * n_hops]), arr(i_ptr[2 * n_hops:]), sizes,
+                                    _stream(dev)))
     hops = []
     for h in range(n_hops):
         n_in, nnz, n_out = sizes[3 * h], sizes[3 * h + 1], sizes[3 * h + 2]
-        hops.append((sub_indptr[h][: n_in + 1], sub_indices[h][:nnz], relabel[h][n_in:n_in + nnz],
-                     frontier[h][:n_out]))
+        x, r, f = i_off[h], i_off[n_hops + h] + n_in, i_off[2 * n_hops + h]
+        hops.append((p_pool[p_off[h]:p_off[h] + n_in + 1], i_pool[x:x + nnz], i_pool[r:r + nnz],
+                     i_pool[f:f + n_out]))
     return hops[-1][3], hops
 
 

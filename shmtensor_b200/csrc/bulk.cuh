@@ -1,7 +1,7 @@
 // Bulk asynchronous copies (the TMA unit's untiled mode, sm_90+/sm_100a) and the
 // mbarrier calls that track them.  Global->shared copies complete on an mbarrier
 // by byte count; shared->global copies are tracked by per-thread bulk groups.
-// No cluster multicast anywhere: every copy has exactly one destination CTA, so
+// Every copy has exactly one destination CTA (the issuing one), so
 // the source may be local HBM, pinned host memory or a peer GPU's buffer.
 // Both addresses must be 16-byte aligned and the size a multiple of 16 bytes.
 #pragma once

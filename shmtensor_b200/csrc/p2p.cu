@@ -8,7 +8,7 @@
 namespace shmt {
 
 // Every thread folds 16-byte loads into a checksum; a few threads publish it so
-// the loads cannot be optimised away.  Plain loads only (no multicast), so the
+// the loads cannot be optimised away.  Plain per-thread loads only, so the
 // source may be local HBM, pinned host memory or a peer GPU's buffer.
 __global__ void __launch_bounds__(256)
 stream_read_kernel(const uint4* __restrict__ src, int64_t n_vec, unsigned long long* sink) {
