@@ -87,6 +87,8 @@ def _row_bytes(data: torch.Tensor) -> int:
 
 
 _rng = {"seed": 7777, "calls": 0}
+_ITEMSIZE = {torch.int32: 4, torch.int64: 8}
+_minibatch_layouts: dict = {}
 
 
 def set_sampling_seed(seed: int) -> None:
@@ -502,36 +504,51 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
         caps.append(caps[-1] * (1 + int(k)))
     # two allocations (one per dtype); the per-hop outputs are 16-byte aligned pieces of them,
     # handed to the library as raw addresses and turned into views only once sizes are known
-    def plan(dtype, counts):
-        item = torch.empty((), dtype=dtype).element_size()
-        step = 16 // item
-        offs, lo = [], 0
-        for c in counts:
-            offs.append(lo)
-            lo += -(-c // step) * step
-        pool = torch.empty(lo, dtype=dtype, device=dev)
-        base = pool.data_ptr()
-        return pool, offs, [base + o * item for o in offs]
-    p_pool, p_off, p_ptr = plan(indptr.dtype, [caps[h] + 1 for h in range(n_hops)])
-    i_pool, i_off, i_ptr = plan(indices.dtype, [caps[h] * int(fanouts[h]) for h in range(n_hops)]
-                                + [caps[h + 1] for h in range(n_hops)] * 2)
-    arr = lambda ptrs: (C.c_void_p * n_hops)(*ptrs)
+    key = (seeds.numel(), tuple(int(k) for k in fanouts), indptr.dtype, indices.dtype)
+    layout = _minibatch_layouts.get(key)
+    if layout is None:
+        def plan(dtype, counts):
+            item = _ITEMSIZE[dtype]
+            step = 16 // item
+            offs, lo = [], 0
+            for c in counts:
+                offs.append(lo)
+                lo += -(-c // step) * step
+            return offs + [lo], item
+        p_off, p_item = plan(indptr.dtype, [caps[h] + 1 for h in range(n_hops)])
+        i_off, i_item = plan(indices.dtype, [caps[h] * int(fanouts[h]) for h in range(n_hops)]
+                             + [caps[h + 1] for h in range(n_hops)] * 2)
+        fan = (C.c_int64 * n_hops)(*[int(k) for k in fanouts])
+        layout = _minibatch_layouts[key] = (p_off, p_item, i_off, i_item, fan)
+    p_off, p_item, i_off, i_item, fan = layout
+    p_pool = torch.empty(p_off[-1], dtype=indptr.dtype, device=dev)
+    i_pool = torch.empty(i_off[-1], dtype=indices.dtype, device=dev)
+    p_base, i_base = p_pool.data_ptr(), i_pool.data_ptr()
+    VP = C.c_void_p * n_hops
     sizes = (C.c_int64 * (3 * n_hops))()
-    fan = (C.c_int64 * n_hops)(*[int(k) for k in fanouts])
     offset = _rng["calls"] + 1
     _rng["calls"] += n_hops
-    check(lib.shmt_sample_minibatch(_ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr),
-                                    _ptr(gpu_indices), hashmap._handle if hashmap is not None else None,
-                                    _ptr(seeds), seeds.numel(), fan, n_hops, int(bool(replace)),
-                                    _rng["seed"], offset, arr(p_ptr), arr(i_ptr[:n_hops]),
-                                    arr(i_ptr[n_hops:2 * n_hops]), arr(i_ptr[2 * n_hops:]), sizes,
-                                    _stream(dev)))
-    hops = []
+    check(lib.shmt_sample_minibatch(
+        _ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr), _ptr(gpu_indices),
+        hashmap._handle if hashmap is not None else None, _ptr(seeds), seeds.numel(), fan, n_hops,
+        int(bool(replace)), _rng["seed"], offset,
+        VP(*[p_base + p_off[h] * p_item for h in range(n_hops)]),
+        VP(*[i_base + i_off[h] * i_item for h in range(n_hops)]),
+        VP(*[i_base + i_off[n_hops + h] * i_item for h in range(n_hops)]),
+        VP(*[i_base + i_off[2 * n_hops + h] * i_item for h in range(n_hops)]), sizes, _stream(dev)))
+    # one split per pool gives every exact-size view: per piece (skip, take, rest)
+    cuts_p, cuts_i = [], [0] * (9 * n_hops)
     for h in range(n_hops):
         n_in, nnz, n_out = sizes[3 * h], sizes[3 * h + 1], sizes[3 * h + 2]
-        x, r, f = i_off[h], i_off[n_hops + h] + n_in, i_off[2 * n_hops + h]
-        hops.append((p_pool[p_off[h]:p_off[h] + n_in + 1], i_pool[x:x + nnz], i_pool[r:r + nnz],
-                     i_pool[f:f + n_out]))
+        room = p_off[h + 1] - p_off[h]
+        cuts_p += [n_in + 1, room - n_in - 1]
+        for piece, skip, take in ((h, 0, nnz), (n_hops + h, n_in, nnz), (2 * n_hops + h, 0, n_out)):
+            room = i_off[piece + 1] - i_off[piece]
+            cuts_i[3 * piece:3 * piece + 3] = [skip, take, room - skip - take]
+    pv = p_pool.split_with_sizes(cuts_p)
+    iv = i_pool.split_with_sizes(cuts_i)
+    hops = [(pv[2 * h], iv[3 * h + 1], iv[3 * (n_hops + h) + 1], iv[3 * (2 * n_hops + h) + 1])
+            for h in range(n_hops)]
     return hops[-1][3], hops
 
 

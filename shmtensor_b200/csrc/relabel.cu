@@ -40,31 +40,11 @@ relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* sta
   resolve_sizes(ps, &numel);
   // The table is provisioned for the largest input the caller allows; hash into only as
   // much of it as this input needs (load <= 0.5), so a small input stays in a small,
-  // cache-resident part.  Only this kernel hashes; the others follow the recorded slots.
-  uint32_t mask = t.mask;
-  if (numel > 0) {
-    const uint32_t want = numel * 2 <= 64 ? 63u : (0xFFFFFFFFu >> __clz((uint32_t)(numel * 2 - 1)));
-    if (want < mask) mask = want;
-  }
-  t.mask = mask;
+  // cache-resident part.  Only the inserting code hashes; the rest follows recorded slots.
+  const uint32_t mask = relabel_mask_for(numel, t.mask);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
-    const long long key = part_elem(ps, i);
-    uint32_t pos = (uint32_t)mix64((uint64_t)key) & t.mask;
-    uint32_t steps = 0;
-    while (true) {
-      long long cur = __ldcg(t.keys + pos);
-      if (cur == kEmptyKey)
-        cur = (long long)atomicCAS(reinterpret_cast<unsigned long long*>(t.keys + pos),
-                                   (unsigned long long)kEmptyKey, (unsigned long long)key);
-      if (cur == kEmptyKey || cur == key) break;
-      pos = (pos + 1) & t.mask;
-      if (++steps > t.mask) {  // cannot happen at load <= 0.5; bounded all the same
-        atomicMax(reinterpret_cast<unsigned long long*>(status), (unsigned long long)DEV_OVERFLOW);
-        break;
-      }
-    }
-    atomicMin(t.first + pos, (unsigned)i);
+    const uint32_t pos = relabel_insert_one(t.keys, t.first, mask, part_elem(ps, i), (unsigned)i, status);
     store_int(out, ps.is64, i, (int64_t)pos);
   }
 }
@@ -144,21 +124,27 @@ uint64_t relabel_capacity(int64_t numel_bound) {
   return cap;
 }
 
-int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
-                   void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
-                   int64_t* status, int64_t* result, cudaStream_t s) {
+int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t s) {
   const uint64_t cap = relabel_capacity(numel_bound);
   if (int rc = ctx_reserve_table(ctx, cap * 12, s)) return rc;
+  t->keys = reinterpret_cast<long long*>(ctx->table);
+  t->first = reinterpret_cast<unsigned*>(ctx->table + cap * 8);
+  t->newid = nullptr;
+  t->mask = (uint32_t)(cap - 1);
+  return SHMT_OK;
+}
+
+int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
+                   void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
+                   int64_t* status, int64_t* result, cudaStream_t s, bool inserted) {
   RelTable t;
-  t.keys = reinterpret_cast<long long*>(ctx->table);
-  t.first = reinterpret_cast<unsigned*>(ctx->table + cap * 8);
+  if (int rc = relabel_table(ctx, numel_bound, &t, s)) return rc;
   t.newid = newid;
-  t.mask = (uint32_t)(cap - 1);
   const int64_t n_tiles = (numel_bound + kRelTile - 1) / kRelTile;
   int64_t blocks = (numel_bound + kRelThreads - 1) / kRelThreads;
   const int64_t cap_blocks = (int64_t)sm_count() * 16;
   const unsigned grid = (unsigned)(blocks < cap_blocks ? blocks : cap_blocks);
-  relabel_insert_kernel<<<grid, kRelThreads, 0, s>>>(ps, t, out_relabel, status);
+  if (!inserted) relabel_insert_kernel<<<grid, kRelThreads, 0, s>>>(ps, t, out_relabel, status);
   relabel_compact_kernel<<<(unsigned)n_tiles, kRelThreads, 0, s>>>(ps, t, out_relabel, out_unique,
                                                                    st, ticket, status, result);
   relabel_remap_kernel<<<grid, kRelThreads, 0, s>>>(ps, t, out_relabel);

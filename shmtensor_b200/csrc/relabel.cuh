@@ -30,14 +30,51 @@ struct RelTable {
   uint32_t mask;    // cap - 1
 };
 
+#ifdef __CUDACC__
+// Hash mask for an input of at most `numel` ids: load <= 0.5, never beyond the table.
+__device__ __forceinline__ uint32_t relabel_mask_for(int64_t numel, uint32_t table_mask) {
+  if (numel <= 0) return table_mask < 63u ? table_mask : 63u;
+  const uint32_t want = numel * 2 <= 64 ? 63u : (0xFFFFFFFFu >> __clz((uint32_t)(numel * 2 - 1)));
+  return want < table_mask ? want : table_mask;
+}
+
+// Claim (or find) the slot of `key`, record `i` as a candidate first occurrence, and return
+// the slot.  Linear probing from mix64(key) & mask; bounded by the table size.
+__device__ __forceinline__ uint32_t relabel_insert_one(long long* keys, unsigned* first,
+                                                       uint32_t mask, long long key, unsigned i,
+                                                       int64_t* status) {
+  uint32_t pos = (uint32_t)mix64((uint64_t)key) & mask;
+  uint32_t steps = 0;
+  while (true) {
+    long long cur = __ldcg(keys + pos);
+    if (cur == kEmptyKey)
+      cur = (long long)atomicCAS(reinterpret_cast<unsigned long long*>(keys + pos),
+                                 (unsigned long long)kEmptyKey, (unsigned long long)key);
+    if (cur == kEmptyKey || cur == key) break;
+    pos = (pos + 1) & mask;
+    if (++steps > mask) {  // cannot happen at load <= 0.5; bounded all the same
+      atomicMax(reinterpret_cast<unsigned long long*>(status), (unsigned long long)DEV_OVERFLOW);
+      break;
+    }
+  }
+  atomicMin(first + pos, i);
+  return pos;
+}
+#endif
+
 // Slots of the table that serves up to `numel_bound` ids.
 uint64_t relabel_capacity(int64_t numel_bound);
 
 // Queue the three relabel kernels.  `numel_bound` >= the real element count sizes the
 // table and the grids; `newid` is scratch of 4 * relabel_capacity(numel_bound) bytes;
 // ticket/status/result are zeroed device words.
+// `inserted`: the slots were already claimed and recorded in out_relabel by the producer
+// of the ids (the fused sampling kernel), so only the compact and remap kernels run.
 int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
                    void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
-                   int64_t* status, int64_t* result, cudaStream_t s);
+                   int64_t* status, int64_t* result, cudaStream_t s, bool inserted = false);
+
+// Keys / first-index arrays of the context's table for `numel_bound` ids (reserving it).
+int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t s);
 
 }  // namespace shmt

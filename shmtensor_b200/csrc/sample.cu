@@ -48,6 +48,14 @@ struct HopJob {
   int64_t* result;        // receives nnz
   const int64_t* n_dev;   // if set, the seed count is read here (it was produced on the device)
   int seeds_per_tile;
+  // Fused relabel insert (multi-hop path): the kernel also claims a relabel-table slot for
+  // every seed and every sampled neighbour, at its index in [seeds | neighbours], and
+  // records the slot in rel_out -- the work of relabel's first kernel, done while this
+  // kernel would otherwise wait on memory.  rel_keys == nullptr: off.
+  long long* rel_keys;
+  unsigned* rel_first;
+  uint32_t rel_mask;
+  void* rel_out;
 };
 
 // indptr[i] and indptr[i+1] with one load when the pair is naturally aligned (one request on
@@ -208,8 +216,19 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
     __syncthreads();
   }
   const int64_t prefix = s_prefix;
-  for (int j = (int)tid; j < rows; j += kHopThreads)
+  const bool relabel = job.rel_keys != nullptr;
+  // ids are hashed into as much of the table as n seeds with k picks each can need
+  const uint32_t rel_mask = relabel ? relabel_mask_for(n * (1 + k), job.rel_mask) : 0u;
+  for (int j = (int)tid; j < rows; j += kHopThreads) {
     store_int(job.sub_indptr, job.indptr64, first + j, prefix + s_off[j]);
+    if (relabel) {
+      const int64_t i = first + j;
+      const uint32_t pos = relabel_insert_one(job.rel_keys, job.rel_first, rel_mask,
+                                              load_int(job.seeds, job.seeds64, i), (unsigned)i,
+                                              job.status);
+      store_int(job.rel_out, sizeof(IxT) == 8, i, (int64_t)pos);
+    }
+  }
   if (tile == n_tiles - 1 && tid == 0) {
     store_int(job.sub_indptr, job.indptr64, n, prefix + s_total);
     *job.result = prefix + s_total;
@@ -220,7 +239,15 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int j = u * kGroups + group;
-      if (src[u]) out_all[prefix + s_off[j] + gl] = v[u];
+      if (src[u]) {
+        const int64_t o = prefix + s_off[j] + gl;
+        out_all[o] = v[u];
+        if (relabel) {
+          const uint32_t pos = relabel_insert_one(job.rel_keys, job.rel_first, rel_mask,
+                                                  (long long)v[u], (unsigned)(n + o), job.status);
+          store_int(job.rel_out, sizeof(IxT) == 8, n + o, (int64_t)pos);
+        }
+      }
     }
     return;
   }
@@ -462,6 +489,10 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
   SHMT_CUDA_TRY(cudaMemsetAsync(base, 0, zero_bytes, s));  // words, tickets and every tile flag
   int64_t* status = words + n_hops * 8;
 
+  {  // the relabel table for the largest hop, reserved before anything is queued
+    RelTable biggest;
+    if (int rc = relabel_table(ctx, cap[n_hops], &biggest, s)) return rc;
+  }
   const void* cur_seeds = seeds;
   for (int h = 0; h < n_hops; ++h) {
     int64_t* w = words + h * 8;  // [0] hop ticket, [1] nnz, [2] relabel ticket, [3] n_unique
@@ -488,6 +519,15 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     job.ticket = w + 0;
     job.status = status;
     job.result = w + 1;
+    const bool fuse_insert = fanouts[h] <= 32;  // the k > 32 sampler keeps relabel's own kernel
+    if (fuse_insert) {
+      RelTable t;
+      if (int rc = relabel_table(ctx, cap[h + 1], &t, s)) return rc;
+      job.rel_keys = t.keys;
+      job.rel_first = t.first;
+      job.rel_mask = t.mask;
+      job.rel_out = out_relabel[h];
+    }
     if (indices_dtype == SHMT_I64)
       launch_hop<long long>(job, hop_tiles[h], s);
     else
@@ -504,7 +544,7 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     ps.dev_n1 = w + 1;
     if (int rc = launch_relabel(ctx, ps, cap[h + 1], newid, out_frontier[h], out_relabel[h],
                                 carve_tile_states(base + off_rel[h], rel_tiles[h]), w + 2, status,
-                                w + 3, s))
+                                w + 3, s, fuse_insert))
       return rc;
     cur_seeds = out_frontier[h];
   }
