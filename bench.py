@@ -658,9 +658,116 @@ def run_sampling(args) -> None:
     capi.unpin_memory(indices)
 
 
+# --------------------------------------------------------------------------- update workload
+U_KEYS, U_DIM, U_LOOKUPS = 4_000_000, 256, 1_000_000
+UPDATE_WORKLOAD = ("cache update path: fused insert/overwrite of 4,000,000 unique int64 keys (uniform over 2^40) with "
+                   "256-d bfloat16 rows into an empty 1-GPU cache at load factor 0.5, then 1,000,000 lookups, "
+                   "half present, half absent")
+
+
+def run_update(args) -> None:
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return
+    row_bytes = U_DIM * 2
+    line = {"metric": "inserted+looked-up keys/s", "unit": "keys/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int64 keys, int32 slots, bf16 rows (byte copy)", "data": "synthetic (seeded)",
+            "config": {"workload": UPDATE_WORKLOAD, "keys": U_KEYS, "row_bytes": row_bytes, "lookups": U_LOOKUPS}}
+    rng = np.random.default_rng(5)
+    keys_n = np.unique(rng.integers(0, 1 << 40, size=U_KEYS + 100_000))
+    keys_n = rng.permutation(keys_n)[:U_KEYS].astype(np.int64)
+    req_n = np.concatenate([keys_n[rng.integers(0, U_KEYS, size=U_LOOKUPS // 2)],
+                            rng.integers(1 << 40, 1 << 41, size=U_LOOKUPS // 2)]).astype(np.int64)
+    rng.shuffle(req_n)
+
+    if args.impl == "reference":
+        # CPU path: row write data[ids] = upd (example/test_cache_set.py:183-184) + an open-addressing
+        # map built and queried on all cores (the reference's map is GPU-only)
+        from oracle import build_oracle
+        lib = build_oracle.load_cpu()
+        rows = np.zeros((U_KEYS, row_bytes), np.uint8)
+        rows[:] = np.arange(row_bytes, dtype=np.uint8)
+        table_rows = np.empty_like(rows)
+        slots = np.arange(U_KEYS, dtype=np.int64)
+        cap = 1 << 23
+        table = np.empty(2 * cap, np.int64)
+        out = np.empty(U_LOOKUPS, np.int32)
+        def step():
+            lib.oracle_map_build_query(keys_n.ctypes.data, U_KEYS, table.ctypes.data, cap, req_n.ctypes.data,
+                                       U_LOOKUPS, out.ctypes.data)
+            lib.oracle_scatter(table_rows.ctypes.data, slots.ctypes.data, U_KEYS, row_bytes, rows.ctypes.data)
+        for _ in range(max(args.warmup, 1)):
+            step()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step()
+        dt = (time.perf_counter() - t0) / args.steps
+        v = (U_KEYS + U_LOOKUPS) / dt
+        line.update({"impl": "reference", "value": round(v, 1), "ms_per_step": round(dt * 1e3, 3),
+                     "cpu_baseline": {"value": round(v, 1), "unit": "keys/s", "cores": lib.oracle_num_threads(),
+                                      "kind": "port", "sample": f"{args.steps} full passes: threaded open-addressing "
+                                      "build + query and a threaded row scatter"},
+                     "e2e": {"value": round(v, 1), "unit": "keys/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        print(json.dumps(line), flush=True)
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    from shmtensor_b200 import capi
+    keys = torch.from_numpy(keys_n).to(dev)
+    req = torch.from_numpy(req_n).to(dev)
+    g = torch.Generator(device=dev).manual_seed(5)
+    rows = torch.randn(U_KEYS, U_DIM, generator=g, device=dev).to(torch.bfloat16)
+    slots = torch.arange(U_KEYS, dtype=torch.int32, device=dev)
+    gpu = torch.empty(U_KEYS, U_DIM, dtype=torch.bfloat16, device=dev)
+    stream = torch.cuda.current_stream()
+    peak, peak_src = measured_peaks()
+
+    def one_pass():
+        m = capi.CUCOStaticHashmap.empty(2 * U_KEYS, torch.int64, torch.int32, dev)
+        capi.cache_insert_set(gpu, keys, slots, rows, m)
+        return m, m.query(req)
+
+    for _ in range(max(args.warmup, 3)):
+        m, out = one_pass()
+    assert torch.equal(gpu.view(torch.int16), rows.view(torch.int16)) and m.size() == U_KEYS
+    assert int((out >= 0).sum().item()) == U_LOOKUPS // 2
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    t_ins = t_q = 0.0
+    torch.cuda.synchronize()
+    for _ in range(args.steps):
+        m = capi.CUCOStaticHashmap.empty(2 * U_KEYS, torch.int64, torch.int32, dev)
+        ev[0].record(stream)
+        capi.cache_insert_set(gpu, keys, slots, rows, m)
+        ev[1].record(stream)
+        out = m.query(req)
+        ev[2].record(stream)
+        torch.cuda.synchronize()
+        t_ins += ev[0].elapsed_time(ev[1])
+        t_q += ev[1].elapsed_time(ev[2])
+    t_ins /= args.steps
+    t_q /= args.steps
+    # algorithmic bytes: insert+set per key 8 (key) + 4 (slot) + 16 (claim) + row read + row written;
+    # lookup per key 8 + 12 + 4
+    b_ins = U_KEYS * (8 + 4 + 16 + 2 * row_bytes)
+    b_q = U_LOOKUPS * (8 + 12 + 4)
+    line.update({"value": round((U_KEYS + U_LOOKUPS) / ((t_ins + t_q) * 1e-3), 1), "ms_per_step": round(t_ins + t_q, 4),
+                 "insert_set": {"ms": round(t_ins, 4), "keys_per_s": round(U_KEYS / (t_ins * 1e-3), 1),
+                                "roofline": {"bound": "hbm", "achieved": round(b_ins / (t_ins * 1e6), 1), "peak": peak,
+                                             "unit": "GB/s", "frac": round(b_ins / (t_ins * 1e6) / peak, 4),
+                                             "peak_source": peak_src}},
+                 "lookup": {"ms": round(t_q, 4), "keys_per_s": round(U_LOOKUPS / (t_q * 1e-3), 1),
+                            "roofline": {"bound": "hbm", "achieved": round(b_q / (t_q * 1e6), 1), "peak": peak,
+                                         "unit": "GB/s", "frac": round(b_q / (t_q * 1e6) / peak, 4)}},
+                 "gpu_launches": args.steps * 2})
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="fetch", choices=["fetch", "sampling"],
+    ap.add_argument("--workload", default="fetch", choices=["fetch", "sampling", "update"],
                     help="fetch: the headline cached feature fetch; sampling: cached 3-hop sampling + relabel")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
@@ -669,6 +776,8 @@ def main() -> None:
     args = ap.parse_args()
     if args.workload == "sampling":
         run_sampling(args)
+    elif args.workload == "update":
+        run_update(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

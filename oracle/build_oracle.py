@@ -35,6 +35,10 @@ def load_cpu() -> C.CDLL:
     lib.oracle_gather.argtypes = [vp, vp, i64, i64, vp]
     lib.oracle_sample_hop.restype = i64
     lib.oracle_sample_hop.argtypes = [vp, vp, i, vp, i64, i64, i, u64, vp, vp]
+    lib.oracle_map_build_query.restype = i64
+    lib.oracle_map_build_query.argtypes = [vp, i64, vp, i64, vp, i64, vp]
+    lib.oracle_scatter.restype = None
+    lib.oracle_scatter.argtypes = [vp, vp, i64, i64, vp]
     lib.oracle_relabel.restype = i64
     lib.oracle_relabel.argtypes = [vp, i64, vp, vp]
     return lib

@@ -94,6 +94,54 @@ int64_t oracle_sample_hop(const int64_t* indptr, const void* indices, int indice
   return sub_indptr[n];
 }
 
+// Open-addressing build + lookup of int64 keys -> int32 slots on all cores: the CPU stand-in
+// for the map half of the update path (cuco insert / find, include/cuco_hashmap.cuh:66-87).
+// table: 2 * cap int64 words, {key, value} pairs, cap a power of two.  Returns hits.
+int64_t oracle_map_build_query(const int64_t* keys, int64_t n, int64_t* table, int64_t cap,
+                               const int64_t* req, int64_t n_req, int32_t* out) {
+  const uint64_t mask = (uint64_t)cap - 1;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < 2 * cap; ++i) table[i] = -1;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    uint64_t pos = mix((uint64_t)keys[i]) & mask;
+    while (true) {
+      int64_t expected = -1;
+      if (__atomic_compare_exchange_n(&table[2 * pos], &expected, keys[i], false, __ATOMIC_RELAXED,
+                                      __ATOMIC_RELAXED) ||
+          expected == keys[i]) {
+        table[2 * pos + 1] = i;
+        break;
+      }
+      pos = (pos + 1) & mask;
+    }
+  }
+  int64_t hits = 0;
+#pragma omp parallel for schedule(static) reduction(+ : hits)
+  for (int64_t i = 0; i < n_req; ++i) {
+    uint64_t pos = mix((uint64_t)req[i]) & mask;
+    int32_t v = -1;
+    while (table[2 * pos] != -1) {
+      if (table[2 * pos] == req[i]) {
+        v = (int32_t)table[2 * pos + 1];
+        break;
+      }
+      pos = (pos + 1) & mask;
+    }
+    out[i] = v;
+    hits += v >= 0;
+  }
+  return hits;
+}
+
+// out[idx[i]] = rows[i]: the row-write half of the update path (data[ids] = upd,
+// example/test_cache_set.py:183-184).
+void oracle_scatter(char* table, const int64_t* idx, int64_t n, int64_t row_bytes, const char* rows) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i)
+    memcpy(table + idx[i] * row_bytes, rows + i * row_bytes, (size_t)row_bytes);
+}
+
 // First-occurrence unique + remap of int64 ids (ids != -1).  Returns n_unique.
 int64_t oracle_relabel(const int64_t* in, int64_t n, int64_t* unique, int64_t* relabel) {
   if (n == 0) return 0;
