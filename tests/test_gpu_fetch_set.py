@@ -251,3 +251,31 @@ def test_config2_full_size_equals_index_select(capi):
         assert torch.equal(out.cpu().view(torch.int32), want.view(torch.int32))
     finally:
         capi.unpin_memory(data)
+
+
+def test_config1_gather_from_shared_memory_tensor(capi):
+    """1,000,000 x 128 float32 table in POSIX shared memory (registered with CUDA), 200,000 int64
+    ids drawn Zipf(1.0), duplicates allowed: the gathered [200000, 128] tensor is bit-exact with
+    torch.index_select on the shared tensor."""
+    import uuid
+    name = f"shmt_test_{uuid.uuid4().hex[:8]}"
+    rows, dim, nq = 1_000_000, 128, 200_000
+    ptr, fd = capi.create_shared_mem(name, rows * dim * 4, pin_memory=True)
+    try:
+        table = capi.open_shared_tensor(ptr, torch.float32, (rows, dim))
+        g = torch.Generator().manual_seed(1)
+        for lo in range(0, rows, 250_000):
+            table[lo:lo + 250_000].normal_(generator=g)
+        rng = np.random.default_rng(1)
+        w = 1.0 / np.arange(1, rows + 1, dtype=np.float64)
+        cdf = np.cumsum(w) / w.sum()
+        ranks = np.minimum(np.searchsorted(cdf, rng.random(nq)), rows - 1)
+        ids = torch.from_numpy(rng.permutation(rows)[ranks].astype(np.int64))
+        out = capi.uva_fetch(table, ids.cuda())
+        want = torch.index_select(table, 0, ids)
+        assert tuple(out.shape) == (nq, dim)
+        assert torch.equal(out.cpu().view(torch.int32), want.view(torch.int32))
+        del table, want
+    finally:
+        capi.release_shared_mem(name, rows * dim * 4, ptr, fd, pin_memory=True)
+    assert not capi.file_exist(name)
