@@ -46,6 +46,10 @@ typedef struct shmt_ctx shmt_ctx;
 int shmt_ctx_create(int device, shmt_ctx** out);
 int shmt_ctx_destroy(shmt_ctx* ctx);
 int64_t shmt_ctx_scratch_bytes(const shmt_ctx* ctx);
+/* Wait for `stream` and report what the last asynchronous op on this context (a scan,
+ * or a hop / relabel called without a host result pointer) left in its status word:
+ * SHMT_OK, SHMT_ERR_TIMEOUT or SHMT_ERR_CAPACITY.  No counterpart in the reference.  */
+int shmt_ctx_check(shmt_ctx* ctx, void* stream);
 
 /* ---- static hashmap --------------------------------------------------------
  * Open addressing, linear probing over 16-byte {int64 key, int64 value} slots,

@@ -287,6 +287,13 @@ def _fetch(uva_data, gpu_data, indices, hashmap, mask, who):
     return out
 
 
+def check_async(device="cuda") -> None:
+    """Extension: wait for the current stream and raise if the last asynchronous call on this
+    device's context (``thrust_scan`` / ``exclusive_scan_``) ended with a device-side error."""
+    device = torch.device(device)
+    check(lib.shmt_ctx_check(_ctx(device), _stream(device)))
+
+
 def device_fault() -> int:
     """Extension: code left by a kernel whose bounded wait ran out (0 = none); synchronises."""
     code = C.c_int(0)

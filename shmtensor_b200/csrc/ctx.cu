@@ -28,6 +28,16 @@ int sm_count() {
   return cached[dev];
 }
 
+int device_of_pointer(const void* p) {
+  int cur = 0;
+  cudaGetDevice(&cur);
+  cudaPointerAttributes a;
+  if (p && cudaPointerGetAttributes(&a, p) == cudaSuccess && a.type == cudaMemoryTypeDevice)
+    return a.device;
+  cudaGetLastError();  // a failed query must not poison the next launch check
+  return cur;
+}
+
 int ctx_reserve(shmt_ctx* ctx, size_t bytes) {
   bytes += 256;  // result words live in front of the region
   if (bytes <= ctx->scratch_bytes) return SHMT_OK;
@@ -128,6 +138,12 @@ int shmt_ctx_destroy(shmt_ctx* ctx) {
   if (ctx->h_words) cudaFreeHost(ctx->h_words);
   delete ctx;
   return SHMT_OK;
+}
+
+int shmt_ctx_check(shmt_ctx* ctx, void* stream) {
+  SHMT_REQUIRE(ctx != nullptr, "shmt_ctx_check: ctx is null");
+  DeviceGuard guard(ctx->device);
+  return ctx_fetch_words(ctx, static_cast<cudaStream_t>(stream), "shmt_ctx_check");
 }
 
 int64_t shmt_ctx_scratch_bytes(const shmt_ctx* ctx) {

@@ -32,6 +32,9 @@ int ctx_reserve_table(shmt_ctx* ctx, size_t bytes, cudaStream_t stream);
 // Returns SHMT_ERR_TIMEOUT / SHMT_ERR_CAPACITY if the kernel flagged either.
 int ctx_fetch_words(shmt_ctx* ctx, cudaStream_t stream, const char* what);
 
+// Device that owns a device pointer (the current device if the runtime cannot tell).
+int device_of_pointer(const void* p);
+
 // RAII device guard for entry points that are handed a context or a map.
 struct DeviceGuard {
   int prev = -1;

@@ -450,6 +450,7 @@ int shmt_fetch(const shmt_map* map, const void* mask, int mask_dtype, const void
   if (int rc = check_common("shmt_fetch", idx, idx_dtype, n, row_bytes)) return rc;
   if (n == 0) return SHMT_OK;
   SHMT_REQUIRE(out != nullptr, "shmt_fetch: out is null");
+  DeviceGuard guard(map ? map->device : device_of_pointer(out));
   RowJob job{};
   if (int rc = fill_mode("shmt_fetch", job, map, mask, mask_dtype)) return rc;
   SHMT_REQUIRE(job.mode == MODE_HOST ? host_base != nullptr : (gpu_base || host_base),
@@ -477,6 +478,7 @@ int shmt_fetch_partitioned(const shmt_map* map, const void* const* bases, int n_
   SHMT_REQUIRE(owner_shift >= 1 && owner_shift <= 62, "shmt_fetch_partitioned: owner_shift 1..62");
   if (n == 0) return SHMT_OK;
   SHMT_REQUIRE(out != nullptr, "shmt_fetch_partitioned: out is null");
+  DeviceGuard guard(map->device);
   RowJob job{};
   job.map = view_of(map);
   job.mode = MODE_MAP;
@@ -506,6 +508,7 @@ int shmt_set(const shmt_map* map, const void* mask, int mask_dtype, void* host_b
   if (int rc = check_common("shmt_set", idx, idx_dtype, n, row_bytes)) return rc;
   if (n == 0) return SHMT_OK;
   SHMT_REQUIRE(update != nullptr, "shmt_set: update is null");
+  DeviceGuard guard(map ? map->device : device_of_pointer(update));
   RowJob job{};
   if (int rc = fill_mode("shmt_set", job, map, mask, mask_dtype)) return rc;
   SHMT_REQUIRE(job.mode == MODE_HOST ? host_base != nullptr : (gpu_base || host_base),

@@ -279,3 +279,8 @@ def test_config1_gather_from_shared_memory_tensor(capi):
     finally:
         capi.release_shared_mem(name, rows * dim * 4, ptr, fd, pin_memory=True)
     assert not capi.file_exist(name)
+
+
+def test_no_bounded_wait_ran_out(capi):
+    """Every fetch above went through the bulk-copy kernel; none of its bounded waits gave up."""
+    assert capi.device_fault() == 0

@@ -23,6 +23,7 @@ def test_scan_matches_cumsum(capi, n, dtype):
     inc, exc = a.clone(), a.clone()
     capi.thrust_scan(inc)
     capi.exclusive_scan_(exc)
+    capi.check_async()          # the look-back's bounded waits all completed
     want = oracle.scan_inclusive(a.cpu().numpy())
     assert np.array_equal(inc.cpu().numpy(), want)
     assert np.array_equal(exc.cpu().numpy(), oracle.scan_exclusive(a.cpu().numpy()))
