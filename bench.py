@@ -347,6 +347,43 @@ def run_ours(args) -> None:
         "clocks": clocks,
     }
 
+    # ---- N > 1: the NVLink regime -- ids all cached, (N-1)/N of the rows on a peer GPU
+    if world > 1:
+        from shmtensor_b200._lib import check, lib
+        from shmtensor_b200.partition import _DeviceBuffer, share_device_buffer
+        probe = _DeviceBuffer(256 << 20)
+        ptrs, opened = share_device_buffer(probe)
+        sink = torch.zeros(1, dtype=torch.int64, device=dev)
+        peer = ptrs[(rank + 1) % world]
+        peer_ms = min(time_launches(lambda: check(lib.shmt_stream_read(peer, 256 << 20, sink.data_ptr(),
+                                                                        stream.cuda_stream)), 1, stream)
+                      for _ in range(5))
+        gen = torch.Generator().manual_seed(1000 + rank)
+        hot_batches = [cached_ids[torch.randint(0, n_cached, (BATCH,), generator=gen)].to(dev) for _ in range(4)]
+        for b in hot_batches[:2]:
+            fetch(b)
+        dist.barrier()
+        ms_hit = time_launches(lambda c=[0]: (fetch(hot_batches[c[0] % 4]), c.__setitem__(0, c[0] + 1)), 40, stream)
+        t = torch.tensor([ms_hit, peer_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_hit, peer_ms = t.tolist()
+        peer_gbs = (256 << 20) / (peer_ms * 1e6)
+        remote_bytes = BATCH * ROW_BYTES * (world - 1) / world
+        line["roofline_all_hit_partitioned"] = {
+            "bound": "nvlink", "kernel_ms": round(ms_hit, 5),
+            "aggregate_gbs": round(world * BATCH * ROW_BYTES / (ms_hit * 1e6), 1),
+            "achieved": round(remote_bytes / (ms_hit * 1e6), 1), "peak": round(peer_gbs, 1), "unit": "GB/s",
+            "frac": round(remote_bytes / (ms_hit * 1e6) / peer_gbs, 4),
+            "peak_source": "streaming read kernel over the next rank's IPC-mapped buffer, measured in this run",
+            "what": "ids uniform over the cached set: 1/N of the rows local, the rest read from peers over NVLink; "
+                    "achieved = remote row bytes per rank / slowest rank's kernel time"}
+        torch.cuda.synchronize()
+        dist.barrier()
+        for p_ in opened:
+            lib.shmt_ipc_close_handle(p_)
+        dist.barrier()
+        lib.shmt_dev_free(probe.ptr)
+
     # ---- rank 0, one GPU: roofline of the fetch kernel and the CPU baseline beside it
     if rank == 0 and world == 1:
         peak, peak_src = measured_peaks()
@@ -395,6 +432,29 @@ def run_ours(args) -> None:
                                      "frac": round(BATCH * ROW_BYTES / (ms_miss * 1e6) / link["peak_gbs"], 4),
                                      "kernel_ms": round(ms_miss, 5),
                                      "ids": "uniform over the 1,920,000 uncached rows, probed and missed"}
+        # the reference's own fetch kernel on the same GPU and batches, when oracle/_ref was built
+        try:
+            from oracle import build_ref
+            ref = build_ref.load_reference()
+        except Exception as exc:  # noqa: BLE001
+            ref = None
+            line["reference_cuda"] = {"unavailable": f"reference build not loadable: {exc}"}
+        if ref is not None:
+            rmap = ref.CUCOStaticHashmap(cached_ids.to(dev), torch.arange(n_cached, dtype=torch.int32, device=dev),
+                                         LOAD_FACTOR)
+            def ref_ms(bs, n):
+                for b in bs[:2]:
+                    ref.cache_fetch(table, gpu_rows, b, rmap)
+                return time_launches(lambda c=[0]: (ref.cache_fetch(table, gpu_rows, bs[c[0] % len(bs)], rmap),
+                                                    c.__setitem__(0, c[0] + 1)), n, stream)
+            r_mixed, r_hit, r_miss = ref_ms(batches, 20), ref_ms(hot_batches, 20), ref_ms(cold_batches, 5)
+            line["reference_cuda"] = {
+                "what": "the reference's MultiDimCacheFetchKernel (src/cache_feature_fetch.cu:106-129), compiled "
+                        "unmodified, over a stand-in for its cuCollections map; same table, cache and batches",
+                "mixed_ms": round(r_mixed, 5), "mixed_gbs": round(BATCH * ROW_BYTES / (r_mixed * 1e6), 2),
+                "all_hit_ms": round(r_hit, 5), "all_hit_gbs": round(alg_hit / (r_hit * 1e6), 1),
+                "all_miss_ms": round(r_miss, 5), "all_miss_gbs": round(BATCH * ROW_BYTES / (r_miss * 1e6), 2)}
+            del rmap
         # CPU baseline: the reference's cpu_fetch line on this box's cores, bounded sample
         from oracle import oracle
         n_cpu = 20

@@ -3,8 +3,8 @@
 The reference is single-GPU; this is the multi-GPU form of its cached fetch.  Each of the
 ``world`` ranks (one process per GPU) keeps the rows of the cached ids it owns in one device
 buffer.  Every rank holds the whole directory — a static hashmap id -> (owner << 40 | slot)
-— so a probe never leaves local HBM; only row payloads cross NVLink, read by plain 16-byte
-loads inside the same fused gather kernel that serves local hits and host misses
+— so a probe never leaves local HBM; only row payloads cross NVLink, read by the same
+per-row bulk copies, inside the same fused gather kernel, that serve local hits and host misses
 (``shmt_fetch_partitioned``).  Peer buffers are mapped with CUDA IPC, handles exchanged through
 ``torch.distributed``.  There is no collective on the data path.
 """
@@ -62,6 +62,28 @@ class _DeviceBuffer:
         return flat.view(dtype).reshape(shape)
 
 
+def share_device_buffer(buf: "_DeviceBuffer", group=None):
+    """Map every rank's buffer into every other rank (CUDA IPC).  Returns ``(ptrs, opened)``:
+    ``ptrs[r]`` is rank r's buffer as seen from this process, ``opened`` the mappings to close
+    with ``shmt_ipc_close_handle`` (on every rank, with nothing in flight, before any free)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    handle = (C.c_char * 64)()
+    check(lib.shmt_ipc_get_handle(buf.ptr, handle))
+    handles: List[bytes] = [b""] * world
+    dist.all_gather_object(handles, bytes(handle.raw), group=group)
+    ptrs, opened = [0] * world, []
+    ptrs[rank] = buf.ptr
+    for r, h in enumerate(handles):
+        if r == rank:
+            continue
+        out = C.c_void_p()
+        check(lib.shmt_ipc_open_handle(h, C.byref(out)))
+        ptrs[r] = out.value
+        opened.append(out.value)
+    dist.barrier(group)
+    return ptrs, opened
+
+
 class PartitionedFeatureCache:
     """``fetch(ids)`` returns ``host_table[ids]`` on this rank's GPU, bit-exact, reading each
     row from the local shard, a peer's shard over NVLink, or pinned host memory."""
@@ -89,22 +111,10 @@ class PartitionedFeatureCache:
         torch.cuda.synchronize()
 
         # peers' shards through CUDA IPC
-        self._peer_ptrs: List[int] = [0] * self.world
-        self._peer_ptrs[self.rank] = self._buf.ptr
+        self._peer_ptrs: List[int] = [self._buf.ptr]
         self._opened: List[int] = []
         if self.world > 1:
-            handle = (C.c_char * 64)()
-            check(lib.shmt_ipc_get_handle(self._buf.ptr, handle))
-            handles: List[bytes] = [b""] * self.world
-            dist.all_gather_object(handles, bytes(handle.raw), group=group)
-            for r, h in enumerate(handles):
-                if r == self.rank:
-                    continue
-                out = C.c_void_p()
-                check(lib.shmt_ipc_open_handle(h, C.byref(out)))
-                self._peer_ptrs[r] = out.value
-                self._opened.append(out.value)
-            dist.barrier(group)
+            self._peer_ptrs, self._opened = share_device_buffer(self._buf, group)
         self._bases = (C.c_void_p * self.world)(*self._peer_ptrs)
 
         # replicated directory: id -> owner << 40 | slot
