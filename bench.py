@@ -171,6 +171,28 @@ def measure_host_link(table: torch.Tensor, stream) -> dict:
             "peak_gbs": round(max(copy_gbs, read_gbs), 2)}
 
 
+_REAL_STDOUT = None
+
+
+def quiet_stdout() -> None:
+    """Send everything libraries print on stdout (NCCL's version banner, for one) to stderr;
+    stdout then carries nothing but the one JSON line written by emit()."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _REAL_STDOUT is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_REAL_STDOUT, data)
+
+
 def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
@@ -209,7 +231,7 @@ def run_reference(args) -> None:
         "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     assert out.shape == (BATCH, DIM)
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # --------------------------------------------------------------------------- our arm
@@ -480,7 +502,7 @@ def run_ours(args) -> None:
                       f"{os.cpu_count()} logical cores"}
 
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
 
     # ---- orderly teardown: nothing in flight, peers unmapped before any shard is freed
     torch.cuda.synchronize()
@@ -597,7 +619,7 @@ def run_sampling(args) -> None:
                                       "kind": "port", "sample": f"{args.steps} full 3-hop mini-batches; threaded C++ "
                                       "restatement of the reference's sampler (seeds split over threads) + serial relabel"},
                      "e2e": {"value": round(v, 1), "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
-        print(json.dumps(line), flush=True)
+        emit(line)
         return
 
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
@@ -721,7 +743,7 @@ def run_sampling(args) -> None:
                  "cpu_baseline": {"value": round(ce / cpu_dt, 1), "unit": "edges/s", "cores": lib.oracle_num_threads(),
                                   "kind": "port", "sample": "10 full 3-hop mini-batches; threaded C++ restatement of the "
                                   "reference's sampler + serial relabel (the reference has no CPU sampler)"}})
-    print(json.dumps(line), flush=True)
+    emit(line)
     capi.unpin_memory(indptr)
     capi.unpin_memory(indices)
 
@@ -777,7 +799,7 @@ def run_update(args) -> None:
                                       "kind": "port", "sample": f"{args.steps} full passes: threaded open-addressing "
                                       "build + query and a threaded row scatter"},
                      "e2e": {"value": round(v, 1), "unit": "keys/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
-        print(json.dumps(line), flush=True)
+        emit(line)
         return
 
     assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
@@ -830,7 +852,7 @@ def run_update(args) -> None:
                             "roofline": {"bound": "hbm", "achieved": round(b_q / (t_q * 1e6), 1), "peak": peak,
                                          "unit": "GB/s", "frac": round(b_q / (t_q * 1e6) / peak, 4)}},
                  "gpu_launches": args.steps * 2})
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def main() -> None:
@@ -842,6 +864,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
+    quiet_stdout()
     if args.workload == "sampling":
         run_sampling(args)
     elif args.workload == "update":
