@@ -748,6 +748,173 @@ def run_sampling(args) -> None:
     capi.unpin_memory(indices)
 
 
+# --------------------------------------------------------------------------- end-to-end mini-batch
+MB_DIM = 128
+MB_CACHE_FRACTION = 0.40
+MINIBATCH_WORKLOAD = ("end-to-end mini-batch over a partitioned cache, config 4 scaled 1:46 to fit a short run: power-law "
+                      "CSR 2,400,000 nodes / 62,000,000 edges, 128-d float32 features (1.2 GB) in pinned host memory; "
+                      "the top 40% of nodes by degree have their adjacency cached on every GPU and their features "
+                      "hash-partitioned over the GPUs; per GPU and step 1,024 seeds, fan-out [15,10,5], then the features "
+                      "of every sampled node are fetched (remote hits over NVLink, misses over UVA)")
+
+
+def run_minibatch(args) -> None:
+    rank, local_rank, world = dist_env()
+    indptr_n, indices_n, deg = make_graph()
+    rng = np.random.default_rng(100 + rank)
+    seed_batches = [rng.integers(0, G_NODES, size=N_SEEDS).astype(np.int32) for _ in range(32)]
+    line = {"metric": "mini-batches/s (sampled edges/s, fetched feature GB/s)", "unit": "mini-batches/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int32 ids, f32 rows (integer / byte work)",
+            "data": "synthetic (seeded)",
+            "config": {"workload": MINIBATCH_WORKLOAD, "nodes": G_NODES, "edges": int(indptr_n[-1]), "dim": MB_DIM,
+                       "fanout": FANOUT, "seeds_per_gpu": N_SEEDS}}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        from oracle import build_oracle, oracle
+        lib = build_oracle.load_cpu()
+        feats = torch.empty(G_NODES, MB_DIM)
+        fill_table(feats)
+        def cpu_step(seeds32):
+            seeds = seeds32.astype(np.int64)
+            edges = 0
+            for k in reversed(FANOUT):
+                sp = np.empty(seeds.size + 1, np.int64)
+                so = np.empty(seeds.size * k, np.int32)
+                nnz = lib.oracle_sample_hop(indptr_n.ctypes.data, indices_n.ctypes.data, 0, seeds.ctypes.data,
+                                            seeds.size, k, 0, 7777, sp.ctypes.data, so.ctypes.data)
+                cat = np.concatenate([seeds, so[:nnz].astype(np.int64)])
+                uniq, rel = np.empty(cat.size, np.int64), np.empty(cat.size, np.int64)
+                nu = lib.oracle_relabel(cat.ctypes.data, cat.size, uniq.ctypes.data, rel.ctypes.data)
+                seeds = uniq[:nu].copy()
+                edges += int(nnz)
+            out = oracle.cpu_fetch_reference(feats, torch.from_numpy(seeds))
+            return edges, out.shape[0]
+        for i in range(max(args.warmup, 1)):
+            cpu_step(seed_batches[i % 32])
+        t0 = time.perf_counter()
+        tot = [cpu_step(seed_batches[i % 32]) for i in range(args.steps)]
+        dt = (time.perf_counter() - t0) / args.steps
+        line.update({"impl": "reference", "value": round(1 / dt, 2), "ms_per_step": round(dt * 1e3, 3),
+                     "edges_per_s": round(sum(t[0] for t in tot) / args.steps / dt, 1),
+                     "fetched_gbs": round(sum(t[1] for t in tot) / args.steps * MB_DIM * 4 / dt / 1e9, 3),
+                     "cpu_baseline": {"value": round(1 / dt, 2), "unit": "mini-batches/s",
+                                      "cores": lib.oracle_num_threads(), "kind": "port",
+                                      "sample": f"{args.steps} full mini-batches: threaded C++ sampler + serial relabel "
+                                                "+ torch.index_select on the host feature table"},
+                     "e2e": {"value": round(1 / dt, 2), "unit": "mini-batches/s", "h2d_bytes_per_step": 0,
+                             "d2h_bytes_per_step": 0}})
+        emit(line)
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    import shmtensor_b200 as st
+    from shmtensor_b200 import capi
+    from shmtensor_b200.partition import PartitionedFeatureCache
+    stream = torch.cuda.current_stream()
+    if world > 1:
+        name = f"shmt_bench_mb_{os.environ.get('MASTER_PORT', '0')}"
+        if rank == 0 and capi.file_exist(name):
+            p, fd = capi.open_shared_mem(name, G_NODES * MB_DIM * 4)
+            capi.release_shared_mem(name, G_NODES * MB_DIM * 4, p, fd)
+        dist.barrier()
+        shm = st.ShmTensor(name, (G_NODES, MB_DIM), rank, world, None, torch.float32, pin_memory=True)
+        feats = shm.tensor_
+        if rank == 0:
+            fill_table(feats)
+        dist.barrier()
+    else:
+        shm = None
+        feats = torch.empty(G_NODES, MB_DIM)
+        fill_table(feats)
+        capi.pin_memory(feats)
+    indptr, indices = torch.from_numpy(indptr_n), torch.from_numpy(indices_n)
+    capi.pin_memory(indptr)
+    capi.pin_memory(indices)
+    n_cached = int(G_NODES * MB_CACHE_FRACTION)
+    hot_n = np.argsort(-deg, kind="stable")[:n_cached].copy()
+    hot = torch.from_numpy(hot_n).to(dev)
+    gp, gi = capi.create_subcsr(indptr, indices, hot)
+    gmap = capi.CUCOStaticHashmap(hot.int(), torch.arange(n_cached, dtype=torch.int32, device=dev), 0.8)
+    fcache = PartitionedFeatureCache(feats, torch.from_numpy(hot_n))
+    seeds_host = [torch.from_numpy(b).pin_memory() for b in seed_batches]
+    seeds_buf = torch.empty(N_SEEDS, dtype=torch.int32, device=dev)
+    tail = torch.empty(MB_DIM, dtype=torch.float32).pin_memory()
+    capi.set_sampling_seed(7777 + rank)
+
+    def step(i):
+        seeds_buf.copy_(seeds_host[i % 32], non_blocking=True)
+        frontier, hops = capi.sample_minibatch(indptr, indices, seeds_buf, list(reversed(FANOUT)), False, gp, gi, gmap)
+        rows = fcache.fetch(frontier)
+        return sum(h[1].numel() for h in hops), frontier, rows
+
+    # parity of one full step: the fetched rows are the host rows of the frontier, bit for bit
+    _, frontier, rows = step(0)
+    assert torch.equal(rows.cpu().view(torch.int32), feats[frontier.cpu().long()].view(torch.int32))
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sampler = ClockSampler(local_rank)
+    region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    region[0].record(stream)
+    edges = n_rows = 0
+    for i in range(args.steps):
+        e, frontier, rows = step(i)
+        tail.copy_(rows[-1], non_blocking=True)
+        edges += e
+        n_rows += rows.shape[0]
+    region[1].record(stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop()
+    ms = region[0].elapsed_time(region[1]) / args.steps
+    t = torch.tensor([ms, float(edges), float(n_rows)], device=dev, dtype=torch.float64)
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        ms, edges, n_rows = tmax[0].item(), t[1].item(), t[2].item()
+    else:
+        edges, n_rows = float(edges), float(n_rows)
+    hits = int((fcache.directory.query(frontier.long()) >= 0).sum().item())
+    v = world / (ms * 1e-3)
+    line.update({"value": round(v, 1), "ms_per_step": round(ms, 5),
+                 "edges_per_s": round(edges / args.steps / (ms * 1e-3), 1),
+                 "fetched_gbs": round(n_rows / args.steps * MB_DIM * 4 / (ms * 1e6), 2),
+                 "rows_fetched_per_gpu_step": round(n_rows / args.steps / world), "feature_hit_rate": round(hits / frontier.numel(), 4),
+                 "e2e": {"value": round(v, 1), "unit": "mini-batches/s", "h2d_bytes_per_step": N_SEEDS * 4,
+                         "d2h_bytes_per_step": MB_DIM * 4 + 9 * 8, "ms_per_step": round(ms, 5),
+                         "note": "the timed loop is already end to end: seeds from pinned host memory, sizes and the "
+                                 "last fetched row read back"},
+                 "gpu_launches": args.steps * 10, "clocks": clocks})
+    if rank == 0:
+        emit(line)
+    torch.cuda.synchronize()
+    fcache.close()
+    capi.unpin_memory(indptr)
+    capi.unpin_memory(indices)
+    if world == 1:
+        capi.unpin_memory(feats)
+    else:
+        dist.barrier()
+        del feats, fcache
+        shm = None
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # --------------------------------------------------------------------------- update workload
 U_KEYS, U_DIM, U_LOOKUPS = 4_000_000, 256, 1_000_000
 UPDATE_WORKLOAD = ("cache update path: fused insert/overwrite of 4,000,000 unique int64 keys (uniform over 2^40) with "
@@ -857,7 +1024,7 @@ def run_update(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="fetch", choices=["fetch", "sampling", "update"],
+    ap.add_argument("--workload", default="fetch", choices=["fetch", "sampling", "update", "minibatch"],
                     help="fetch: the headline cached feature fetch; sampling: cached 3-hop sampling + relabel")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
@@ -869,6 +1036,8 @@ def main() -> None:
         run_sampling(args)
     elif args.workload == "update":
         run_update(args)
+    elif args.workload == "minibatch":
+        run_minibatch(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
