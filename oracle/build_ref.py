@@ -1,7 +1,7 @@
 """Compile the reference's own sources into ``oracle/_ref/ShmTensorLib.so``.
 
-TEST AND BENCH INFRASTRUCTURE.  The sources are compiled where they lie (``/root/reference``,
-unmodified; nothing is copied into this repository) with nvcc for sm_100a, against this
+TEST AND BENCH INFRASTRUCTURE.  The sources are compiled where they lie (the read-only reference
+checkout named by ``REFERENCE`` below, unmodified; nothing is copied into this repository) with nvcc for sm_100a, against this
 image's torch headers and ``oracle/ref_shim`` — a stand-in for the one header the reference's
 build downloads (cuCollections, see ``oracle/ref_shim/cuco/static_map.cuh``).  The reference's
 own build system (CMake + CPM download) is not run.  Output goes only to ``oracle/_ref/``

@@ -39,6 +39,26 @@ int sm_count();
 // Device-side status word layout shared by every kernel that can give up.
 enum : int { DEV_OK = 0, DEV_OVERFLOW = 1, DEV_TIMEOUT = 2 };
 
+// Launch `kernel` allowing it to overlap its scheduling with the tail of the previous kernel
+// in `stream` (see pdl_prologue); plain launch when `pdl` is false.
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(bool pdl, void (*kernel)(KArgs...), unsigned grid, unsigned block,
+                                 size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+#endif
+
 // ---- device side -----------------------------------------------------------------
 #ifdef __CUDACC__
 
@@ -98,6 +118,16 @@ __device__ __forceinline__ void st_stream16(void* p, uint4 v) {
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
                "r"(v.z), "r"(v.w)
                : "memory");
+}
+
+// Programmatic dependent launch (sm_90+): a kernel that starts with pdl_prologue() lets the
+// next kernel of the stream be scheduled as soon as all of its own CTAs are resident, and
+// itself waits until the kernel before it has completed and flushed its writes.  Without the
+// launch attribute both instructions do nothing.  Hides the launch latency between the short
+// dependent kernels of a multi-hop mini-batch.
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
 // Philox4x32-10 (Salmon et al., SC'11): counter-based, so every (call, seed row,

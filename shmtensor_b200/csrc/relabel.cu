@@ -36,6 +36,7 @@ __device__ __forceinline__ int64_t part_elem(const Parts& ps, int64_t i) {
 
 __global__ void __launch_bounds__(kRelThreads)
 relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* status) {
+  pdl_prologue();
   int64_t numel;
   resolve_sizes(ps, &numel);
   // The table is provisioned for the largest input the caller allows; hash into only as
@@ -57,6 +58,7 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
   __shared__ int64_t s_total;
   __shared__ int64_t s_prefix;
   __shared__ int s_tile;
+  pdl_prologue();
   int64_t numel;
   resolve_sizes(ps, &numel);
   const int64_t n_tiles = (numel + kRelTile - 1) / kRelTile;
@@ -101,6 +103,7 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
 
 __global__ void __launch_bounds__(kRelThreads)
 relabel_remap_kernel(Parts ps, RelTable t, void* out) {
+  pdl_prologue();
   int64_t numel;
   resolve_sizes(ps, &numel);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -136,7 +139,7 @@ int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t 
 
 int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
                    void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
-                   int64_t* status, int64_t* result, cudaStream_t s, bool inserted) {
+                   int64_t* status, int64_t* result, cudaStream_t s, bool inserted, bool pdl) {
   RelTable t;
   if (int rc = relabel_table(ctx, numel_bound, &t, s)) return rc;
   t.newid = newid;
@@ -144,10 +147,11 @@ int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned
   int64_t blocks = (numel_bound + kRelThreads - 1) / kRelThreads;
   const int64_t cap_blocks = (int64_t)sm_count() * 16;
   const unsigned grid = (unsigned)(blocks < cap_blocks ? blocks : cap_blocks);
-  if (!inserted) relabel_insert_kernel<<<grid, kRelThreads, 0, s>>>(ps, t, out_relabel, status);
-  relabel_compact_kernel<<<(unsigned)n_tiles, kRelThreads, 0, s>>>(ps, t, out_relabel, out_unique,
-                                                                   st, ticket, status, result);
-  relabel_remap_kernel<<<grid, kRelThreads, 0, s>>>(ps, t, out_relabel);
+  if (!inserted)
+    SHMT_CUDA_TRY(launch_kernel(pdl, relabel_insert_kernel, grid, kRelThreads, 0, s, ps, t, out_relabel, status));
+  SHMT_CUDA_TRY(launch_kernel(pdl, relabel_compact_kernel, (unsigned)n_tiles, kRelThreads, 0, s, ps, t,
+                              (const void*)out_relabel, out_unique, st, ticket, status, result));
+  SHMT_CUDA_TRY(launch_kernel(pdl, relabel_remap_kernel, grid, kRelThreads, 0, s, ps, t, out_relabel));
   SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;
 }

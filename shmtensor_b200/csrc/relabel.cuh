@@ -68,11 +68,13 @@ uint64_t relabel_capacity(int64_t numel_bound);
 // Queue the three relabel kernels.  `numel_bound` >= the real element count sizes the
 // table and the grids; `newid` is scratch of 4 * relabel_capacity(numel_bound) bytes;
 // ticket/status/result are zeroed device words.
+// `pdl`: launch with programmatic stream serialization (see pdl_prologue in common.cuh).
 // `inserted`: the slots were already claimed and recorded in out_relabel by the producer
 // of the ids (the fused sampling kernel), so only the compact and remap kernels run.
 int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
                    void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
-                   int64_t* status, int64_t* result, cudaStream_t s, bool inserted = false);
+                   int64_t* status, int64_t* result, cudaStream_t s, bool inserted = false,
+                   bool pdl = false);
 
 // Keys / first-index arrays of the context's table for `numel_bound` ids (reserving it).
 int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t s);

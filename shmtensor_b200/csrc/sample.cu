@@ -95,6 +95,7 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
   __shared__ int64_t s_prefix;
   __shared__ int s_tile;
 
+  pdl_prologue();
   const unsigned full = 0xffffffffu;
   const unsigned tid = threadIdx.x, lane = tid & 31;
   const int S = job.seeds_per_tile;
@@ -349,14 +350,14 @@ static int pick_seeds_per_tile(int64_t n, int64_t k) {
 }
 
 template <typename IxT>
-static void launch_hop(const HopJob& job, int64_t n_tiles, cudaStream_t s) {
+static void launch_hop(const HopJob& job, int64_t n_tiles, cudaStream_t s, bool pdl = false) {
   const unsigned grid = (unsigned)n_tiles;
   if (job.k <= 8)
-    sample_hop_kernel<IxT, 8><<<grid, kHopThreads, 0, s>>>(job);
+    launch_kernel(pdl, sample_hop_kernel<IxT, 8>, grid, kHopThreads, 0, s, job);
   else if (job.k <= 16)
-    sample_hop_kernel<IxT, 16><<<grid, kHopThreads, 0, s>>>(job);
+    launch_kernel(pdl, sample_hop_kernel<IxT, 16>, grid, kHopThreads, 0, s, job);
   else
-    sample_hop_kernel<IxT, 32><<<grid, kHopThreads, 0, s>>>(job);
+    launch_kernel(pdl, sample_hop_kernel<IxT, 32>, grid, kHopThreads, 0, s, job);
 }
 
 }  // namespace shmt
@@ -529,9 +530,9 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
       job.rel_out = out_relabel[h];
     }
     if (indices_dtype == SHMT_I64)
-      launch_hop<long long>(job, hop_tiles[h], s);
+      launch_hop<long long>(job, hop_tiles[h], s, /*pdl=*/h > 0);
     else
-      launch_hop<int>(job, hop_tiles[h], s);
+      launch_hop<int>(job, hop_tiles[h], s, /*pdl=*/h > 0);
     SHMT_CUDA_TRY(cudaGetLastError());
 
     Parts ps{};
@@ -544,7 +545,7 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     ps.dev_n1 = w + 1;
     if (int rc = launch_relabel(ctx, ps, cap[h + 1], newid, out_frontier[h], out_relabel[h],
                                 carve_tile_states(base + off_rel[h], rel_tiles[h]), w + 2, status,
-                                w + 3, s, fuse_insert))
+                                w + 3, s, fuse_insert, /*pdl=*/true))
       return rc;
     cur_seeds = out_frontier[h];
   }
