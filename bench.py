@@ -1006,6 +1006,14 @@ def run_update(args) -> None:
         t_q += ev[1].elapsed_time(ev[2])
     t_ins /= args.steps
     t_q /= args.steps
+    # the reference-named overwrite of the same rows through the finished map (all hits)
+    for _ in range(2):
+        capi.cache_set(None, gpu, keys, rows, m)
+    t_set = time_launches(lambda: capi.cache_set(None, gpu, keys, rows, m), 10, stream)
+    b_set = U_KEYS * (8 + 12 + 2 * row_bytes)
+    line["cache_set"] = {"ms": round(t_set, 4), "keys_per_s": round(U_KEYS / (t_set * 1e-3), 1),
+                         "roofline": {"bound": "hbm", "achieved": round(b_set / (t_set * 1e6), 1), "peak": peak,
+                                      "unit": "GB/s", "frac": round(b_set / (t_set * 1e6) / peak, 4)}}
     # algorithmic bytes: insert+set per key 8 (key) + 4 (slot) + 16 (claim) + row read + row written;
     # lookup per key 8 + 12 + 4
     b_ins = U_KEYS * (8 + 4 + 16 + 2 * row_bytes)

@@ -165,6 +165,12 @@ int shmt_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
  * one stream do not.  This entry point has no counterpart in the reference.        */
 int shmt_scan_static(void* data, int dtype, int64_t n, int exclusive, void* stream);
 
+/* Test hook for the failure path of every look-back scan: runs one warp whose predecessor
+ * tile never publishes, with a short spin limit, and returns what the host sees --
+ * SHMT_ERR_TIMEOUT -- leaving the context usable.  Nothing faults, traps or hangs.
+ * No counterpart in the reference.                                                    */
+int shmt_debug_lookback_timeout(shmt_ctx* ctx, void* stream);
+
 /* ---- relabel ---------------------------------------------------------------
  * Concatenation of `n_parts` id arrays -> distinct ids in first-occurrence
  * order (out_unique, capacity = total) and, for every input element, the index

@@ -185,6 +185,76 @@ row_gather_bulk_kernel(const RowJob job) {
   bulk_wait_read<0>();  // shared memory must outlive the stores that read it
 }
 
+// The mirror image for set: the tile's update rows are contiguous, so ONE bulk load brings
+// them into the stage buffer; each lane then stores its row to where the probe sent it (the
+// cached copy on a hit, the host table on a miss) with its own bulk store.
+template <int STAGES>
+__global__ void __launch_bounds__(kRowThreads)
+row_scatter_bulk_kernel(const RowJob job) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t s_bar[kRowWarps][STAGES];
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int R = job.rows_per_tile;
+  const uint32_t rb = (uint32_t)job.row_bytes;
+  const uint32_t stage_bytes = (uint32_t)R * rb;
+  unsigned char* wbase = smem_raw + (size_t)warp * STAGES * stage_bytes;
+  const int64_t n_tiles = (job.n + R - 1) / R;
+  const int64_t stride = (int64_t)gridDim.x * kRowWarps;
+  const int64_t slot_mask = ((int64_t)1 << job.owner_shift) - 1;
+
+  if (lane == 0)
+    for (int s = 0; s < STAGES; ++s) mbar_init(&s_bar[warp][s], 1);
+  mbar_init_fence();
+  __syncwarp();
+
+  char* dst_row[STAGES];  // where this lane's row of the stage goes (nullptr: nowhere)
+  uint32_t parity = 0;
+
+  auto issue = [&](int64_t tile, int s) {
+    const int64_t first = tile * R;
+    const int rows = (int)min((int64_t)R, job.n - first);
+    dst_row[s] = resolve_row(job, first, rows, lane, slot_mask, load_id(job, first, rows, lane));
+    if (lane == 0) {
+      mbar_arrive_expect_tx(&s_bar[warp][s], (uint32_t)rows * rb);
+      bulk_load(wbase + (size_t)s * stage_bytes, job.flat + first * job.row_bytes, (uint32_t)rows * rb,
+                &s_bar[warp][s]);
+    }
+  };
+
+  constexpr int D = STAGES - 1;
+  int64_t tile = (int64_t)blockIdx.x * kRowWarps + warp;
+  bool ok = true;
+#pragma unroll
+  for (int j = 0; j < D; ++j)
+    if (tile + j * stride < n_tiles) issue(tile + j * stride, j);
+  while (tile < n_tiles && ok) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      if (tile >= n_tiles || !ok) break;
+      const int64_t ahead = tile + D * stride;
+      if (ahead < n_tiles) {
+        bulk_wait_read<0>();  // every lane's store out of that stage has read it
+        __syncwarp();
+        issue(ahead, (s + D) % STAGES);
+      }
+      if (!mbar_wait_bounded(&s_bar[warp][s], (parity >> s) & 1u)) {
+        atomicExch(&g_device_fault, 1);
+        ok = false;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      parity ^= 1u << s;
+      if (ok) {
+        async_proxy_fence();
+        if (dst_row[s])
+          bulk_store(dst_row[s], wbase + (size_t)s * stage_bytes + (size_t)lane * rb, rb);
+        bulk_commit();
+      }
+      tile += stride;
+    }
+  }
+  bulk_wait_read<0>();
+}
+
 // SET == false: table row -> flat (fetch).  SET == true: flat -> table row.
 template <int VEC, bool SET, int U>
 __global__ void __launch_bounds__(kRowThreads) row_copy_kernel(const RowJob job) {
@@ -368,30 +438,31 @@ static int bulk_rows_per_stage(int64_t row_bytes, int vec, int R_small) {
   return (int)r;
 }
 
-static int launch_gather_bulk(RowJob job, int R, cudaStream_t s) {
+template <bool SET>
+static int launch_bulk(RowJob job, int R, cudaStream_t s) {
+  auto kernel = SET ? row_scatter_bulk_kernel<kBulkStages> : row_gather_bulk_kernel<kBulkStages>;
   static bool configured[64] = {false};
   int dev = 0;
   SHMT_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 64 && !configured[dev]) {
-    SHMT_CUDA_TRY(cudaFuncSetAttribute(row_gather_bulk_kernel<kBulkStages>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+    SHMT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)kBulkSmemMax));
     configured[dev] = true;
   }
   job.rows_per_tile = R;
   const size_t smem = (size_t)kRowWarps * kBulkStages * R * job.row_bytes;
-  const unsigned blocks = grid_for_tiles(row_gather_bulk_kernel<kBulkStages>, job.n, R, smem);
-  row_gather_bulk_kernel<kBulkStages><<<blocks, kRowThreads, smem, s>>>(job);
+  const unsigned blocks = grid_for_tiles(kernel, job.n, R, smem);
+  kernel<<<blocks, kRowThreads, smem, s>>>(job);
   SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;
 }
 
 template <bool SET>
 static int launch_row_copy(const RowJob& job, int vec, cudaStream_t s) {
-  if (!SET) {
+  {
     static const bool no_bulk = getenv("SHMT_NO_BULK") != nullptr;
     const int R = no_bulk ? 0 : bulk_rows_per_stage(job.row_bytes, vec, job.rows_per_tile);
-    if (R >= 1) return launch_gather_bulk(job, R, s);
+    if (R >= 1) return launch_bulk<SET>(job, R, s);
   }
   switch (vec) {
     case 16: return launch_lsu<16, SET>(job, s);

@@ -49,7 +49,8 @@ __device__ __forceinline__ int take_tile(int64_t* ticket, int* smem_slot) {
 // lanes of ONE warp of the CTA; every lane gets the result.
 __device__ __forceinline__ int64_t lookback_exclusive_prefix(const TileStates& st, int tile,
                                                              int64_t aggregate,
-                                                             int64_t* status_word) {
+                                                             int64_t* status_word,
+                                                             int spin_limit = kLookbackSpinLimit) {
   const unsigned lane = threadIdx.x & 31;
   if (tile == 0) {
     if (lane == 0) {
@@ -71,7 +72,7 @@ __device__ __forceinline__ int64_t lookback_exclusive_prefix(const TileStates& s
     if (t >= 0) {
       int spins = 0;
       f = ld_acquire(st.flag + t);
-      while (f == 0u && spins < kLookbackSpinLimit) {
+      while (f == 0u && spins < spin_limit) {
         __nanosleep(32);
         f = ld_acquire(st.flag + t);
         ++spins;

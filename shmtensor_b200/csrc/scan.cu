@@ -50,6 +50,13 @@ scan_kernel(T* __restrict__ data, int64_t n, int exclusive, TileStates st, int64
   }
 }
 
+// Exercises the give-up path of the look-back on purpose, harmlessly: one warp plays tile 1
+// of a scan whose tile 0 never runs, with a short spin limit.  It must record DEV_TIMEOUT and
+// return; nothing else is touched.
+__global__ void lookback_timeout_probe_kernel(TileStates st, int64_t* words, int spin_limit) {
+  lookback_exclusive_prefix(st, /*tile=*/1, /*aggregate=*/1, words + W_STATUS, spin_limit);
+}
+
 // Launch helper shared with relabel / sub-CSR: scans `n` items in place using
 // ctx scratch at byte offset `scratch_off` for the tile states.
 int launch_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
@@ -132,6 +139,18 @@ extern "C" int shmt_scan_static(void* data, int dtype, int64_t n, int exclusive,
                                                                 exclusive, st, words);
   SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;
+}
+
+extern "C" int shmt_debug_lookback_timeout(shmt_ctx* ctx, void* stream) {
+  SHMT_REQUIRE(ctx != nullptr, "shmt_debug_lookback_timeout: ctx is null");
+  DeviceGuard guard(ctx->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (int rc = ctx_reserve(ctx, tile_state_bytes(2))) return rc;
+  TileStates st = carve_tile_states(ctx->region(), 2);
+  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + 2 * 4, s));
+  lookback_timeout_probe_kernel<<<1, 32, 0, s>>>(st, ctx->d_words(), 1 << 10);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  return ctx_fetch_words(ctx, s, "shmt_debug_lookback_timeout");
 }
 
 extern "C" int shmt_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,

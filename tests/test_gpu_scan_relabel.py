@@ -92,3 +92,19 @@ def test_relabel_errors(capi):
     e = torch.empty(0, dtype=torch.int64, device="cuda")
     u, (r,) = capi.tensor_relabel([e])
     assert u.numel() == 0 and r.numel() == 0
+
+
+def test_lookback_wait_is_bounded_and_reported(capi):
+    """A look-back whose predecessor never publishes gives up after its spin limit: the host
+    gets SHMT_ERR_TIMEOUT, and the same context keeps working afterwards."""
+    from shmtensor_b200 import _lib
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ctx = capi._ctx(dev)
+    rc = _lib.lib.shmt_debug_lookback_timeout(ctx, torch.cuda.current_stream().cuda_stream)
+    assert rc == _lib.ERR_TIMEOUT and "bounded look-back wait ran out" in _lib.last_error()
+    a = torch.arange(1, 10_001, dtype=torch.int64, device="cuda")
+    capi.thrust_scan(a)
+    capi.check_async()
+    assert a[-1].item() == 50_005_000
+    u, (r,) = capi.tensor_relabel([torch.tensor([7, 7, 3], device="cuda")])   # table was re-cleaned
+    assert u.cpu().tolist() == [7, 3] and r.cpu().tolist() == [0, 0, 1]
