@@ -428,8 +428,8 @@ def run_ours(args) -> None:
             "frac": round(alg / (kernel_ms * 1e6) / peak, 4), "peak_source": peak_src,
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
             # workload, from the ncu capture summarised in profiles/row_gather_bulk_mixed.md
-            "traffic": {"bytes": NCU_DRAM_BYTES_PER_LAUNCH, "algorithmic_bytes": int(alg),
-                        "source": "profiles/row_gather_bulk_mixed.md (ncu --set full, 2 launches)"},
+            "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "algorithmic_bytes": int(alg),
+            "traffic_source": "profiles/row_gather_bulk_mixed.md (ncu --set full, 2 launches; bytes per launch)",
             "kernel_ms": round(kernel_ms, 5),
             "note": "the 80%-hit batch is bound by the host link, not HBM: see roofline_link and "
                     "frac_of_bound (time at the binding ceiling / measured time)",
