@@ -141,9 +141,16 @@ class GPUSamplingDataloader:
             self.indices, self.indptr = self.indices.cuda(), self.indptr.cuda()
             return
 
-        degrees = self.indptr[1:] - self.indptr[:-1]
+        degrees = (self.indptr[1:] - self.indptr[:-1]).cpu()
+        # The row offsets are small next to the adjacency lists (8 bytes per node): when they
+        # fit in a quarter of the budget they all go to the GPU first.  A row whose adjacency
+        # stays on the host then costs one trip over the host link instead of two, and such
+        # trips, not bytes, are what bound the sampler on cold rows.
+        if not self.indptr.is_cuda and self.indptr.nbytes <= cache_capacity // 4:
+            cache_capacity -= self.indptr.nbytes
+            self.indptr = self.indptr.cuda()
         candidates = torch.sort(hotness, descending=True).indices
-        cost = degrees[candidates.to(degrees.device)].cpu() * self.indices.element_size() \
+        cost = degrees[candidates.cpu()] * self.indices.element_size() \
             + self.indptr.element_size() + 1.25 * 2 * 4
         n_rows = int(torch.searchsorted(torch.cumsum(cost, dim=0), cache_capacity).item())
         candidates = candidates[:n_rows].cuda()

@@ -25,8 +25,9 @@ def test_three_hop_batches_are_consistent(cached):
                                shuffle=False)
     if cached:
         hotness = torch.from_numpy(np.diff(indptr_n).astype(np.float32))
-        dl.create_cache(int((indptr.nbytes + indices.nbytes) * 0.3), hotness)
+        dl.create_cache(int((indptr.nbytes + indices.nbytes) * 0.5), hotness)
         assert dl.has_cache and dl.hashmap.key_dtype == torch.int32
+        assert dl.indptr.is_cuda and not dl.indices.is_cuda      # offsets on the GPU, cold rows on the host
     assert len(dl) == 4
     deg = np.diff(indptr_n)
     n_batches = 0
