@@ -1014,6 +1014,31 @@ def run_update(args) -> None:
     line["cache_set"] = {"ms": round(t_set, 4), "keys_per_s": round(U_KEYS / (t_set * 1e-3), 1),
                          "roofline": {"bound": "hbm", "achieved": round(b_set / (t_set * 1e6), 1), "peak": peak,
                                       "unit": "GB/s", "frac": round(b_set / (t_set * 1e6) / peak, 4)}}
+    # plain map construction + query (CUCOStaticHashmap(keys, values, 0.5), the reference's flow),
+    # and the reference's own map on the same GPU when oracle/_ref was built
+    def build_query(mod):
+        t0 = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        t0[0].record(stream)
+        mm = mod.CUCOStaticHashmap(keys, slots, 0.5)
+        t0[1].record(stream)
+        r = mm.query(req)
+        t0[2].record(stream)
+        torch.cuda.synchronize()
+        return t0[0].elapsed_time(t0[1]), t0[1].elapsed_time(t0[2]), r
+    build_query(capi)
+    b_ms, q_ms, r_ours = build_query(capi)
+    line["map_build_query"] = {"build_ms": round(b_ms, 4), "query_ms": round(q_ms, 4)}
+    try:
+        from oracle import build_ref
+        ref = build_ref.load_reference()
+    except Exception:  # noqa: BLE001
+        ref = None
+    if ref is not None:
+        build_query(ref)
+        rb_ms, rq_ms, r_ref = build_query(ref)
+        assert torch.equal(r_ours, r_ref), "map query differs from the reference's"
+        line["map_build_query"]["reference_cuda"] = {"build_ms": round(rb_ms, 4), "query_ms": round(rq_ms, 4),
+                                                     "what": "the reference's wrapper over a stand-in for cuCollections"}
     # algorithmic bytes: insert+set per key 8 (key) + 4 (slot) + 16 (claim) + row read + row written;
     # lookup per key 8 + 12 + 4
     b_ins = U_KEYS * (8 + 4 + 16 + 2 * row_bytes)

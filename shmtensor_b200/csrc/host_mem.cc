@@ -60,7 +60,9 @@ int map_shared(const char* who, const char* name, int64_t size, int pin_memory, 
     return SHMT_ERR_OS;
   }
   if (pin_memory) {
-    if (int rc = register_host(ptr, (size_t)size, cudaHostRegisterDefault, who)) {
+    // Portable: usable from every GPU of the process, not only the one current now (the
+    // reference registers with the default flag, which binds to the current context)
+    if (int rc = register_host(ptr, (size_t)size, cudaHostRegisterPortable, who)) {
       munmap(ptr, (size_t)size);
       close(fd);
       if (create) shm_unlink(name);
@@ -207,7 +209,7 @@ int shmt_npy_open(const char* path, int pin_memory, shmt_npy_info* out) {
   out->fd = fd;
   if (pin_memory) {
     // like the reference, register the whole mapping (header included)
-    if (int rc = register_host(base, file_size, cudaHostRegisterDefault, "shmt_npy_open")) {
+    if (int rc = register_host(base, file_size, cudaHostRegisterPortable, "shmt_npy_open")) {
       munmap(base, file_size);
       close(fd);
       return rc;
