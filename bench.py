@@ -311,11 +311,14 @@ def run_ours(args) -> None:
         fetch(batches[i % N_BATCHES])
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, period_s=0.1)
+    sampler.start()  # its first NVML queries are slow and can stall a launch: let them pass now
+    for i in range(3):
+        fetch(batches[i % N_BATCHES])
+    torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    sampler.start()
     region[0].record(stream)
     for i, (a, b) in enumerate(evs):
         a.record(stream)
@@ -328,6 +331,10 @@ def run_ours(args) -> None:
     clocks = sampler.stop()
     region_ms = region[0].elapsed_time(region[1])
     kernel_ms = sum(a.elapsed_time(b) for a, b in evs) / args.steps
+    per_launch = [a.elapsed_time(b) for a, b in evs]
+    print(f"[rank {rank}] timed region {region_ms:.3f} ms, launches min/median/max "
+          f"{min(per_launch):.3f}/{statistics.median(per_launch):.3f}/{max(per_launch):.3f} ms, "
+          f"first five {[round(x, 3) for x in per_launch[:5]]}", file=sys.stderr, flush=True)
     if world > 1:
         t = torch.tensor([region_ms, kernel_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -407,6 +414,22 @@ def run_ours(args) -> None:
             "peak_source": "streaming read kernel over the next rank's IPC-mapped buffer, measured in this run",
             "what": "ids uniform over the cached set: 1/N of the rows local, the rest read from peers over NVLink; "
                     "achieved = remote row bytes per rank / slowest rank's kernel time"}
+        # the batched alternative (NCCL all-to-all of ids, then of rows) on the same batches
+        a2a = pcache.fetch_alltoall(batches[0])
+        assert torch.equal(a2a.view(torch.int32), fetch(batches[0]).view(torch.int32)), "all-to-all route differs"
+        def a2a_ms(bs, reps):
+            for b in bs[:2]:
+                pcache.fetch_alltoall(b)
+            dist.barrier()
+            t_ = time_launches(lambda c=[0]: (pcache.fetch_alltoall(bs[c[0] % len(bs)]), c.__setitem__(0, c[0] + 1)),
+                               reps, stream)
+            t_ = torch.tensor([t_], device=dev)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            return t_.item()
+        line["alltoall_route"] = {"mixed_ms": round(a2a_ms(batches, 10), 4), "all_hit_ms": round(a2a_ms(hot_batches, 10), 4),
+                                  "p2p_mixed_ms": round(ms_per_step, 4), "p2p_all_hit_ms": round(ms_hit, 4),
+                                  "what": "PartitionedFeatureCache.fetch_alltoall (ids bucketed by owner, NCCL all-to-all of "
+                                          "ids and of rows, misses read locally) against the fused peer-load kernel"}
         torch.cuda.synchronize()
         dist.barrier()
         for p_ in opened:

@@ -134,6 +134,37 @@ class PartitionedFeatureCache:
                                          capi._ptr(out), capi._stream(ids.device)))
         return out
 
+    def fetch_alltoall(self, ids: torch.Tensor) -> torch.Tensor:
+        """The same result by the batched route: ids are bucketed by owner, exchanged with an
+        NCCL all-to-all, gathered on the owner, and the rows come back with a second
+        all-to-all; misses are read locally from the host table.  A collective, so every rank
+        must call it, with batches of any size.  Kept for comparison with ``fetch``: direct
+        peer loads need no exchange of ids and no staging copies."""
+        capi._check_cuda(ids, "ids")
+        ids = ids.contiguous()
+        n, world = ids.numel(), self.world
+        out = torch.empty((n, *self.host_table.shape[1:]), dtype=self.host_table.dtype, device=ids.device)
+        value = self.directory.query(ids)
+        miss = (value < 0).nonzero(as_tuple=True)[0]
+        if miss.numel():
+            out[miss] = capi.uva_fetch(self.host_table, ids[miss])
+        hit = (value >= 0).nonzero(as_tuple=True)[0]
+        owner = value[hit] >> OWNER_SHIFT
+        order = torch.argsort(owner, stable=True)
+        send_slots = (value[hit] & ((1 << OWNER_SHIFT) - 1))[order]
+        send_counts = torch.bincount(owner, minlength=world)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        sc, rc = send_counts.tolist(), recv_counts.tolist()
+        recv_slots = torch.empty(sum(rc), dtype=send_slots.dtype, device=ids.device)
+        dist.all_to_all_single(recv_slots, send_slots, rc, sc, group=self.group)
+        rows_out = self.shard[recv_slots]
+        rows_in = torch.empty((sum(sc), *self.host_table.shape[1:]), dtype=self.host_table.dtype,
+                              device=ids.device)
+        dist.all_to_all_single(rows_in, rows_out, sc, rc, group=self.group)
+        out[hit[order]] = rows_in
+        return out
+
     def close(self) -> None:
         """Unmap the peers' buffers and free this rank's shard.  Call on every rank, between
         steps, with no fetch in flight; the ranks meet at a barrier before any memory goes."""
