@@ -307,14 +307,15 @@ def run_ours(args) -> None:
     del got, want
 
     # ---- warm-up, then the timed region: K launches, one CUDA-event pair each
+    out = None
     for i in range(max(args.warmup, 3)):
-        fetch(batches[i % N_BATCHES])
+        out = fetch(batches[i % N_BATCHES])  # held like in the timed loop: two output blocks get cached
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
     sampler = ClockSampler(local_rank, period_s=0.1)
     sampler.start()  # its first NVML queries are slow and can stall a launch: let them pass now
     for i in range(3):
-        fetch(batches[i % N_BATCHES])
+        out = fetch(batches[i % N_BATCHES])
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -660,9 +661,9 @@ def run_sampling(args) -> None:
     seeds_dev = [b.to(dev) for b in seeds_host]
     stream = torch.cuda.current_stream()
     capi.set_sampling_seed(7777)
-    for i in range(max(args.warmup, 3)):
-        minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
-    sampler = ClockSampler(local_rank)
+    for i in range(max(args.warmup, 3)):  # results held as in the timed loop, so its blocks get cached
+        e, frontier = minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
+    sampler = ClockSampler(local_rank, period_s=0.1)
     region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
     torch.cuda.synchronize()
     sampler.start()
@@ -883,8 +884,8 @@ def run_minibatch(args) -> None:
     _, frontier, rows = step(0)
     assert torch.equal(rows.cpu().view(torch.int32), feats[frontier.cpu().long()].view(torch.int32))
     for i in range(max(args.warmup, 3)):
-        step(i)
-    sampler = ClockSampler(local_rank)
+        e, frontier, rows = step(i)
+    sampler = ClockSampler(local_rank, period_s=0.1)
     region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
     if world > 1:
         dist.barrier()
