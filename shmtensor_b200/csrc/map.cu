@@ -11,22 +11,19 @@ constexpr int kMapThreads = 256;
 __global__ void __launch_bounds__(kMapThreads)
 map_insert_kernel(MapView m, const void* __restrict__ keys, int keys64,
                   const void* __restrict__ vals, int vals64, int64_t n, int64_t* meta) {
-  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int64_t n_warps = ((int64_t)gridDim.x * blockDim.x) >> 5;
-  const unsigned lane = threadIdx.x & 31;
-  const int64_t n_batches = (n + 31) >> 5;
-  int64_t total_new = 0;
-  for (int64_t b = warp; b < n_batches; b += n_warps) {
-    const int64_t i = b * 32 + lane;
-    const bool valid = i < n;
-    const int64_t k = valid ? load_int(keys, keys64, i) : kEmptyKey;
-    const int64_t v = valid ? load_int(vals, vals64, i) : -1;
-    int n_new = 0;
-    warp_insert(m, k, v, valid, /*assign=*/true, meta, &n_new);
-    total_new += n_new;
-  }
-  if (lane == 0 && total_new)
-    atomicAdd(reinterpret_cast<unsigned long long*>(meta + 1), (unsigned long long)total_new);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int added = 0;
+  bool overflow = false;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    added += thread_insert(m, load_int(keys, keys64, i), load_int(vals, vals64, i), /*assign=*/true,
+                           &overflow);
+  // one atomic per warp for the key count
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) added += __shfl_xor_sync(0xffffffffu, added, o);
+  if ((threadIdx.x & 31) == 0 && added)
+    atomicAdd(reinterpret_cast<unsigned long long*>(meta + 1), (unsigned long long)added);
+  if (overflow)
+    atomicMax(reinterpret_cast<unsigned long long*>(meta), (unsigned long long)DEV_OVERFLOW);
 }
 
 __global__ void __launch_bounds__(kMapThreads)
@@ -126,7 +123,9 @@ int shmt_map_insert(shmt_map* map, const void* keys, const void* values, int64_t
   SHMT_REQUIRE(keys != nullptr && values != nullptr, "shmt_map_insert: keys/values are null");
   DeviceGuard guard(map->device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  map_insert_kernel<<<grid_for_warps(n), kMapThreads, 0, s>>>(
+  int64_t ins_blocks = (n + kMapThreads - 1) / kMapThreads;
+  const int64_t ins_cap = (int64_t)sm_count() * 16;
+  map_insert_kernel<<<(unsigned)(ins_blocks < ins_cap ? ins_blocks : ins_cap), kMapThreads, 0, s>>>(
       map->view, keys, map->key_dtype == SHMT_I64, values, map->val_dtype == SHMT_I64, n,
       map->d_meta);
   SHMT_CUDA_TRY(cudaGetLastError());

@@ -132,6 +132,37 @@ __device__ __forceinline__ longlong2 cas_slot(Slot* p, longlong2 expect, longlon
   return old;
 }
 
+// One thread inserts one (key, value): walk the slots from the start of the home window, claim
+// the first empty one with a 16-byte CAS.  Same placement rule as warp_insert (first empty slot
+// in window order), so both can fill one table.  For bulk builds, where every thread has its own
+// key and nothing else to wait for, this is faster than the cooperative form.  Returns true if
+// the key is new; *overflow is set if the table is full.
+__device__ __forceinline__ bool thread_insert(const MapView& m, int64_t key, int64_t val, bool assign,
+                                              bool* overflow) {
+  key = narrow_key(m, key);
+  if (key == kEmptyKey) return false;
+  const uint64_t n_slots = m.n_windows * kWindow;
+  uint64_t pos = home_window(m, key) * kWindow;
+  for (uint64_t step = 0; step < n_slots; ++step) {
+    Slot* p = m.slots + pos;
+    const long long cur = __ldcg(&p->key);
+    if (cur == kEmptyKey) {
+      const longlong2 old = cas_slot(p, make_longlong2(kEmptyKey, -1), make_longlong2(key, val));
+      if (old.x == kEmptyKey) return true;
+      if (old.x == key) {
+        if (assign) p->val = val;
+        return false;
+      }
+    } else if (cur == key) {
+      if (assign) p->val = val;
+      return false;
+    }
+    pos = pos + 1 == n_slots ? 0 : pos + 1;
+  }
+  *overflow = true;
+  return false;
+}
+
 // Insert one (key, value) per lane; all 32 lanes must call.  A key already in
 // the table keeps its slot; its value is replaced only if `assign`.  Returns
 // the value now stored for the key (-1 for invalid lanes or on overflow) and
