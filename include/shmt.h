@@ -74,11 +74,21 @@ int shmt_map_create(int device, int64_t capacity, int64_t expected_keys,
                     int key_dtype, int val_dtype, void* table_buf, void* stream,
                     shmt_map** out);
 
-/* insert_or_assign of n (key, value) pairs, key != -1.  Synchronises `stream`
- * and returns SHMT_ERR_CAPACITY if the table overflowed.  Bulk-insert half of
- * include/cuco_hashmap.cuh:68-70; inserting into an existing map is new.      */
+/* insert_or_assign of n (key, value) pairs; keys -1 and -2 are reserved and
+ * skipped.  Synchronises `stream` and returns SHMT_ERR_CAPACITY if the table
+ * overflowed.  Bulk-insert half of include/cuco_hashmap.cuh:68-70; inserting
+ * into an existing map is new.  Slots freed by shmt_map_erase are taken again. */
 int shmt_map_insert(shmt_map* map, const void* keys, const void* values,
                     int64_t n, void* stream);
+
+/* Remove n keys (key dtype of the map).  out_values, if not NULL, receives per
+ * key the value it had (value dtype of the map) or -1 if it was absent; a key
+ * listed twice reports its value once.  Synchronises `stream` (the key count
+ * is read back).  Must not overlap an insert into the same map.  No counterpart
+ * in the reference, whose map is built once (include/cuco_hashmap.cuh:49-93):
+ * it is what lets a cache evict rows and hand their slots to new ids.          */
+int shmt_map_erase(shmt_map* map, const void* keys, int64_t n, void* out_values,
+                   void* stream);
 
 /* out[i] = value of requests[i] or -1 (include/cuco_hashmap.cuh:81-87).
  * Requests are first narrowed to the key dtype, as the reference's

@@ -52,6 +52,14 @@ def hashmap_query(table: Dict[int, int], requests: np.ndarray, key_dtype=np.int6
     return out.astype(value_dtype).reshape(req.shape)
 
 
+def hashmap_erase(table: Dict[int, int], keys: np.ndarray) -> np.ndarray:
+    """Removal of keys from the map: per key the value it had, or -1 (absent, or listed before
+    in the same call).  The reference has no erase (its map is built once,
+    include/cuco_hashmap.cuh:49-93); this states the contract of the added entry point."""
+    return np.array([table.pop(int(k), -1) for k in np.asarray(keys).reshape(-1).tolist()],
+                    dtype=np.int64)
+
+
 # --------------------------------------------------------------------------- fetch / set
 def uva_fetch(data: np.ndarray, indices: np.ndarray) -> np.ndarray:
     """src/cache_feature_fetch.cu:27-45 — ``out[i] = data[indices[i]]``."""

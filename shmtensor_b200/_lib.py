@@ -52,6 +52,7 @@ SIGNATURES = {
     "shmt_map_table_bytes": (_i64, [_i64, _i64]),
     "shmt_map_create": (_i, [_i, _i64, _i64, _i, _i, _vp, _vp, _pvp]),
     "shmt_map_insert": (_i, [_vp, _vp, _vp, _i64, _vp]),
+    "shmt_map_erase": (_i, [_vp, _vp, _i64, _vp, _vp]),
     "shmt_map_query": (_i, [_vp, _vp, _i, _i64, _vp, _vp]),
     "shmt_map_capacity": (_i64, [_vp]),
     "shmt_map_memory_usage": (_i64, [_vp]),

@@ -229,6 +229,16 @@ class CUCOStaticHashmap:
         check(lib.shmt_map_insert(self._handle, _ptr(keys), _ptr(values), keys.numel(),
                                   _stream(self._device)))
 
+    def erase(self, keys: torch.Tensor) -> torch.Tensor:
+        """Extension: remove ``keys``; returns per key the value it had, or -1 if it was absent.
+        The freed slots are taken again by later ``insert`` calls."""
+        _check_cuda(keys, "keys")
+        keys = keys.contiguous().to(_CODE_DTYPES[self._kd])
+        out = torch.empty(keys.shape, dtype=_CODE_DTYPES[self._vd], device=keys.device)
+        check(lib.shmt_map_erase(self._handle, _ptr(keys), keys.numel(), _ptr(out),
+                                 _stream(self._device)))
+        return out
+
     def query(self, requests: torch.Tensor) -> torch.Tensor:
         _check_cuda(requests, "requests")
         if requests.dtype not in _INT_CODES:
@@ -378,6 +388,24 @@ def cache_insert_set(gpu_data: torch.Tensor, indices: torch.Tensor, slots: torch
 
 
 # --------------------------------------------------------------------------- scan / relabel
+def cache_replace(uva_data: torch.Tensor, gpu_data: torch.Tensor, hashmap: CUCOStaticHashmap,
+                  evict_ids: torch.Tensor, admit_ids: torch.Tensor) -> int:
+    """Extension: turn the cache over in place.  The rows of ``evict_ids`` leave the cache; the ids
+    of ``admit_ids`` (distinct, not cached yet) take their rows of ``gpu_data`` and are filled from
+    ``uva_data`` by the UVA gather kernel.  The reference rebuilds the map and re-copies every
+    row from the CPU to change the cached set (example/test_cache_set.py:57-61).  Admits at most
+    as many ids as rows were freed, in order; returns how many."""
+    freed = hashmap.erase(evict_ids)
+    freed = freed[freed >= 0]
+    n = min(int(freed.numel()), int(admit_ids.numel()))
+    if n == 0:
+        return 0
+    admit, rows = admit_ids[:n].contiguous(), freed[:n].contiguous()
+    hashmap.insert(admit, rows)
+    uva_set(gpu_data, rows, uva_fetch(uva_data, admit))
+    return n
+
+
 def thrust_scan(tensor: torch.Tensor) -> None:
     """src/thrust_scan.cu:9-18 — in-place inclusive prefix sum (int32; int64 also accepted)."""
     _check_cuda(tensor, "tensor")

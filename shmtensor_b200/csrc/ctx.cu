@@ -38,7 +38,73 @@ int device_of_pointer(const void* p) {
   return cur;
 }
 
+HostPost ctx_begin_post(shmt_ctx* ctx, const int64_t* dev_words, int n_words, int64_t* done_word) {
+  HostPost p{};
+  p.words = dev_words;
+  p.n_words = n_words;
+  p.done = done_word;
+  if (n_words > kCtxWords - 1) return p;  // no room: ctx_await_post copies instead
+  void* dev_view = nullptr;
+  if (cudaHostGetDevicePointer(&dev_view, ctx->h_words, 0) != cudaSuccess) {
+    cudaGetLastError();
+    return p;
+  }
+  p.host = static_cast<int64_t*>(dev_view);
+  p.flag_at = kCtxWords - 1;
+  p.seq = ++ctx->post_seq;
+  return p;
+}
+
+static inline void cpu_relax() {
+#if defined(__x86_64__) || defined(__i386__)
+  __builtin_ia32_pause();
+#else
+  asm volatile("" ::: "memory");
+#endif
+}
+
+int ctx_await_post(shmt_ctx* ctx, const HostPost& post, cudaStream_t stream) {
+  if (post.host) {
+    const int64_t* flag = ctx->h_words + post.flag_at;
+    for (uint64_t it = 1;; ++it) {
+      if (__atomic_load_n(flag, __ATOMIC_ACQUIRE) == post.seq) return SHMT_OK;
+      if ((it & 0xFFF) == 0) {
+        const cudaError_t q = cudaStreamQuery(stream);
+        if (q == cudaSuccess) {
+          if (__atomic_load_n(flag, __ATOMIC_ACQUIRE) == post.seq) return SHMT_OK;
+          break;  // drained without a post: read the words the ordinary way
+        }
+        if (q != cudaErrorNotReady) {
+          set_error("waiting for posted results: %s", cudaGetErrorString(q));
+          return SHMT_ERR_CUDA;
+        }
+      }
+      cpu_relax();
+    }
+  }
+  SHMT_CUDA_TRY(cudaMemcpyAsync(ctx->h_words, post.words, (size_t)post.n_words * sizeof(int64_t),
+                                cudaMemcpyDeviceToHost, stream));
+  SHMT_CUDA_TRY(cudaStreamSynchronize(stream));
+  return SHMT_OK;
+}
+
+int ctx_mark_tail(shmt_ctx* ctx, cudaStream_t stream) {
+  if (!ctx->tail_event)
+    SHMT_CUDA_TRY(cudaEventCreateWithFlags(&ctx->tail_event, cudaEventDisableTiming));
+  SHMT_CUDA_TRY(cudaEventRecord(ctx->tail_event, stream));
+  ctx->tail_pending = true;
+  return SHMT_OK;
+}
+
+int ctx_join_tail(shmt_ctx* ctx) {
+  if (!ctx->tail_pending) return SHMT_OK;
+  ctx->tail_pending = false;
+  SHMT_CUDA_TRY(cudaEventSynchronize(ctx->tail_event));
+  return SHMT_OK;
+}
+
 int ctx_reserve(shmt_ctx* ctx, size_t bytes) {
+  if (int rc = ctx_join_tail(ctx)) return rc;
   bytes += 256;  // result words live in front of the region
   if (bytes <= ctx->scratch_bytes) return SHMT_OK;
   // cudaFree waits for work that may still read the old block.
@@ -56,6 +122,7 @@ int ctx_reserve(shmt_ctx* ctx, size_t bytes) {
 }
 
 int ctx_reserve_table(shmt_ctx* ctx, size_t bytes, cudaStream_t stream) {
+  if (int rc = ctx_join_tail(ctx)) return rc;
   if (bytes > ctx->table_bytes) {
     if (ctx->table) SHMT_CUDA_TRY(cudaFree(ctx->table));
     ctx->table = nullptr;
@@ -80,6 +147,10 @@ int ctx_fetch_words(shmt_ctx* ctx, cudaStream_t stream, const char* what) {
   SHMT_CUDA_TRY(cudaMemcpyAsync(ctx->h_words, ctx->d_words(), 4 * sizeof(int64_t),
                                 cudaMemcpyDeviceToHost, stream));
   SHMT_CUDA_TRY(cudaStreamSynchronize(stream));
+  return ctx_status_of_words(ctx, what);
+}
+
+int ctx_status_of_words(shmt_ctx* ctx, const char* what) {
   const int64_t st = ctx->h_words[W_STATUS];
   if (st != DEV_OK) ctx->table_dirty = true;
   if (st == DEV_TIMEOUT) {
@@ -113,7 +184,8 @@ int shmt_ctx_create(int device, shmt_ctx** out) {
   shmt_ctx* ctx = new shmt_ctx();
   ctx->device = device;
   void* h = nullptr;
-  cudaError_t e = cudaHostAlloc(&h, kCtxWords * sizeof(int64_t), cudaHostAllocDefault);
+  cudaError_t e = cudaHostAlloc(&h, kCtxWords * sizeof(int64_t),
+                                cudaHostAllocMapped | cudaHostAllocPortable);
   if (e != cudaSuccess) {
     set_error("shmt_ctx_create: %s", cudaGetErrorString(e));
     delete ctx;
@@ -136,6 +208,7 @@ int shmt_ctx_destroy(shmt_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->table) cudaFree(ctx->table);
   if (ctx->h_words) cudaFreeHost(ctx->h_words);
+  if (ctx->tail_event) cudaEventDestroy(ctx->tail_event);
   delete ctx;
   return SHMT_OK;
 }

@@ -1,4 +1,4 @@
-// Static hashmap: creation, bulk insert_or_assign, bulk query.
+// Static hashmap: creation, bulk insert_or_assign, bulk query, bulk erase.
 // Replaces pycuco::CUCOHashmap / CUCOHashmapWrapper of the reference
 // (include/cuco_hashmap.cuh:49-93, src/cuco_hashmap.cu:10-41).
 #include "ctx.cuh"
@@ -24,6 +24,22 @@ map_insert_kernel(MapView m, const void* __restrict__ keys, int keys64,
     atomicAdd(reinterpret_cast<unsigned long long*>(meta + 1), (unsigned long long)added);
   if (overflow)
     atomicMax(reinterpret_cast<unsigned long long*>(meta), (unsigned long long)DEV_OVERFLOW);
+}
+
+__global__ void __launch_bounds__(kMapThreads)
+map_erase_kernel(MapView m, const void* __restrict__ keys, int keys64, int64_t n,
+                 void* __restrict__ out, int out64, int64_t* meta) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  int removed = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const int64_t v = thread_erase(m, load_int(keys, keys64, i));
+    removed += v >= 0;
+    if (out) store_int(out, out64, i, v);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) removed += __shfl_xor_sync(0xffffffffu, removed, o);
+  if ((threadIdx.x & 31) == 0 && removed)
+    atomicAdd(reinterpret_cast<unsigned long long*>(meta + 1), 0ULL - (unsigned long long)removed);
 }
 
 __global__ void __launch_bounds__(kMapThreads)
@@ -138,6 +154,26 @@ int shmt_map_insert(shmt_map* map, const void* keys, const void* values, int64_t
               (long long)meta[1], (long long)map->capacity);
     return SHMT_ERR_CAPACITY;
   }
+  return SHMT_OK;
+}
+
+int shmt_map_erase(shmt_map* map, const void* keys, int64_t n, void* out_values, void* stream) {
+  SHMT_REQUIRE(map != nullptr, "shmt_map_erase: map is null");
+  SHMT_REQUIRE(n >= 0, "shmt_map_erase: negative count");
+  if (n == 0) return SHMT_OK;
+  SHMT_REQUIRE(keys != nullptr, "shmt_map_erase: keys are null");
+  DeviceGuard guard(map->device);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int64_t blocks = (n + kMapThreads - 1) / kMapThreads;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  map_erase_kernel<<<(unsigned)(blocks < cap ? blocks : cap), kMapThreads, 0, s>>>(
+      map->view, keys, map->key_dtype == SHMT_I64, n, out_values, map->val_dtype == SHMT_I64,
+      map->d_meta);
+  SHMT_CUDA_TRY(cudaGetLastError());
+  int64_t meta[2] = {0, 0};
+  SHMT_CUDA_TRY(cudaMemcpyAsync(meta, map->d_meta, sizeof(meta), cudaMemcpyDeviceToHost, s));
+  SHMT_CUDA_TRY(cudaStreamSynchronize(s));
+  map->size = meta[1];
   return SHMT_OK;
 }
 

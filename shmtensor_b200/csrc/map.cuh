@@ -5,8 +5,10 @@
 // n_windows); probing is linear over windows.  A 4-lane tile inspects one
 // window per step (each lane one 16-byte load) and votes with a ballot, so a
 // warp resolves 8 keys per step and 32 keys with four independent steps in
-// flight.  Keys are never deleted, so an empty slot ends a probe.
+// flight.  An empty slot ends a probe; an erased slot (key -2) does not, and is
+// taken again by a later bulk insert.
 // Empty key = -1 (the reference's sentinel, include/cuco_hashmap.cuh:58-59);
+// -2 marks an erased slot, so both are reserved (ids are non-negative);
 // int32 keys are stored sign-extended, int32 values likewise.
 #pragma once
 
@@ -26,6 +28,7 @@ struct MapView {
 };
 
 constexpr int kWindow = 4;
+constexpr int64_t kErasedKey = -2;
 
 }  // namespace shmt
 
@@ -53,6 +56,8 @@ __device__ __forceinline__ int64_t narrow_key(const MapView& m, int64_t k) {
   return m.key32 ? (int64_t)(int32_t)k : k;
 }
 
+__device__ __forceinline__ bool reserved_key(int64_t k) { return k == kEmptyKey || k == kErasedKey; }
+
 __device__ __forceinline__ uint64_t home_window(const MapView& m, int64_t k) {
   return __umul64hi(mix64((uint64_t)k), m.n_windows);
 }
@@ -63,7 +68,7 @@ __device__ __forceinline__ int64_t warp_find(const MapView& m, int64_t key, bool
   const unsigned full = 0xffffffffu;
   const unsigned lane = threadIdx.x & 31, sub = lane & 3, tile = lane >> 2;
   key = narrow_key(m, key);
-  if (key == kEmptyKey) valid = false;
+  if (reserved_key(key)) valid = false;
   const longlong2* slots = reinterpret_cast<const longlong2*>(m.slots);
 
   longlong2 s[4];
@@ -132,35 +137,71 @@ __device__ __forceinline__ longlong2 cas_slot(Slot* p, longlong2 expect, longlon
   return old;
 }
 
-// One thread inserts one (key, value): walk the slots from the start of the home window, claim
-// the first empty one with a 16-byte CAS.  Same placement rule as warp_insert (first empty slot
-// in window order), so both can fill one table.  For bulk builds, where every thread has its own
-// key and nothing else to wait for, this is faster than the cooperative form.  Returns true if
-// the key is new; *overflow is set if the table is full.
+// One thread inserts one (key, value): walk the slots from the start of the home window up to the
+// first empty one, which proves the key absent, then claim the first erased slot met on the way,
+// else that empty slot, with a 16-byte CAS.  Occupied slots never change while inserts run, so
+// two threads inserting the same key meet at the same slot and one of them sees the other's key.
+// Without erased slots this is the placement rule of warp_insert (first empty slot in window
+// order), so both can fill one table.  For bulk builds, where every thread has its own key and
+// nothing else to wait for, this is faster than the cooperative form.  Must not run concurrently
+// with thread_erase.  Returns true if the key is new; *overflow is set if the table is full.
 __device__ __forceinline__ bool thread_insert(const MapView& m, int64_t key, int64_t val, bool assign,
                                               bool* overflow) {
   key = narrow_key(m, key);
-  if (key == kEmptyKey) return false;
-  const uint64_t n_slots = m.n_windows * kWindow;
-  uint64_t pos = home_window(m, key) * kWindow;
-  for (uint64_t step = 0; step < n_slots; ++step) {
-    Slot* p = m.slots + pos;
-    const long long cur = __ldcg(&p->key);
+  if (reserved_key(key)) return false;
+  const uint64_t n_slots = m.n_windows * kWindow, none = ~0ULL;
+  uint64_t pos = home_window(m, key) * kWindow, erased_at = none;
+  // a lost race restarts the walk behind the lost slot, so allow two laps
+  for (uint64_t step = 0; step < 2 * n_slots; ++step) {
+    const long long cur = __ldcg(&m.slots[pos].key);
+    if (cur == key) {
+      if (assign) m.slots[pos].val = val;
+      return false;
+    }
+    if (cur == kErasedKey && erased_at == none) erased_at = pos;
     if (cur == kEmptyKey) {
-      const longlong2 old = cas_slot(p, make_longlong2(kEmptyKey, -1), make_longlong2(key, val));
-      if (old.x == kEmptyKey) return true;
+      const uint64_t at = erased_at != none ? erased_at : pos;
+      const long long expect = erased_at != none ? kErasedKey : kEmptyKey;
+      const longlong2 old = cas_slot(m.slots + at, make_longlong2(expect, -1), make_longlong2(key, val));
+      if (old.x == expect) return true;
       if (old.x == key) {
-        if (assign) p->val = val;
+        if (assign) m.slots[at].val = val;
         return false;
       }
-    } else if (cur == key) {
-      if (assign) p->val = val;
-      return false;
+      // another key took the slot first: go on behind it
+      pos = at;
+      erased_at = none;
     }
     pos = pos + 1 == n_slots ? 0 : pos + 1;
   }
   *overflow = true;
   return false;
+}
+
+// One thread erases one key: the slot becomes {-2, -1}.  Returns the value the key had, or -1 if
+// it was absent (or another thread of the same launch erased it first).
+__device__ __forceinline__ int64_t thread_erase(const MapView& m, int64_t key) {
+  key = narrow_key(m, key);
+  if (reserved_key(key)) return -1;
+  const uint64_t n_slots = m.n_windows * kWindow;
+  uint64_t pos = home_window(m, key) * kWindow;
+  for (uint64_t step = 0; step < n_slots; ++step) {
+    Slot* p = m.slots + pos;
+    const long long cur = __ldcg(&p->key);
+    if (cur == kEmptyKey) return -1;
+    if (cur == key) {
+      long long v = __ldcg(&p->val);
+      for (int tries = 0; tries < 4; ++tries) {
+        const longlong2 old = cas_slot(p, make_longlong2(key, v), make_longlong2(kErasedKey, -1));
+        if (old.x != key) return -1;
+        if (old.y == v) return v;
+        v = old.y;
+      }
+      return -1;
+    }
+    pos = pos + 1 == n_slots ? 0 : pos + 1;
+  }
+  return -1;
 }
 
 // Insert one (key, value) per lane; all 32 lanes must call.  A key already in
@@ -173,7 +214,7 @@ __device__ __forceinline__ int64_t warp_insert(const MapView& m, int64_t key, in
   const unsigned full = 0xffffffffu;
   const unsigned lane = threadIdx.x & 31, sub = lane & 3, tile = lane >> 2;
   key = narrow_key(m, key);
-  if (key == kEmptyKey) valid = false;
+  if (reserved_key(key)) valid = false;
   int64_t result = -1;
   int added = 0;
 #pragma unroll 1

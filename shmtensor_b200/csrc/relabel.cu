@@ -53,7 +53,7 @@ relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* sta
 __global__ void __launch_bounds__(kRelThreads)
 relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
                        void* __restrict__ unique, TileStates st, int64_t* ticket, int64_t* status,
-                       int64_t* result) {
+                       int64_t* result, HostPost post) {
   __shared__ int64_t warp_sums[32];
   __shared__ int64_t s_total;
   __shared__ int64_t s_prefix;
@@ -64,7 +64,10 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
   const int64_t n_tiles = (numel + kRelTile - 1) / kRelTile;
   const int tile = take_tile(ticket, &s_tile);
   if (tile >= n_tiles) {  // the grid is sized for the largest input the caller allows
-    if (numel == 0 && tile == 0 && threadIdx.x == 0) *result = 0;
+    if (numel == 0 && tile == 0 && threadIdx.x == 0) {
+      *result = 0;
+      post_to_host(post);
+    }
     return;
   }
   const int64_t base = (int64_t)tile * kRelTile + (int64_t)threadIdx.x * kRelItems;
@@ -86,10 +89,11 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
     const int64_t p = lookback_exclusive_prefix(st, tile, s_total, status);
     if (threadIdx.x == 0) {
       s_prefix = p;
-      if (tile == n_tiles - 1) *result = p + s_total;
+      if (tile == n_tiles - 1) st_relaxed64(result, p + s_total);
     }
   }
   __syncthreads();
+  if (threadIdx.x == 0) post_when_last(post, n_tiles);
   int64_t uid = s_prefix + local;
 #pragma unroll
   for (int j = 0; j < kRelItems; ++j) {
@@ -139,7 +143,8 @@ int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t 
 
 int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
                    void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
-                   int64_t* status, int64_t* result, cudaStream_t s, bool inserted, bool pdl) {
+                   int64_t* status, int64_t* result, cudaStream_t s, bool inserted, bool pdl,
+                   const HostPost* post) {
   RelTable t;
   if (int rc = relabel_table(ctx, numel_bound, &t, s)) return rc;
   t.newid = newid;
@@ -150,7 +155,8 @@ int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned
   if (!inserted)
     SHMT_CUDA_TRY(launch_kernel(pdl, relabel_insert_kernel, grid, kRelThreads, 0, s, ps, t, out_relabel, status));
   SHMT_CUDA_TRY(launch_kernel(pdl, relabel_compact_kernel, (unsigned)n_tiles, kRelThreads, 0, s, ps, t,
-                              (const void*)out_relabel, out_unique, st, ticket, status, result));
+                              (const void*)out_relabel, out_unique, st, ticket, status, result,
+                              post ? *post : HostPost{}));
   SHMT_CUDA_TRY(launch_kernel(pdl, relabel_remap_kernel, grid, kRelThreads, 0, s, ps, t, out_relabel));
   SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;
@@ -196,11 +202,18 @@ extern "C" int shmt_relabel(shmt_ctx* ctx, const void* const* parts, const int64
   // result words + tile flags to zero
   SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + (size_t)n_tiles * 4, s));
   int64_t* w = ctx->d_words();
+  // with a count to return, the compact kernel posts it and the call returns while the remap
+  // kernel runs; the next user of the context waits for that kernel first
+  HostPost post{};
+  if (n_unique_host) post = ctx_begin_post(ctx, w, 4, w + W_DONE);
   if (int rc = launch_relabel(ctx, ps, numel, newid, out_unique, out_relabel, st, w + W_TICKET,
-                              w + W_STATUS, w + W_RESULT, s))
+                              w + W_STATUS, w + W_RESULT, s, false, false,
+                              n_unique_host ? &post : nullptr))
     return rc;
   if (n_unique_host) {
-    if (int rc = ctx_fetch_words(ctx, s, "shmt_relabel")) return rc;
+    if (int rc = ctx_mark_tail(ctx, s)) return rc;
+    if (int rc = ctx_await_post(ctx, post, s)) return rc;
+    if (int rc = ctx_status_of_words(ctx, "shmt_relabel")) return rc;
     *n_unique_host = ctx->h_words[W_RESULT];
   }
   return SHMT_OK;

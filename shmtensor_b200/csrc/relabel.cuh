@@ -71,10 +71,12 @@ uint64_t relabel_capacity(int64_t numel_bound);
 // `pdl`: launch with programmatic stream serialization (see pdl_prologue in common.cuh).
 // `inserted`: the slots were already claimed and recorded in out_relabel by the producer
 // of the ids (the fused sampling kernel), so only the compact and remap kernels run.
+// `post`: the compact kernel hands the result words to the host as soon as the unique count is
+// final, i.e. while the remap kernel is still to run (it produces neither sizes nor errors).
 int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
                    void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
                    int64_t* status, int64_t* result, cudaStream_t s, bool inserted = false,
-                   bool pdl = false);
+                   bool pdl = false, const HostPost* post = nullptr);
 
 // Keys / first-index arrays of the context's table for `numel_bound` ids (reserving it).
 int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t s);

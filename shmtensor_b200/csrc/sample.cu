@@ -495,8 +495,9 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     if (int rc = relabel_table(ctx, cap[n_hops], &biggest, s)) return rc;
   }
   const void* cur_seeds = seeds;
+  HostPost post{};
   for (int h = 0; h < n_hops; ++h) {
-    int64_t* w = words + h * 8;  // [0] hop ticket, [1] nnz, [2] relabel ticket, [3] n_unique
+    int64_t* w = words + h * 8;  // [0] hop ticket, [1] nnz, [2] relabel ticket, [3] n_unique, [4] CTAs done
     HopJob job{};
     job.indptr = indptr;
     job.indptr64 = indptr_dtype == SHMT_I64;
@@ -543,15 +544,17 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     ps.start[1] = n_seeds;  // used for hop 0 only, whose seed count the host knows
     ps.dev_n0 = h == 0 ? nullptr : words + (h - 1) * 8 + 3;
     ps.dev_n1 = w + 1;
+    // every size and the status word are final once the last hop's ids are counted: that kernel
+    // hands them to the host, which returns while the last remap kernel is still running
+    if (h == n_hops - 1) post = ctx_begin_post(ctx, words, n_hops * 8 + 8, w + 4);
     if (int rc = launch_relabel(ctx, ps, cap[h + 1], newid, out_frontier[h], out_relabel[h],
                                 carve_tile_states(base + off_rel[h], rel_tiles[h]), w + 2, status,
-                                w + 3, s, fuse_insert, /*pdl=*/true))
+                                w + 3, s, fuse_insert, /*pdl=*/true, h == n_hops - 1 ? &post : nullptr))
       return rc;
     cur_seeds = out_frontier[h];
   }
-  const size_t n_words = (size_t)n_hops * 8 + 8;
-  SHMT_CUDA_TRY(cudaMemcpyAsync(ctx->h_words, words, n_words * sizeof(int64_t), cudaMemcpyDeviceToHost, s));
-  SHMT_CUDA_TRY(cudaStreamSynchronize(s));
+  if (int rc = ctx_mark_tail(ctx, s)) return rc;
+  if (int rc = ctx_await_post(ctx, post, s)) return rc;
   const int64_t st = ctx->h_words[n_hops * 8];
   if (st != DEV_OK) {
     ctx->table_dirty = true;

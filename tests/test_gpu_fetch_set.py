@@ -284,3 +284,31 @@ def test_config1_gather_from_shared_memory_tensor(capi):
 def test_no_bounded_wait_ran_out(capi):
     """Every fetch above went through the bulk-copy kernel; none of its bounded waits gave up."""
     assert capi.device_fault() == 0
+
+
+def test_cache_replace_keeps_fetch_exact(capi):
+    """Evict a quarter of the cached rows, admit other ids into their slots, fetch again."""
+    rng = np.random.default_rng(21)
+    n_rows, width, n_cached = 40_000, 100, 8_000
+    table_n = rng.standard_normal((n_rows, width)).astype(np.float32)
+    table = torch.from_numpy(table_n.copy())
+    capi.pin_memory(table)
+    try:
+        perm = rng.permutation(n_rows)
+        cached, others = perm[:n_cached].copy(), perm[n_cached:]
+        gpu_rows = torch.from_numpy(table_n[cached]).cuda()
+        hmap = capi.CUCOStaticHashmap(torch.from_numpy(cached).cuda(),
+                                      torch.arange(n_cached, dtype=torch.int32, device="cuda"), 0.5)
+        evict, admit = cached[:2000], others[:2000]
+        assert capi.cache_replace(table, gpu_rows, hmap, torch.from_numpy(evict).cuda(),
+                                  torch.from_numpy(admit).cuda()) == 2000
+        assert hmap.size() == n_cached
+        ids = torch.from_numpy(rng.integers(0, n_rows, size=50_000)).cuda()
+        out = capi.cache_fetch(table, gpu_rows, ids, hmap)
+        assert torch.equal(out.cpu(), table[ids.cpu()])
+        # the admitted ids are served from HBM now: poison the host copy and fetch them
+        slots = hmap.query(torch.from_numpy(admit).cuda())
+        assert (slots >= 0).all() and (hmap.query(torch.from_numpy(evict).cuda()) == -1).all()
+        assert torch.equal(gpu_rows[slots.long()].cpu(), torch.from_numpy(table_n[admit]))
+    finally:
+        capi.unpin_memory(table)

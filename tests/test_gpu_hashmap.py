@@ -107,3 +107,60 @@ def test_config5_map_full_size(capi):
     assert (req[perm][~hit] >= (1 << 40)).all()
     # and every key maps to its own slot
     assert torch.equal(m.query(keys), slots)
+
+
+@pytest.mark.parametrize("kd,vd", [("int64", "int64"), ("int32", "int32"), ("int64", "int32")])
+def test_erase_against_oracle(capi, kd, vd):
+    rng = np.random.default_rng(11)
+    hi = 1 << (30 if kd == "int32" else 40)
+    keys = rng.choice(hi, size=20_000, replace=False).astype(np.int64)
+    vals = rng.integers(0, 1 << 30, size=keys.size).astype(np.int64)
+    m = capi.CUCOStaticHashmap(torch.from_numpy(keys).cuda().to(DT[kd]),
+                               torch.from_numpy(vals).cuda().to(DT[vd]), 0.5)
+    table = oracle.hashmap_build(keys, vals)
+    # erase a third of the keys, some absent ones and one key listed twice
+    gone = np.concatenate([keys[::3], rng.integers(hi, 2 * hi - 1, size=500) if kd == "int64"
+                           else np.array([], dtype=np.int64)])
+    got = m.erase(torch.from_numpy(gone).cuda().to(DT[kd]))
+    want = oracle.hashmap_erase(table, gone)
+    assert got.dtype == DT[vd] and np.array_equal(got.cpu().numpy().astype(np.int64), want)
+    assert m.size() == len(table)
+    twice = torch.from_numpy(np.array([keys[1], keys[1]])).cuda().to(DT[kd])
+    assert sorted(m.erase(twice).cpu().tolist()) == [-1, table.pop(int(keys[1]))]
+    probe = np.concatenate([keys, gone])
+    got = m.query(torch.from_numpy(probe).cuda()).cpu().numpy().astype(np.int64)
+    assert np.array_equal(got, oracle.hashmap_query(table, probe))
+    # reserved keys are no-ops
+    assert m.erase(torch.tensor([-1, -2], device="cuda").to(DT[kd])).cpu().tolist() == [-1, -1]
+    assert m.query(torch.tensor([-2], device="cuda")).cpu().tolist() == [-1]
+
+
+def test_erased_slots_are_taken_again(capi):
+    """Forty rounds of evicting half of the keys and admitting as many new ones into a map with
+    two slots per key: without reuse of erased slots the table would fill up and overflow."""
+    rng = np.random.default_rng(12)
+    n = 50_000
+    pool = rng.choice(1 << 40, size=n * 25, replace=False).astype(np.int64)
+    live = pool[:n].copy()
+    vals = np.arange(n, dtype=np.int64)
+    m = capi.CUCOStaticHashmap(torch.from_numpy(live).cuda(), torch.from_numpy(vals).cuda(), 0.5)
+    table = oracle.hashmap_build(live, vals)
+    nxt = n
+    for r in range(40):
+        out_idx = rng.choice(n, size=n // 2, replace=False)
+        freed = m.erase(torch.from_numpy(live[out_idx]).cuda())
+        assert np.array_equal(freed.cpu().numpy(), oracle.hashmap_erase(table, live[out_idx]))
+        fresh = pool[nxt:nxt + n // 2]
+        nxt += n // 2
+        m.insert(torch.from_numpy(fresh).cuda(), freed)          # new ids take the freed values
+        table.update(oracle.hashmap_build(fresh, freed.cpu().numpy()))
+        live[out_idx] = fresh
+        assert m.size() == n
+    probe = np.concatenate([live, pool[:n]])
+    got = m.query(torch.from_numpy(probe).cuda()).cpu().numpy()
+    assert np.array_equal(got, oracle.hashmap_query(table, probe))
+    # duplicates inside one insert batch still land in one slot
+    dup = torch.from_numpy(np.repeat(pool[-1000:], 4)).cuda()
+    m.erase(torch.from_numpy(live[:2000]).cuda())
+    m.insert(dup, torch.arange(dup.numel(), device="cuda"))
+    assert m.size() == n - 2000 + 1000

@@ -78,6 +78,13 @@ def test_hashmap_golden():
     assert oracle.hashmap_query(table, wide, np.int64)[0] == -1
 
 
+def test_hashmap_erase_contract():
+    table = oracle.hashmap_build(np.arange(10), np.arange(10) * 7)
+    assert oracle.hashmap_erase(table, np.array([3, 99, 3, 0])).tolist() == [21, -1, -1, 0]
+    assert oracle.hashmap_query(table, np.array([0, 3, 4])).tolist() == [-1, -1, 28]
+    assert len(table) == 8
+
+
 def test_fetch_set_round_trip():
     g = load_golden("fetch_set.json")
     rng = np.random.default_rng(g["multi_dim_seed"])
