@@ -1063,6 +1063,25 @@ def run_update(args) -> None:
         assert torch.equal(r_ours, r_ref), "map query differs from the reference's"
         line["map_build_query"]["reference_cuda"] = {"build_ms": round(rb_ms, 4), "query_ms": round(rq_ms, 4),
                                                      "what": "the reference's wrapper over a stand-in for cuCollections"}
+    # cache turnover on the finished map: evict 10 % of the ids, admit as many new ones into the freed
+    # rows (erased slots are taken again, so the table never fills); then the same back again
+    n_turn = U_KEYS // 10
+    evict, admit = keys[:n_turn].contiguous(), keys[:n_turn] + (1 << 41)
+    t_er = t_ad = 0.0
+    for a, b in ((evict, admit), (admit, evict), (evict, admit), (admit, evict)):
+        t0 = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        t0[0].record(stream)
+        freed = m.erase(a)
+        t0[1].record(stream)
+        m.insert(b, freed)
+        t0[2].record(stream)
+        torch.cuda.synchronize()
+        t_er, t_ad = t0[0].elapsed_time(t0[1]), t0[1].elapsed_time(t0[2])
+        assert m.size() == U_KEYS and torch.equal(m.query(b), freed) and bool((m.query(a) == -1).all())
+    assert torch.equal(m.query(keys), slots)
+    line["cache_turnover"] = {"ids": n_turn, "erase_ms": round(t_er, 4), "admit_ms": round(t_ad, 4),
+                              "what": "shmt_map_erase of 10 % of the keys, then shmt_map_insert of as many new ids "
+                                      "with the freed row numbers (host-synchronous calls, device time)"}
     # algorithmic bytes: insert+set per key 8 (key) + 4 (slot) + 16 (claim) + row read + row written;
     # lookup per key 8 + 12 + 4
     b_ins = U_KEYS * (8 + 4 + 16 + 2 * row_bytes)

@@ -56,6 +56,9 @@ struct HopJob {
   unsigned* rel_first;
   uint32_t rel_mask;
   void* rel_out;
+  // Single-hop call with a host result: the CTA that finishes its bookkeeping last hands the
+  // result words to the host, which returns while the rows are still being written.
+  HostPost post;
 };
 
 // indptr[i] and indptr[i+1] with one load when the pair is naturally aligned (one request on
@@ -105,7 +108,8 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
   if (tile >= n_tiles) {  // the grid is sized for the largest n the caller allows
     if (n == 0 && tile == 0 && tid == 0) {
       store_int(job.sub_indptr, job.indptr64, 0, 0);
-      *job.result = 0;
+      st_relaxed64(job.result, 0);
+      post_to_host(job.post);
     }
     return;
   }
@@ -232,7 +236,11 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
   }
   if (tile == n_tiles - 1 && tid == 0) {
     store_int(job.sub_indptr, job.indptr64, n, prefix + s_total);
-    *job.result = prefix + s_total;
+    st_relaxed64(job.result, prefix + s_total);
+  }
+  if (job.post.host) {  // uniform over the grid; the fused path (which may still flag the relabel table) never posts here
+    __syncthreads();
+    if (tid == 0) post_when_last(job.post, n_tiles);
   }
 
   // ---- 4. output
@@ -419,6 +427,7 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const v
   job.status = ctx->d_words() + W_STATUS;
   job.result = ctx->d_words() + W_RESULT;
   job.n_dev = nullptr;
+  if (nnz_host) job.post = ctx_begin_post(ctx, ctx->d_words(), 4, ctx->d_words() + W_DONE);
   SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + (size_t)n_tiles * 4, s));
   if (indices_dtype == SHMT_I64)
     launch_hop<long long>(job, n_tiles, s);
@@ -426,7 +435,9 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const v
     launch_hop<int>(job, n_tiles, s);
   SHMT_CUDA_TRY(cudaGetLastError());
   if (nnz_host) {
-    if (int rc = ctx_fetch_words(ctx, s, "shmt_sample_hop")) return rc;
+    if (int rc = ctx_mark_tail(ctx, s)) return rc;
+    if (int rc = ctx_await_post(ctx, job.post, s)) return rc;
+    if (int rc = ctx_status_of_words(ctx, "shmt_sample_hop")) return rc;
     *nnz_host = ctx->h_words[W_RESULT];
   }
   return SHMT_OK;
