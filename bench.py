@@ -377,7 +377,8 @@ def run_ours(args) -> None:
                    "hit_rate": round(hit_rate, 4),
                    "l2": "inputs larger than L2: 192 MB cached rows + 200 MB output per launch, "
                          f"{N_BATCHES} distinct query batches rotated",
-                   "partition": "single GPU" if world == 1 else f"hash-partitioned over {world} GPUs, NVLink P2P loads"},
+                   "partition": "single GPU" if world == 1 else
+                   f"hash-partitioned over {world} GPUs, NVLink P2P loads; the {pcache.replicated} hottest rows on every GPU"},
         "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": BATCH * 8,
                 "d2h_bytes_per_step": DIM * 4, "ms_per_step": round(e2e_ms, 5),
                 "wall_ms_per_step": round(e2e_wall_ms, 5)},
@@ -406,15 +407,20 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_hit, peer_ms = t.tolist()
         peer_gbs = (256 << 20) / (peer_ms * 1e6)
-        remote_bytes = BATCH * ROW_BYTES * (world - 1) / world
+        # rows that really came from a peer (the hottest ids are replicated on every rank)
+        n_remote = sum(int(((pcache.directory.query(b) >> 40) != rank).sum().item()) for b in hot_batches) / 4
+        t = torch.tensor([n_remote], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        remote_bytes = t.item() * ROW_BYTES
         line["roofline_all_hit_partitioned"] = {
             "bound": "nvlink", "kernel_ms": round(ms_hit, 5),
             "aggregate_gbs": round(world * BATCH * ROW_BYTES / (ms_hit * 1e6), 1),
             "achieved": round(remote_bytes / (ms_hit * 1e6), 1), "peak": round(peer_gbs, 1), "unit": "GB/s",
             "frac": round(remote_bytes / (ms_hit * 1e6) / peer_gbs, 4),
             "peak_source": "streaming read kernel over the next rank's IPC-mapped buffer, measured in this run",
-            "what": "ids uniform over the cached set: 1/N of the rows local, the rest read from peers over NVLink; "
-                    "achieved = remote row bytes per rank / slowest rank's kernel time"}
+            "what": "ids uniform over the cached set: about 1/N of the rows local, the rest read from peers over "
+                    "NVLink; achieved = remote row bytes per rank (the least over ranks) / slowest rank's kernel time",
+            "replicated_rows_per_gpu": pcache.replicated}
         # the batched alternative (NCCL all-to-all of ids, then of rows) on the same batches
         a2a = pcache.fetch_alltoall(batches[0])
         assert torch.equal(a2a.view(torch.int32), fetch(batches[0]).view(torch.int32)), "all-to-all route differs"
@@ -431,6 +437,30 @@ def run_ours(args) -> None:
                                   "p2p_mixed_ms": round(ms_per_step, 4), "p2p_all_hit_ms": round(ms_hit, 4),
                                   "what": "PartitionedFeatureCache.fetch_alltoall (ids bucketed by owner, NCCL all-to-all of "
                                           "ids and of rows, misses read locally) against the fused peer-load kernel"}
+        # the other way to spend N GPUs: every GPU keeps the cache budget of the 1-GPU run (480,000 rows),
+        # so the partitioned cache holds N times as many ids and fewer rows cross the host link
+        n_grown = min(world * n_cached, ROWS)
+        grown = PartitionedFeatureCache(table, torch.from_numpy(ranking[:n_grown].copy()), load_factor=LOAD_FACTOR)
+        got = grown.fetch(batches[0])
+        assert torch.equal(got.cpu().view(torch.int32),
+                           torch.index_select(table, 0, batches_host[0]).view(torch.int32)), "grown cache differs"
+        del got
+        grown_hits = sum(int((grown.directory.query(b) >= 0).sum().item()) for b in batches) / (N_BATCHES * BATCH)
+        for b in batches[:3]:
+            grown.fetch(b)
+        dist.barrier()
+        ms_grown = time_launches(lambda c=[0]: (grown.fetch(batches[c[0] % N_BATCHES]), c.__setitem__(0, c[0] + 1)),
+                                 40, stream)
+        t = torch.tensor([ms_grown], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_grown = t.item()
+        line["cache_budget_per_gpu"] = {
+            "cached_rows_total": n_grown, "cached_rows_per_gpu": n_grown // world, "hit_rate": round(grown_hits, 4),
+            "ms_per_step": round(ms_grown, 5), "value": round(world * BATCH * ROW_BYTES / (ms_grown * 1e6), 2),
+            "unit": UNIT,
+            "what": "same batches; every GPU contributes the 1-GPU cache budget, so the partitioned cache grows "
+                    "with N (the headline keeps the total cached set fixed and splits it)"}
+        grown.close()
         torch.cuda.synchronize()
         dist.barrier()
         for p_ in opened:
