@@ -167,6 +167,38 @@ class PartitionedFeatureCache:
                                          capi._ptr(out), capi._stream(ids.device)))
         return out
 
+    def replace(self, evict_ids: torch.Tensor, admit_ids: torch.Tensor) -> int:
+        """Turn the cache over in place: ``evict_ids`` leave it, ``admit_ids`` (distinct, not
+        cached) take their rows, wherever those are: the directory names the owner of every id,
+        so an admitted id simply inherits the (owner, row) of an evicted one.  Every rank makes
+        the same call (a collective when there are several ranks, with no fetch in flight);
+        each updates its own directory and fills the freed rows it owns from the host table.
+        Ids held on every rank (the replicated hottest rows) cannot be evicted.  Admits at most
+        as many ids as rows were freed, in order; returns how many."""
+        dev = self.device
+        evict = evict_ids.to(dev, torch.int64).contiguous()
+        admit = admit_ids.to(dev, torch.int64).contiguous()
+        low = (1 << OWNER_SHIFT) - 1
+        if self.replicated:
+            seen = self.directory.query(evict)
+            mine = (seen >> OWNER_SHIFT) == self.rank
+            if bool((mine & ((seen & low) >= self.counts[self.rank]) & (seen >= 0)).any()):
+                raise RuntimeError("PartitionedFeatureCache.replace: a replicated id cannot be evicted")
+        freed = self.directory.erase(evict)
+        freed = freed[freed >= 0]
+        n = min(int(freed.numel()), int(admit.numel()))
+        if n:
+            admit, freed = admit[:n].contiguous(), freed[:n].contiguous()
+            self.directory.insert(admit, freed)
+            here = (freed >> OWNER_SHIFT) == self.rank
+            if bool(here.any()):
+                rows = (freed[here] & low).contiguous()
+                capi.uva_set(self.shard, rows, capi.uva_fetch(self.host_table, admit[here].contiguous()))
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(self.group)  # no rank reads a freed row of a peer before its owner refilled it
+        return n
+
     def fetch_alltoall(self, ids: torch.Tensor) -> torch.Tensor:
         """The same result by the batched route: ids are bucketed by owner, exchanged with an
         NCCL all-to-all, gathered on the owner, and the rows come back with a second

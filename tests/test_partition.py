@@ -115,6 +115,14 @@ def test_partitioned_fetch_single_rank_is_bit_exact():
         out2 = pc.fetch(cached[:100].cuda())
         assert torch.equal(out2.cpu(), table[cached[:100]] + 1.0)
         assert capi.device_fault() == 0
+        # turnover in place: a fifth of the cached ids leave, other ids take their rows
+        pc.shard.copy_(table[cached].cuda())
+        others = torch.from_numpy(np.setdiff1d(np.arange(50_000), cached.numpy())[:2_000])
+        assert pc.replace(cached[:2_000], others) == 2_000 and pc.directory.size() == 10_000
+        assert bool((pc.directory.query(cached[:2_000].cuda()) == -1).all())
+        rows = pc.directory.query(others.cuda())
+        assert bool((rows >= 0).all()) and torch.equal(pc.shard[rows].cpu(), table[others])
+        assert torch.equal(pc.fetch(q).cpu().view(torch.int32), table[q.cpu()].view(torch.int32))
         pc.close()
     finally:
         capi.unpin_memory(table)
