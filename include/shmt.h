@@ -162,7 +162,7 @@ int shmt_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
  * device memory, a serving loop with a hard latency bound (cudaMalloc and cudaFree
  * stall the whole device, and a context's scratch may have to grow), or any code
  * that runs where the CUDA allocator may not be entered.  The look-back state lives
- * in a fixed array inside the library (about 160 KB per GPU, held from library load
+ * in a fixed array inside the library (about 33 KB per GPU, held from library load
  * to process exit), so the call needs no context and never calls cudaMalloc or
  * cudaFree: it is one memset of that state plus one kernel on `stream`.
  * Limit: n <= 16,777,216 items; larger inputs are refused with SHMT_ERR_INVALID.

@@ -1,42 +1,63 @@
 // Single-pass prefix hand-off between CTAs (decoupled look-back, Merrill &
 // Garland 2016), shared by the scan, the sampling hop and relabel.
 //
-// Tile t publishes its local aggregate (flag 1) as soon as it has it, then looks
-// back over its predecessors 32 at a time until it meets one whose inclusive
-// prefix is known (flag 2), and finally publishes its own inclusive prefix.
-// Tiles take their index from an atomic ticket, so every predecessor of a
-// running tile has already started: no wait depends on an unscheduled CTA.
-// Every wait is bounded; a tile that gives up records DEV_TIMEOUT and carries on
-// with what it has, so the kernel always terminates.
+// Every tile owns one 16-byte descriptor {value, state}, read and written as a single 128-bit
+// access, so a reader always sees a value together with the state it belongs to.  Tile t
+// publishes its local aggregate (state 1) as soon as it has it, then looks back over its
+// predecessors 32 at a time, one load per predecessor, until it meets one whose inclusive prefix
+// is known (state 2), and finally replaces its own descriptor by its inclusive prefix.
+// Tiles take their index from an atomic ticket, so every predecessor of a running tile has
+// already started: no wait depends on an unscheduled CTA.
+// Every wait is bounded; a tile that gives up records DEV_TIMEOUT and carries on with what it
+// has, so the kernel always terminates.
 #pragma once
 
 #include "common.cuh"
 
 namespace shmt {
 
-struct TileStates {
-  uint32_t* flag;  // 0 = nothing yet, 1 = aggregate valid, 2 = inclusive valid
-  int64_t* agg;
-  int64_t* inc;
+struct __align__(16) TileDesc {
+  long long value;
+  unsigned long long state;  // 0 = nothing yet, 1 = value is the aggregate, 2 = the inclusive prefix
 };
 
-constexpr size_t tile_state_bytes(int64_t n_tiles) {
-  // flags padded so the two int64 arrays stay 8-byte aligned
-  return ((size_t)n_tiles * 4 + 7) / 8 * 8 + (size_t)n_tiles * 16;
-}
+struct TileStates {
+  TileDesc* d;
+};
 
-inline TileStates carve_tile_states(char* base, int64_t n_tiles) {
-  TileStates st;
-  st.flag = reinterpret_cast<uint32_t*>(base);
-  char* p = base + ((size_t)n_tiles * 4 + 7) / 8 * 8;
-  st.agg = reinterpret_cast<int64_t*>(p);
-  st.inc = st.agg + n_tiles;
-  return st;
+// Bytes of look-back state for n_tiles tiles; they must be zero when the kernel starts.
+constexpr size_t tile_state_bytes(int64_t n_tiles) { return (size_t)n_tiles * sizeof(TileDesc); }
+
+inline TileStates carve_tile_states(char* base, int64_t /*n_tiles*/) {  // base: 16-byte aligned
+  return TileStates{reinterpret_cast<TileDesc*>(base)};
 }
 
 #ifdef __CUDACC__
 
 constexpr int kLookbackSpinLimit = 1 << 22;
+constexpr unsigned long long kTileAggregate = 1, kTileInclusive = 2;
+
+__device__ __forceinline__ void st_desc(TileDesc* p, long long value, unsigned long long state) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b128 t;\n\t"
+      "mov.b128 t, {%1, %2};\n\t"
+      "st.relaxed.gpu.global.b128 [%0], t;\n\t"
+      "}" ::"l"(p), "l"(value), "l"(state)
+      : "memory");
+}
+
+__device__ __forceinline__ void ld_desc(const TileDesc* p, long long* value, unsigned long long* state) {
+  asm volatile(
+      "{\n\t"
+      ".reg .b128 t;\n\t"
+      "ld.relaxed.gpu.global.b128 t, [%2];\n\t"
+      "mov.b128 {%0, %1}, t;\n\t"
+      "}"
+      : "=l"(*value), "=l"(*state)
+      : "l"(p)
+      : "memory");
+}
 
 // Ticketed tile index for the calling CTA (call from every thread).
 __device__ __forceinline__ int take_tile(int64_t* ticket, int* smem_slot) {
@@ -53,52 +74,42 @@ __device__ __forceinline__ int64_t lookback_exclusive_prefix(const TileStates& s
                                                              int spin_limit = kLookbackSpinLimit) {
   const unsigned lane = threadIdx.x & 31;
   if (tile == 0) {
-    if (lane == 0) {
-      st_relaxed64(st.inc, aggregate);
-      st_release(st.flag, 2u);
-    }
+    if (lane == 0) st_desc(st.d, aggregate, kTileInclusive);
     return 0;
   }
-  if (lane == 0) {
-    st_relaxed64(st.agg + tile, aggregate);
-    st_release(st.flag + tile, 1u);
-  }
+  if (lane == 0) st_desc(st.d + tile, aggregate, kTileAggregate);
   int64_t prefix = 0;
   int base = tile - 1;
   while (true) {
     const int t = base - (int)lane;
-    uint32_t f = 2u;
-    int64_t v = 0;
+    unsigned long long f = kTileInclusive;
+    long long v = 0;
     if (t >= 0) {
       int spins = 0;
-      f = ld_acquire(st.flag + t);
-      while (f == 0u && spins < spin_limit) {
-        __nanosleep(32);
-        f = ld_acquire(st.flag + t);
+      ld_desc(st.d + t, &v, &f);
+      while (f == 0ULL && spins < spin_limit) {
+        __nanosleep(20);
+        ld_desc(st.d + t, &v, &f);
         ++spins;
       }
-      if (f == 0u) {
+      if (f == 0ULL) {
         atomicMax(reinterpret_cast<unsigned long long*>(status_word),
                   (unsigned long long)DEV_TIMEOUT);
-        f = 2u;  // give up: treat as a known (zero) prefix so the chain ends here
-      } else {
-        v = ld_relaxed64((f == 2u ? st.inc : st.agg) + t);
+        f = kTileInclusive;  // give up: treat as a known (zero) prefix so the chain ends here
+        v = 0;
       }
     }
-    const unsigned known = __ballot_sync(0xffffffffu, f == 2u);
+    const unsigned known = __ballot_sync(0xffffffffu, f == kTileInclusive);
     // lanes at or before the nearest tile with a known inclusive prefix contribute
     const unsigned upto = known ? (unsigned)(__ffs(known) - 1) : 31u;
-    int64_t part = lane <= upto ? v : 0;
+    int64_t part = lane <= upto ? (int64_t)v : 0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
     prefix += part;
     if (known) break;
     base -= 32;
   }
-  if (lane == 0) {
-    st_relaxed64(st.inc + tile, prefix + aggregate);
-    st_release(st.flag + tile, 2u);
-  }
+  if (lane == 0) st_desc(st.d + tile, prefix + aggregate, kTileInclusive);
   return prefix;
 }
 

@@ -45,7 +45,7 @@ relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* sta
   const uint32_t mask = relabel_mask_for(numel, t.mask);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
-    const uint32_t pos = relabel_insert_one(t.keys, t.first, mask, part_elem(ps, i), (unsigned)i, status);
+    const uint32_t pos = relabel_insert_one(t.slots, mask, part_elem(ps, i), (unsigned)i, status);
     store_int(out, ps.is64, i, (int64_t)pos);
   }
 }
@@ -80,7 +80,7 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
     is_first[j] = false;
     if (i < numel) {
       pos[j] = (uint32_t)load_int(slot_of, ps.is64, i);
-      is_first[j] = __ldcg(t.first + pos[j]) == (unsigned)i;
+      is_first[j] = __ldcg(&t.slots[pos[j]].first) == (unsigned)i;
     }
     cnt += is_first[j];
   }
@@ -99,7 +99,7 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
   for (int j = 0; j < kRelItems; ++j) {
     if (is_first[j]) {
       store_int(unique, ps.is64, uid, part_elem(ps, base + j));
-      t.newid[pos[j]] = (unsigned)uid;
+      t.slots[pos[j]].newid = (unsigned)uid;
       ++uid;
     }
   }
@@ -114,17 +114,17 @@ relabel_remap_kernel(Parts ps, RelTable t, void* out) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
     const int64_t pos = ps.is64 ? reinterpret_cast<const long long*>(out)[i]
                                 : (int64_t) reinterpret_cast<const int*>(out)[i];
-    store_int(out, ps.is64, i, (int64_t)__ldcg(t.newid + pos));
-    // leave the slot empty for the next call (every duplicate writes the same values)
-    t.keys[pos] = kEmptyKey;
-    t.first[pos] = 0xFFFFFFFFu;
+    store_int(out, ps.is64, i, (int64_t)__ldcg(&t.slots[pos].newid));
+    // leave the slot empty for the next call (every duplicate writes the same values); the new id
+    // stays, because another element of the same id may not have read it yet
+    t.slots[pos].key = kEmptyKey;
+    t.slots[pos].first = 0xFFFFFFFFu;
   }
 }
 
-// Table for up to `numel_bound` ids at load <= 0.5.  Keys and first-index words live in the
-// context's all-ones block (whatever the capacity, the block is all ones between calls, so
-// regions of different capacities may overlap freely); the slot -> new-id words need no
-// initial value and come from ordinary scratch (`newid`, 4 * relabel_capacity bytes).
+// Table for up to `numel_bound` ids at load <= 0.5, in the context's block whose keys and
+// first-index words are all ones between calls (whatever the capacity, so regions of different
+// capacities may overlap freely); the new-id words need no initial value.
 uint64_t relabel_capacity(int64_t numel_bound) {
   uint64_t cap = 64;
   while (cap < (uint64_t)numel_bound * 2) cap <<= 1;
@@ -133,21 +133,17 @@ uint64_t relabel_capacity(int64_t numel_bound) {
 
 int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t s) {
   const uint64_t cap = relabel_capacity(numel_bound);
-  if (int rc = ctx_reserve_table(ctx, cap * 12, s)) return rc;
-  t->keys = reinterpret_cast<long long*>(ctx->table);
-  t->first = reinterpret_cast<unsigned*>(ctx->table + cap * 8);
-  t->newid = nullptr;
+  if (int rc = ctx_reserve_table(ctx, cap * sizeof(RelSlot), s)) return rc;
+  t->slots = reinterpret_cast<RelSlot*>(ctx->table);
   t->mask = (uint32_t)(cap - 1);
   return SHMT_OK;
 }
 
-int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
-                   void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
+int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
                    int64_t* status, int64_t* result, cudaStream_t s, bool inserted, bool pdl,
                    const HostPost* post) {
   RelTable t;
   if (int rc = relabel_table(ctx, numel_bound, &t, s)) return rc;
-  t.newid = newid;
   const int64_t n_tiles = (numel_bound + kRelTile - 1) / kRelTile;
   int64_t blocks = (numel_bound + kRelThreads - 1) / kRelThreads;
   const int64_t cap_blocks = (int64_t)sm_count() * 16;
@@ -196,17 +192,16 @@ extern "C" int shmt_relabel(shmt_ctx* ctx, const void* const* parts, const int64
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t n_tiles = (numel + kRelTile - 1) / kRelTile;
   const size_t states = (tile_state_bytes(n_tiles) + 255) & ~(size_t)255;
-  if (int rc = ctx_reserve(ctx, states + relabel_capacity(numel) * 4)) return rc;
+  if (int rc = ctx_reserve(ctx, states)) return rc;
   TileStates st = carve_tile_states(ctx->region(), n_tiles);
-  unsigned* newid = reinterpret_cast<unsigned*>(ctx->region() + states);
-  // result words + tile flags to zero
-  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + (size_t)n_tiles * 4, s));
+  // result words + tile descriptors to zero
+  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + tile_state_bytes(n_tiles), s));
   int64_t* w = ctx->d_words();
   // with a count to return, the compact kernel posts it and the call returns while the remap
   // kernel runs; the next user of the context waits for that kernel first
   HostPost post{};
   if (n_unique_host) post = ctx_begin_post(ctx, w, 4, w + W_DONE);
-  if (int rc = launch_relabel(ctx, ps, numel, newid, out_unique, out_relabel, st, w + W_TICKET,
+  if (int rc = launch_relabel(ctx, ps, numel, out_unique, out_relabel, st, w + W_TICKET,
                               w + W_STATUS, w + W_RESULT, s, false, false,
                               n_unique_host ? &post : nullptr))
     return rc;

@@ -23,11 +23,17 @@ struct Parts {
   const int64_t* dev_n1;
 };
 
+// One 16-byte slot per distinct id, so that claiming the key and recording the first occurrence
+// touch one sector, as do reading the new id and emptying the slot.
+struct __align__(16) RelSlot {
+  long long key;   // -1 = empty
+  unsigned first;  // smallest input index holding the key (all ones = none)
+  unsigned newid;  // dense id of the key (written by the compact kernel; needs no initial value)
+};
+
 struct RelTable {
-  long long* keys;  // cap entries, -1 = empty
-  unsigned* first;  // cap entries, smallest input index holding the key (all ones = none)
-  unsigned* newid;  // cap entries, dense id of the key (written by the compact kernel)
-  uint32_t mask;    // cap - 1
+  RelSlot* slots;  // cap entries
+  uint32_t mask;   // cap - 1
 };
 
 #ifdef __CUDACC__
@@ -40,15 +46,14 @@ __device__ __forceinline__ uint32_t relabel_mask_for(int64_t numel, uint32_t tab
 
 // Claim (or find) the slot of `key`, record `i` as a candidate first occurrence, and return
 // the slot.  Linear probing from mix64(key) & mask; bounded by the table size.
-__device__ __forceinline__ uint32_t relabel_insert_one(long long* keys, unsigned* first,
-                                                       uint32_t mask, long long key, unsigned i,
-                                                       int64_t* status) {
+__device__ __forceinline__ uint32_t relabel_insert_one(RelSlot* slots, uint32_t mask, long long key,
+                                                       unsigned i, int64_t* status) {
   uint32_t pos = (uint32_t)mix64((uint64_t)key) & mask;
   uint32_t steps = 0;
   while (true) {
-    long long cur = __ldcg(keys + pos);
+    long long cur = __ldcg(&slots[pos].key);
     if (cur == kEmptyKey)
-      cur = (long long)atomicCAS(reinterpret_cast<unsigned long long*>(keys + pos),
+      cur = (long long)atomicCAS(reinterpret_cast<unsigned long long*>(&slots[pos].key),
                                  (unsigned long long)kEmptyKey, (unsigned long long)key);
     if (cur == kEmptyKey || cur == key) break;
     pos = (pos + 1) & mask;
@@ -57,7 +62,7 @@ __device__ __forceinline__ uint32_t relabel_insert_one(long long* keys, unsigned
       break;
     }
   }
-  atomicMin(first + pos, i);
+  atomicMin(&slots[pos].first, i);
   return pos;
 }
 #endif
@@ -66,19 +71,17 @@ __device__ __forceinline__ uint32_t relabel_insert_one(long long* keys, unsigned
 uint64_t relabel_capacity(int64_t numel_bound);
 
 // Queue the three relabel kernels.  `numel_bound` >= the real element count sizes the
-// table and the grids; `newid` is scratch of 4 * relabel_capacity(numel_bound) bytes;
-// ticket/status/result are zeroed device words.
+// table and the grids; ticket/status/result are zeroed device words.
 // `pdl`: launch with programmatic stream serialization (see pdl_prologue in common.cuh).
 // `inserted`: the slots were already claimed and recorded in out_relabel by the producer
 // of the ids (the fused sampling kernel), so only the compact and remap kernels run.
 // `post`: the compact kernel hands the result words to the host as soon as the unique count is
 // final, i.e. while the remap kernel is still to run (it produces neither sizes nor errors).
-int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, unsigned* newid,
-                   void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
+int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
                    int64_t* status, int64_t* result, cudaStream_t s, bool inserted = false,
                    bool pdl = false, const HostPost* post = nullptr);
 
-// Keys / first-index arrays of the context's table for `numel_bound` ids (reserving it).
+// The context's table for `numel_bound` ids (reserving it).
 int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t s);
 
 }  // namespace shmt

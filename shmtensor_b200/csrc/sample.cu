@@ -51,9 +51,8 @@ struct HopJob {
   // Fused relabel insert (multi-hop path): the kernel also claims a relabel-table slot for
   // every seed and every sampled neighbour, at its index in [seeds | neighbours], and
   // records the slot in rel_out -- the work of relabel's first kernel, done while this
-  // kernel would otherwise wait on memory.  rel_keys == nullptr: off.
-  long long* rel_keys;
-  unsigned* rel_first;
+  // kernel would otherwise wait on memory.  rel_slots == nullptr: off.
+  RelSlot* rel_slots;
   uint32_t rel_mask;
   void* rel_out;
   // Single-hop call with a host result: the CTA that finishes its bookkeeping last hands the
@@ -221,14 +220,14 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
     __syncthreads();
   }
   const int64_t prefix = s_prefix;
-  const bool relabel = job.rel_keys != nullptr;
+  const bool relabel = job.rel_slots != nullptr;
   // ids are hashed into as much of the table as n seeds with k picks each can need
   const uint32_t rel_mask = relabel ? relabel_mask_for(n * (1 + k), job.rel_mask) : 0u;
   for (int j = (int)tid; j < rows; j += kHopThreads) {
     store_int(job.sub_indptr, job.indptr64, first + j, prefix + s_off[j]);
     if (relabel) {
       const int64_t i = first + j;
-      const uint32_t pos = relabel_insert_one(job.rel_keys, job.rel_first, rel_mask,
+      const uint32_t pos = relabel_insert_one(job.rel_slots, rel_mask,
                                               load_int(job.seeds, job.seeds64, i), (unsigned)i,
                                               job.status);
       store_int(job.rel_out, sizeof(IxT) == 8, i, (int64_t)pos);
@@ -252,7 +251,7 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
         const int64_t o = prefix + s_off[j] + gl;
         out_all[o] = v[u];
         if (relabel) {
-          const uint32_t pos = relabel_insert_one(job.rel_keys, job.rel_first, rel_mask,
+          const uint32_t pos = relabel_insert_one(job.rel_slots, rel_mask,
                                                   (long long)v[u], (unsigned)(n + o), job.status);
           store_int(job.rel_out, sizeof(IxT) == 8, n + o, (int64_t)pos);
         }
@@ -428,7 +427,7 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const v
   job.result = ctx->d_words() + W_RESULT;
   job.n_dev = nullptr;
   if (nnz_host) job.post = ctx_begin_post(ctx, ctx->d_words(), 4, ctx->d_words() + W_DONE);
-  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + (size_t)n_tiles * 4, s));
+  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + tile_state_bytes(n_tiles), s));
   if (indices_dtype == SHMT_I64)
     launch_hop<long long>(job, n_tiles, s);
   else
@@ -468,14 +467,12 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
   DeviceGuard guard(ctx->device);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  // worst-case frontier sizes and the scratch plan: [words][per hop: sample tiles | relabel tiles][new-id]
+  // worst-case frontier sizes and the scratch plan: [words][per hop: sample tiles | relabel tiles]
   int64_t cap[kMaxHops + 1], hop_tiles[kMaxHops], rel_tiles[kMaxHops];
   int spt[kMaxHops];
   size_t off_hop[kMaxHops], off_rel[kMaxHops];
   cap[0] = n_seeds;
   size_t cursor = ((size_t)(n_hops * 8 + 8) * 8 + 255) & ~(size_t)255;
-  const size_t words_bytes = cursor;
-  uint64_t newid_slots = 0;
   for (int h = 0; h < n_hops; ++h) {
     SHMT_REQUIRE(fanouts[h] >= 1 && fanouts[h] < ((int64_t)1 << 20), "shmt_sample_minibatch: fan-out out of range");
     SHMT_REQUIRE(out_sub_indptr[h] && out_sub_indices[h] && out_relabel[h] && out_frontier[h],
@@ -489,16 +486,11 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     cursor += (tile_state_bytes(hop_tiles[h]) + 255) & ~(size_t)255;
     off_rel[h] = cursor;
     cursor += (tile_state_bytes(rel_tiles[h]) + 255) & ~(size_t)255;
-    const uint64_t c = relabel_capacity(cap[h + 1]);
-    if (c > newid_slots) newid_slots = c;
   }
-  const size_t zero_bytes = cursor;
-  if (int rc = ctx_reserve(ctx, cursor + newid_slots * 4)) return rc;
+  if (int rc = ctx_reserve(ctx, cursor)) return rc;
   char* base = ctx->region();
   int64_t* words = reinterpret_cast<int64_t*>(base);
-  unsigned* newid = reinterpret_cast<unsigned*>(base + cursor);
-  (void)words_bytes;
-  SHMT_CUDA_TRY(cudaMemsetAsync(base, 0, zero_bytes, s));  // words, tickets and every tile flag
+  SHMT_CUDA_TRY(cudaMemsetAsync(base, 0, cursor, s));  // words, tickets and every tile flag
   int64_t* status = words + n_hops * 8;
 
   {  // the relabel table for the largest hop, reserved before anything is queued
@@ -536,8 +528,7 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     if (fuse_insert) {
       RelTable t;
       if (int rc = relabel_table(ctx, cap[h + 1], &t, s)) return rc;
-      job.rel_keys = t.keys;
-      job.rel_first = t.first;
+      job.rel_slots = t.slots;
       job.rel_mask = t.mask;
       job.rel_out = out_relabel[h];
     }
@@ -558,7 +549,7 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     // every size and the status word are final once the last hop's ids are counted: that kernel
     // hands them to the host, which returns while the last remap kernel is still running
     if (h == n_hops - 1) post = ctx_begin_post(ctx, words, n_hops * 8 + 8, w + 4);
-    if (int rc = launch_relabel(ctx, ps, cap[h + 1], newid, out_frontier[h], out_relabel[h],
+    if (int rc = launch_relabel(ctx, ps, cap[h + 1], out_frontier[h], out_relabel[h],
                                 carve_tile_states(base + off_rel[h], rel_tiles[h]), w + 2, status,
                                 w + 3, s, fuse_insert, /*pdl=*/true, h == n_hops - 1 ? &post : nullptr))
       return rc;

@@ -1,4 +1,4 @@
-// In-place prefix sum: one kernel, decoupled look-back between 2048-item tiles.
+// In-place prefix sum: one kernel, decoupled look-back between 64 KB tiles.
 // Semantics follow cub_exclusiveSum (reference src/cache_graph_sampling.cu:30-45)
 // and the intended meaning of thrust_scan (reference src/thrust_scan.cu:9-18,
 // whose own lambda races); integer arithmetic wraps.
@@ -7,47 +7,131 @@
 
 namespace shmt {
 
-constexpr int kScanThreads = 256;
-constexpr int kScanItems = 8;
-constexpr int kScanTile = kScanThreads * kScanItems;
+constexpr int kScanThreads = 512;
+constexpr int kScanWarps = kScanThreads / 32;
+constexpr int kScanVecs = 8;                                     // 16-byte vectors per thread
+constexpr int kScanTileBytes = kScanThreads * kScanVecs * 16;    // 64 KB per tile
+constexpr int kScanTile = kScanTileBytes / 8;                    // items per tile of the widest type
+constexpr int kScanPartials = kScanVecs * kScanWarps;            // one per (row, warp)
+static_assert(kScanPartials % 32 == 0, "warp 0 scans the per-warp partials, the same number per lane");
 
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads)
-scan_kernel(T* __restrict__ data, int64_t n, int exclusive, TileStates st, int64_t* words) {
-  __shared__ int64_t warp_sums[32];
-  __shared__ int64_t s_total;
+struct ScanWord;
+template <>
+struct ScanWord<int> { using type = unsigned; };
+template <>
+struct ScanWord<long long> { using type = unsigned long long; };
+
+// A tile is 8 rows of 512 16-byte vectors (64 KB); thread t owns vector t of every row, so each
+// load and store instruction of a warp covers 512 contiguous bytes.  Sums are taken in the unsigned
+// type of the data (wrap-around is defined and the low bits are all the result keeps): inside a
+// vector, across the warp with shuffles, across the 128 (row, warp) partials by warp 0, which
+// also does the look-back; every thread then adds its three offsets and stores.  Large tiles
+// matter: the look-back hands a prefix over at most 32 tiles per round trip through L2, so the
+// bytes per tile bound the rate of the whole scan.
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads, 2)
+scan_kernel(T* __restrict__ data, int64_t n, int exclusive, int vec_ok, TileStates st, int64_t* words) {
+  using U = typename ScanWord<T>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  constexpr int TILE = kScanTileBytes / (int)sizeof(T);
+  constexpr int PER_LANE = kScanPartials / 32;
+  __shared__ U partial[kScanPartials];  // [row][warp]
   __shared__ int64_t s_prefix;
   __shared__ int s_tile;
+  const unsigned full = 0xffffffffu;
+  const unsigned tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int tile = take_tile(words + W_TICKET, &s_tile);
-  const int64_t base = (int64_t)tile * kScanTile + (int64_t)threadIdx.x * kScanItems;
+  const int64_t tile_base = (int64_t)tile * TILE;
+  union Pack {
+    uint4 q;
+    U a[VEC];
+  };
 
-  T v[kScanItems];
-  int64_t sum = 0;
+  U v[kScanVecs][VEC], vsum[kScanVecs], inc[kScanVecs];
 #pragma unroll
-  for (int j = 0; j < kScanItems; ++j) {
-    v[j] = base + j < n ? data[base + j] : T(0);
-    sum += (int64_t)v[j];
-  }
-  const int64_t local = block_exclusive_scan(sum, warp_sums, &s_total);
-  if (threadIdx.x < 32) {
-    const int64_t p = lookback_exclusive_prefix(st, tile, s_total, words + W_STATUS);
-    if (threadIdx.x == 0) s_prefix = p;
-  }
-  __syncthreads();
-  // unsigned accumulation: wrap-around is defined, and narrowing to T keeps the low bits
-  uint64_t run = (uint64_t)(s_prefix + local);
+  for (int k = 0; k < kScanVecs; ++k) {
+    const int64_t at = tile_base + ((int64_t)k * kScanThreads + tid) * VEC;
+    if (vec_ok && at + VEC <= n) {
+      Pack p;
+      p.q = *reinterpret_cast<const uint4*>(data + at);
 #pragma unroll
-  for (int j = 0; j < kScanItems; ++j) {
-    if (base + j < n) {
-      if (exclusive) {
-        data[base + j] = (T)run;
-        run += (uint64_t)(int64_t)v[j];
-      } else {
-        run += (uint64_t)(int64_t)v[j];
-        data[base + j] = (T)run;
-      }
+      for (int j = 0; j < VEC; ++j) v[k][j] = p.a[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) v[k][j] = at + j < n ? (U)data[at + j] : U(0);
     }
   }
+#pragma unroll
+  for (int k = 0; k < kScanVecs; ++k) {
+#pragma unroll
+    for (int j = 1; j < VEC; ++j) v[k][j] += v[k][j - 1];
+    vsum[k] = v[k][VEC - 1];
+    inc[k] = vsum[k];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const U up = __shfl_up_sync(full, inc[k], o);
+      if (lane >= (unsigned)o) inc[k] += up;
+    }
+    if (lane == 31) partial[k * kScanWarps + warp] = inc[k];
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // the partials in tile order, PER_LANE consecutive ones per lane
+    U a[PER_LANE], lsum = 0;
+#pragma unroll
+    for (int q = 0; q < PER_LANE; ++q) {
+      a[q] = partial[lane * PER_LANE + q];
+      lsum += a[q];
+    }
+    U linc = lsum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const U up = __shfl_up_sync(full, linc, o);
+      if (lane >= (unsigned)o) linc += up;
+    }
+    U run = linc - lsum;
+#pragma unroll
+    for (int q = 0; q < PER_LANE; ++q) {
+      partial[lane * PER_LANE + q] = run;  // everything ahead of this (row, warp)
+      run += a[q];
+    }
+    const U total = __shfl_sync(full, linc, 31);
+    // zero-extended aggregate: tile sums add up in 64 bits, of which the low bits are used
+    const int64_t p = lookback_exclusive_prefix(st, tile, (int64_t)(uint64_t)total, words + W_STATUS);
+    if (lane == 0) s_prefix = p;
+  }
+  __syncthreads();
+  const U prefix = (U)(uint64_t)s_prefix;
+#pragma unroll
+  for (int k = 0; k < kScanVecs; ++k) {
+    const int64_t at = tile_base + ((int64_t)k * kScanThreads + tid) * VEC;
+    const U before = prefix + partial[k * kScanWarps + warp] + (inc[k] - vsum[k]);
+    Pack p;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j)
+      p.a[j] = before + (exclusive ? (j ? v[k][j - 1] : U(0)) : v[k][j]);
+    if (vec_ok && at + VEC <= n) {
+      *reinterpret_cast<uint4*>(data + at) = p.q;
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j)
+        if (at + j < n) data[at + j] = (T)p.a[j];
+    }
+  }
+}
+
+template <typename T>
+static int64_t scan_tiles(int64_t n) {
+  const int64_t tile = kScanTileBytes / (int64_t)sizeof(T);
+  return (n + tile - 1) / tile;
+}
+
+template <typename T>
+static void run_scan(void* data, int64_t n, int exclusive, TileStates st, int64_t* words, cudaStream_t s) {
+  const int vec_ok = ((uintptr_t)data & 15) == 0;
+  scan_kernel<T><<<(unsigned)scan_tiles<T>(n), kScanThreads, 0, s>>>(static_cast<T*>(data), n, exclusive,
+                                                                      vec_ok, st, words);
 }
 
 // Exercises the give-up path of the look-back on purpose, harmlessly: one warp plays tile 1
@@ -67,13 +151,11 @@ int launch_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
   TileStates st = carve_tile_states(ctx->region() + scratch_off, n_tiles);
   // status / result / ticket words and the tile flags start at zero
   SHMT_CUDA_TRY(cudaMemsetAsync(ctx->d_words(), 0, 256, stream));
-  SHMT_CUDA_TRY(cudaMemsetAsync(st.flag, 0, (size_t)n_tiles * 4, stream));
+  SHMT_CUDA_TRY(cudaMemsetAsync(st.d, 0, tile_state_bytes(n_tiles), stream));
   if (dtype == SHMT_I64)
-    scan_kernel<long long><<<(unsigned)n_tiles, kScanThreads, 0, stream>>>(
-        static_cast<long long*>(data), n, exclusive, st, ctx->d_words());
+    run_scan<long long>(data, n, exclusive, st, ctx->d_words(), stream);
   else
-    scan_kernel<int><<<(unsigned)n_tiles, kScanThreads, 0, stream>>>(
-        static_cast<int*>(data), n, exclusive, st, ctx->d_words());
+    run_scan<int>(data, n, exclusive, st, ctx->d_words(), stream);
   SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;
 }
@@ -85,7 +167,7 @@ size_t scan_scratch_bytes(int64_t n) {
 
 // ---- scan without any allocation ----------------------------------------------------
 // Look-back state for shmt_scan_static lives in this fixed array instead of context
-// scratch.  Every GPU that loads the library carries it (about 160 KB) until exit.
+// scratch.  Every GPU that loads the library carries it (about 33 KB) until exit.
 constexpr int64_t kStaticScanMaxItems = (int64_t)1 << 24;
 constexpr int64_t kStaticScanMaxTiles = kStaticScanMaxItems / kScanTile;
 constexpr size_t kStaticScanBytes = 256 + ((tile_state_bytes(kStaticScanMaxTiles) + 255) & ~(size_t)255);
@@ -128,15 +210,13 @@ extern "C" int shmt_scan_static(void* data, int dtype, int64_t n, int exclusive,
   const int64_t n_tiles = (n + kScanTile - 1) / kScanTile;
   int64_t* words = reinterpret_cast<int64_t*>(base);
   TileStates st = carve_tile_states(reinterpret_cast<char*>(base) + 256, n_tiles);
-  // the array still holds the previous call's ticket, status and tile flags: zero the
-  // words and the flags this call will use (flags sit right behind the 256-byte header)
-  SHMT_CUDA_TRY(cudaMemsetAsync(base, 0, 256 + (size_t)n_tiles * 4, s));
+  // the array still holds the previous call's ticket, status and tile descriptors: zero the
+  // words and the descriptors this call will use (they sit right behind the 256-byte header)
+  SHMT_CUDA_TRY(cudaMemsetAsync(base, 0, 256 + tile_state_bytes(n_tiles), s));
   if (dtype == SHMT_I64)
-    scan_kernel<long long><<<(unsigned)n_tiles, kScanThreads, 0, s>>>(
-        static_cast<long long*>(data), n, exclusive, st, words);
+    run_scan<long long>(data, n, exclusive, st, words, s);
   else
-    scan_kernel<int><<<(unsigned)n_tiles, kScanThreads, 0, s>>>(static_cast<int*>(data), n,
-                                                                exclusive, st, words);
+    run_scan<int>(data, n, exclusive, st, words, s);
   SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;
 }
@@ -147,7 +227,7 @@ extern "C" int shmt_debug_lookback_timeout(shmt_ctx* ctx, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (int rc = ctx_reserve(ctx, tile_state_bytes(2))) return rc;
   TileStates st = carve_tile_states(ctx->region(), 2);
-  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + 2 * 4, s));
+  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + tile_state_bytes(2), s));
   lookback_timeout_probe_kernel<<<1, 32, 0, s>>>(st, ctx->d_words(), 1 << 10);
   SHMT_CUDA_TRY(cudaGetLastError());
   return ctx_fetch_words(ctx, s, "shmt_debug_lookback_timeout");
