@@ -29,6 +29,30 @@ def test_scan_matches_cumsum(capi, n, dtype):
     assert np.array_equal(exc.cpu().numpy(), oracle.scan_exclusive(a.cpu().numpy()))
 
 
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64])
+def test_scan_tile_edges_views_and_many_tiles(capi, dtype):
+    """Lengths around multiples of the 32 KB and 64 KB tiles, ragged tails shorter than 16 bytes,
+    views that start off a 16-byte boundary, and enough tiles for every persistent CTA to loop."""
+    item = 4 if dtype == torch.int32 else 8
+    per32k = 32768 // item
+    g = torch.Generator(device="cuda").manual_seed(77)
+    big = torch.randint(-50, 50, (24_000_011,), generator=g, device="cuda").to(dtype)
+    sizes = [4 * per32k - 1, 4 * per32k, 4 * per32k + 1, 5 * per32k + 3, 16 * per32k + per32k // 2 + 1,
+             1000 * per32k + 7 if item == 4 else 700 * per32k + 1, big.numel()]
+    for n in sizes:
+        for off in (0, 1, 3, 4):
+            src = big[off:off + n] if off + n <= big.numel() else big[off:]
+            for fn, excl in ((capi.thrust_scan, False), (capi.exclusive_scan_, True)):
+                work = big.clone()[off:off + src.numel()]      # a view: same alignment as src
+                fn(work)
+                want = torch.cumsum(src, 0, dtype=dtype)
+                if excl:
+                    want = want - src
+                assert torch.equal(work, want), (n, off, excl)
+    capi.check_async()
+    assert capi.device_fault() == 0
+
+
 def test_scan_int32_wraps_like_the_oracle(capi):
     a = torch.full((5000,), 2**30, dtype=torch.int32, device="cuda")
     want = oracle.scan_inclusive(a.cpu().numpy())
