@@ -8,7 +8,7 @@ struct shmt_ctx {
   char* scratch = nullptr;      // device scratch, grown geometrically; the first
   size_t scratch_bytes = 0;     // 256 bytes are the result words (status, result, ticket ...)
   int64_t* h_words = nullptr;   // pinned host mirror of the result words
-  // Relabel table (keys i64 | first-index u32 | new-id u32 per slot).  Kept all-ones between
+  // Relabel table (16-byte slots: key i64, first-index u32, new-id u32).  Keys and first-index words all ones between
   // calls: the remap kernel restores every slot it leaves, so no per-call memset is needed.
   char* table = nullptr;
   size_t table_bytes = 0;

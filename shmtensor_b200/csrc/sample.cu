@@ -490,7 +490,7 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
   if (int rc = ctx_reserve(ctx, cursor)) return rc;
   char* base = ctx->region();
   int64_t* words = reinterpret_cast<int64_t*>(base);
-  SHMT_CUDA_TRY(cudaMemsetAsync(base, 0, cursor, s));  // words, tickets and every tile flag
+  SHMT_CUDA_TRY(cudaMemsetAsync(base, 0, cursor, s));  // words, tickets and every tile descriptor
   int64_t* status = words + n_hops * 8;
 
   {  // the relabel table for the largest hop, reserved before anything is queued

@@ -149,7 +149,7 @@ int launch_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
   const int64_t n_tiles = (n + kScanTile - 1) / kScanTile;
   SHMT_REQUIRE(n_tiles < (int64_t)1 << 30, "scan: %lld items is too many", (long long)n);
   TileStates st = carve_tile_states(ctx->region() + scratch_off, n_tiles);
-  // status / result / ticket words and the tile flags start at zero
+  // status / result / ticket words and the tile descriptors start at zero
   SHMT_CUDA_TRY(cudaMemsetAsync(ctx->d_words(), 0, 256, stream));
   SHMT_CUDA_TRY(cudaMemsetAsync(st.d, 0, tile_state_bytes(n_tiles), stream));
   if (dtype == SHMT_I64)
