@@ -185,8 +185,10 @@ int shmt_debug_lookback_timeout(shmt_ctx* ctx, void* stream);
  * Concatenation of `n_parts` id arrays -> distinct ids in first-occurrence
  * order (out_unique, capacity = total) and, for every input element, the index
  * of its id in out_unique (out_relabel, total elements, same dtype).  Ids must
- * not be -1.  If n_unique_host != NULL the call synchronises and stores the
- * number of distinct ids there.  TensorRelabel (src/tensor_relabel.cu:125-209). */
+ * not be -1.  If n_unique_host != NULL the call waits for the number of distinct
+ * ids and stores it there; it returns as soon as that number is known, while the
+ * last kernel may still be writing out_relabel (consume the outputs in `stream`
+ * order, or synchronise).  TensorRelabel (src/tensor_relabel.cu:125-209).        */
 int shmt_relabel(shmt_ctx* ctx, const void* const* parts,
                  const int64_t* part_sizes, int n_parts, int dtype,
                  void* out_unique, void* out_relabel, int64_t* n_unique_host,
@@ -201,7 +203,9 @@ int shmt_relabel(shmt_ctx* ctx, const void* const* parts,
  * otherwise k distinct uniform positions (without replacement) or k iid
  * uniform positions (with).  out_sub_indptr: n+1 entries of indptr dtype;
  * out_sub_indices: capacity n*k entries of indices dtype.  If nnz_host != NULL
- * the call synchronises and stores out_sub_indptr[n] there.
+ * the call waits for out_sub_indptr[n] and stores it there; it returns as soon as
+ * that number is known, while the kernel may still be writing rows (consume the
+ * outputs in `stream` order, or synchronise).
  * CSRWiseSampling / CSRWiseCacheSampling
  * (src/cache_graph_sampling.cu:179-220, :382-426; kernels :91-177, :291-380;
  *  GetSubIndptr(:47-89) / GetSubIndptrWithCache(:222-289)).
@@ -221,7 +225,9 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
  * (python/shmtensor/sampling.py:124-143) with csr_(cache_)sampling + tensor_relabel inside.
  * Nothing returns to the host between hops: every kernel reads its input size from the
  * device word the stage before it wrote, with grids sized for the largest frontier the
- * fan-outs allow, and the host waits once at the end.  `seeds` and every id output have
+ * fan-outs allow, and the host waits once, for the sizes: the call returns as soon as
+ * they are known, while the last hop's final kernel may still be running (consume the
+ * outputs in `stream` order, or synchronise).  `seeds` and every id output have
  * the indices dtype.  With c_0 = n_seeds and c_{h+1} = c_h * (1 + fanouts[h]) the caller
  * provides per hop: out_sub_indptr[h] (c_h + 1 entries, indptr dtype), out_sub_indices[h]
  * (c_h * fanouts[h]), out_relabel[h] (c_{h+1}: relabelled seeds, then relabelled
