@@ -174,6 +174,10 @@ int shmt_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
  * streams with no dependency between them — corrupt each other, calls ordered on
  * one stream do not.  This entry point has no counterpart in the reference.        */
 int shmt_scan_static(void* data, int dtype, int64_t n, int exclusive, void* stream);
+/* Wait for `stream` and report whether the last shmt_scan_static call on the current device
+ * ran into its bounded look-back wait (SHMT_ERR_TIMEOUT) or not (SHMT_OK).  Allocates nothing
+ * either.  This entry point has no counterpart in the reference.                          */
+int shmt_scan_static_check(void* stream);
 
 /* Test hook for the failure path of every look-back scan: runs one warp whose predecessor
  * tile never publishes, with a short spin limit, and returns what the host sees --

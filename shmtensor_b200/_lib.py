@@ -67,6 +67,7 @@ SIGNATURES = {
     "shmt_insert_set": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i64, _i64, _vp, _vp]),
     "shmt_scan": (_i, [_vp, _vp, _i, _i64, _i, _vp]),
     "shmt_scan_static": (_i, [_vp, _i, _i64, _i, _vp]),
+    "shmt_scan_static_check": (_i, [_vp]),
     "shmt_debug_lookback_timeout": (_i, [_vp, _vp]),
     "shmt_relabel": (_i, [_vp, _pvp, _pi64, _i, _i, _vp, _vp, _pi64, _vp]),
     "shmt_sample_hop": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i, _i64, _i64, _i, _u64,

@@ -394,8 +394,9 @@ def cache_replace(uva_data: torch.Tensor, gpu_data: torch.Tensor, hashmap: CUCOS
     of ``admit_ids`` (distinct, not cached yet) take their rows of ``gpu_data`` and are filled from
     ``uva_data`` by the UVA gather kernel.  The reference rebuilds the map and re-copies every
     row from the CPU to change the cached set (example/test_cache_set.py:57-61).  Admits at most
-    as many ids as rows were freed, in order; returns how many."""
-    freed = hashmap.erase(evict_ids)
+    as many ids as rows were freed, in order; returns how many.  An id listed twice in
+    ``evict_ids`` is evicted once."""
+    freed = hashmap.erase(torch.unique(evict_ids, sorted=True))
     freed = freed[freed >= 0]
     n = min(int(freed.numel()), int(admit_ids.numel()))
     if n == 0:

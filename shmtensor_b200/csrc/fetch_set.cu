@@ -613,6 +613,8 @@ int shmt_insert_set(shmt_map* map, void* gpu_base, const void* keys, int key_dty
   char* g = static_cast<char*>(gpu_base);
   const char* u = static_cast<const char*>(update);
   const int k64 = key_dtype == SHMT_I64, s64 = slots_dtype == SHMT_I64;
+  // the status word reports on this call only (see shmt_map_insert)
+  SHMT_CUDA_TRY(cudaMemsetAsync(map->d_meta, 0, sizeof(int64_t), s));
   switch (vec) {
     case 16: insert_set_kernel<16, 8><<<grid, kRowThreads, 0, s>>>(map->view, g, keys, k64, slots, s64, n, row_bytes, u, R, map->d_meta); break;
     case 8: insert_set_kernel<8, 8><<<grid, kRowThreads, 0, s>>>(map->view, g, keys, k64, slots, s64, n, row_bytes, u, R, map->d_meta); break;

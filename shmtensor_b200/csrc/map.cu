@@ -141,6 +141,9 @@ int shmt_map_insert(shmt_map* map, const void* keys, const void* values, int64_t
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int64_t ins_blocks = (n + kMapThreads - 1) / kMapThreads;
   const int64_t ins_cap = (int64_t)sm_count() * 16;
+  // the status word reports on this call only: an overflow of an earlier call must not make
+  // every later insert fail once room has been freed again (the key count behind it stays)
+  SHMT_CUDA_TRY(cudaMemsetAsync(map->d_meta, 0, sizeof(int64_t), s));
   map_insert_kernel<<<(unsigned)(ins_blocks < ins_cap ? ins_blocks : ins_cap), kMapThreads, 0, s>>>(
       map->view, keys, map->key_dtype == SHMT_I64, values, map->val_dtype == SHMT_I64, n,
       map->d_meta);

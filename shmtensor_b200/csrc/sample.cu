@@ -61,23 +61,31 @@ struct HopJob {
 };
 
 // indptr[i] and indptr[i+1] with one load when the pair is naturally aligned (one request on
-// the host link instead of two for a row that lives in host memory).
+// the host link instead of two for a row that lives in host memory).  Alignment is decided on
+// the address of element i, so a view that starts at an odd element (indptr[1:], an .npy
+// payload at an offset that is no multiple of 16) pairs its odd rows and never issues a
+// misaligned vector load.
 __device__ __forceinline__ void load_bounds(const void* indptr, int is64, int64_t i, int64_t* b,
                                             int64_t* e) {
-  if ((i & 1) == 0) {
-    if (is64) {
-      const longlong2 v = __ldg(reinterpret_cast<const longlong2*>(indptr) + (i >> 1));
+  if (is64) {
+    const long long* p = reinterpret_cast<const long long*>(indptr) + i;
+    if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+      const longlong2 v = __ldg(reinterpret_cast<const longlong2*>(p));
       *b = v.x;
       *e = v.y;
-    } else {
-      const int2 v = __ldg(reinterpret_cast<const int2*>(indptr) + (i >> 1));
-      *b = v.x;
-      *e = v.y;
+      return;
     }
   } else {
-    *b = load_int(indptr, is64, i);
-    *e = load_int(indptr, is64, i + 1);
+    const int* p = reinterpret_cast<const int*>(indptr) + i;
+    if ((reinterpret_cast<uintptr_t>(p) & 7) == 0) {
+      const int2 v = __ldg(reinterpret_cast<const int2*>(p));
+      *b = v.x;
+      *e = v.y;
+      return;
+    }
   }
+  *b = load_int(indptr, is64, i);
+  *e = load_int(indptr, is64, i + 1);
 }
 
 __device__ __forceinline__ uint64_t draw_below(const Philox& rng, uint32_t seed_idx, uint32_t draw,

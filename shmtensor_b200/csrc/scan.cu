@@ -221,6 +221,24 @@ extern "C" int shmt_scan_static(void* data, int dtype, int64_t n, int exclusive,
   return SHMT_OK;
 }
 
+// What the last shmt_scan_static call on the current device left in its status word.  The word
+// lives in the fixed array, which no context covers, so it has a check of its own; like the
+// scan itself it allocates nothing (one 8-byte copy and a wait for `stream`).
+extern "C" int shmt_scan_static_check(void* stream) {
+  unsigned char* base = nullptr;
+  if (int rc = static_scan_scratch(&base)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int64_t status = 0;
+  SHMT_CUDA_TRY(cudaMemcpyAsync(&status, reinterpret_cast<int64_t*>(base) + W_STATUS, sizeof(status),
+                                cudaMemcpyDeviceToHost, s));
+  SHMT_CUDA_TRY(cudaStreamSynchronize(s));
+  if (status == DEV_TIMEOUT) {
+    set_error("shmt_scan_static: a bounded look-back wait ran out; the result is not a prefix sum");
+    return SHMT_ERR_TIMEOUT;
+  }
+  return SHMT_OK;
+}
+
 extern "C" int shmt_debug_lookback_timeout(shmt_ctx* ctx, void* stream) {
   SHMT_REQUIRE(ctx != nullptr, "shmt_debug_lookback_timeout: ctx is null");
   DeviceGuard guard(ctx->device);

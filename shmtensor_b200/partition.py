@@ -174,9 +174,12 @@ class PartitionedFeatureCache:
         the same call (a collective when there are several ranks, with no fetch in flight);
         each updates its own directory and fills the freed rows it owns from the host table.
         Ids held on every rank (the replicated hottest rows) cannot be evicted.  Admits at most
-        as many ids as rows were freed, in order; returns how many."""
+        as many ids as rows were freed, in order; returns how many.  ``evict_ids`` may list an
+        id twice (it is evicted once); ``admit_ids`` must be distinct."""
         dev = self.device
-        evict = evict_ids.to(dev, torch.int64).contiguous()
+        # every rank must pair the same freed row with the same admitted id: a duplicate would let
+        # whichever thread erases first report the row, in an order that differs between ranks
+        evict = torch.unique(evict_ids.to(dev, torch.int64), sorted=True).contiguous()
         admit = admit_ids.to(dev, torch.int64).contiguous()
         low = (1 << OWNER_SHIFT) - 1
         if self.replicated:

@@ -87,6 +87,29 @@ def test_insert_into_live_map_and_overflow(capi):
     assert m.query(torch.tensor([5, 599], device="cuda")).cpu().tolist() == [15, 1198]
 
 
+def test_overflow_is_reported_once_not_forever(capi):
+    """An overflow belongs to the call that overflowed: once erase has made room, the next insert
+    (and the fused insert+set) that fits must succeed."""
+    from shmtensor_b200._lib import ShmtError, ERR_CAPACITY
+    m = capi.CUCOStaticHashmap.empty(1000)
+    base = torch.arange(0, 900, device="cuda")
+    m.insert(base, base)
+    with pytest.raises(ShmtError) as err:
+        m.insert(torch.arange(10_000, 20_000, device="cuda"), torch.arange(10_000, device="cuda"))
+    assert err.value.code == ERR_CAPACITY
+    stored = m.query(torch.arange(10_000, 20_000, device="cuda"))
+    m.erase(torch.arange(10_000, 20_000, device="cuda")[stored >= 0])
+    m.erase(base[:500])
+    assert m.size() == 400
+    fresh = torch.arange(50_000, 50_300, device="cuda")
+    m.insert(fresh, fresh + 1)                      # fits: must not raise
+    assert torch.equal(m.query(fresh), fresh + 1) and m.size() == 700
+    rows = torch.zeros(1000, 4, device="cuda")
+    more = torch.arange(60_000, 60_100, device="cuda")
+    capi.cache_insert_set(rows, more, torch.arange(100, device="cuda"), torch.ones(100, 4, device="cuda"), m)
+    assert m.size() == 800 and rows[:100].eq(1).all()
+
+
 def test_config5_map_full_size(capi):
     """4,000,000 unique int64 keys over 2^40 at load factor 0.5; 1,000,000 lookups, half absent."""
     g = torch.Generator(device="cuda").manual_seed(5)

@@ -191,3 +191,37 @@ def test_sampling_errors(capi):
         capi.csr_sampling(indptr, indices, torch.tensor([0]), 2, False)
     with pytest.raises(RuntimeError, match="int32 or int64"):
         capi.csr_sampling(indptr.float(), indices, torch.tensor([0], device="cuda"), 2, False)
+
+
+@pytest.mark.parametrize("ptr_dt", [torch.int64, torch.int32])
+def test_row_offsets_at_an_odd_element_offset(capi, ptr_dt):
+    """`indptr` handed over as a view that starts one element into its storage (a slice, or an .npy
+    payload at an odd offset) is only element-aligned: the paired row-bound load must not be used
+    on misaligned addresses, and results must equal those of an aligned copy."""
+    rng = np.random.default_rng(5)
+    deg = rng.integers(0, 40, size=3000)
+    indptr_n = np.concatenate([[0], np.cumsum(deg)]).astype(DT[ptr_dt])
+    indices_n = rng.integers(0, 3000, size=int(indptr_n[-1])).astype(np.int32)
+    indices = torch.from_numpy(indices_n).cuda()
+    padded = torch.empty(indptr_n.size + 1, dtype=ptr_dt, device="cuda")
+    padded[1:] = torch.from_numpy(indptr_n).cuda()
+    view = padded[1:]
+    assert view.data_ptr() % (2 * view.element_size()) != 0 and view.is_contiguous()
+    aligned = view.clone()
+    seeds = torch.from_numpy(rng.integers(0, 3000, size=2000)).cuda()
+    hot = torch.from_numpy(rng.choice(3000, size=700, replace=False)).cuda()
+    gp, gi = capi.create_subcsr(aligned, indices, hot)
+    gp_pad = torch.empty(gp.numel() + 1, dtype=gp.dtype, device="cuda")
+    gp_pad[1:] = gp
+    hmap = capi.CUCOStaticHashmap(hot, torch.arange(700, device="cuda"), 0.5)
+    for k in (5, 64):
+        capi.set_sampling_seed(99)
+        p0, x0 = capi.csr_sampling(aligned, indices, seeds, k, False)
+        q0, y0 = capi.csr_cache_sampling(aligned, indices, gp, gi, hmap, seeds, k, False)
+        capi.set_sampling_seed(99)
+        p1, x1 = capi.csr_sampling(view, indices, seeds, k, False)
+        q1, y1 = capi.csr_cache_sampling(view, indices, gp_pad[1:], gi, hmap, seeds, k, False)
+        assert torch.equal(p0, p1) and torch.equal(x0, x1)
+        assert torch.equal(q0, q1) and torch.equal(y0, y1)
+        oracle.check_sample(indptr_n, indices_n, seeds.cpu().numpy(), k, False, p1.cpu().numpy(),
+                            x1.cpu().numpy())

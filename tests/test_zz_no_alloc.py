@@ -47,7 +47,8 @@ def test_static_scan_equals_regular_scan_twice_in_a_row(dtype):
             a, b = src.clone(), src.clone()
             _lib.check(_scan_static(lib, a, exclusive))
             _lib.check(_scan_regular(lib, ctx, b, exclusive))
-            torch.cuda.synchronize()
+            # no bounded wait ran out (the check also waits for the stream)
+            _lib.check(lib.shmt_scan_static_check(torch.cuda.current_stream().cuda_stream))
             assert torch.equal(a, b), f"n={n} exclusive={exclusive}"
             want = torch.cumsum(src.to(torch.int64), 0)
             if exclusive:
