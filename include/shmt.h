@@ -268,6 +268,13 @@ int shmt_shm_create(const char* name, int64_t size, int pin_memory,
                     int64_t* out_ptr, int64_t* out_fd);
 int shmt_shm_open(const char* name, int64_t size, int pin_memory,
                   int64_t* out_ptr, int64_t* out_fd);
+/* Create, failing with SHMT_ERR_OS if a segment of that name exists: one atomic step where
+ * python/shmtensor/shm_tensor.py:38-53 tests file_exist() and creates afterwards (two
+ * processes can both pass the test).  shmt_shm_unlink removes a name, e.g. the segment a
+ * killed run left behind; a name that does not exist is not an error.                     */
+int shmt_shm_create_excl(const char* name, int64_t size, int pin_memory,
+                         int64_t* out_ptr, int64_t* out_fd);
+int shmt_shm_unlink(const char* name);
 int shmt_shm_release(const char* name, int64_t size, int64_t ptr, int64_t fd,
                      int pin_memory);
 int shmt_shm_exists(const char* name); /* 1 / 0 */
@@ -282,11 +289,29 @@ typedef struct shmt_npy_info {
   int64_t ptr;         /* base address of the mapping                         */
   int64_t fd;
 } shmt_npy_info;
-int shmt_npy_open(const char* path, int pin_memory, shmt_npy_info* out);
+/* flags: SHMT_NPY_PIN registers the mapping with CUDA (the reference's pin_memory argument,
+ * src/mmap_tensor.cc:10); SHMT_NPY_READONLY opens and maps the file without write permission
+ * (the reference maps read/write only, src/mmap_tensor.cc:32) and registers it read-only.  */
+#define SHMT_NPY_PIN 1
+#define SHMT_NPY_READONLY 2
+int shmt_npy_open(const char* path, int flags, shmt_npy_info* out);
 int shmt_npy_close(int64_t size, int64_t ptr, int64_t fd, int pin_memory);
 
 int shmt_host_register(void* ptr, int64_t nbytes);
 int shmt_host_unregister(void* ptr);
+
+/* Where the pages of a host table live decides which memory controllers, and which
+ * inter-socket links, the GPUs' reads of it load.  SHMT_NUMA_INTERLEAVE spreads the range
+ * over all memory nodes; SHMT_NUMA_BIND puts it on `node` (one copy of a read-mostly table per
+ * socket).  Call it on a fresh mapping, before the data is written and before the range is
+ * registered: mbind() where the kernel allows it (pages already present are moved), else
+ * first touch from threads running on the wanted node.  The range must start on a page
+ * boundary.  No counterpart in the reference, which leaves placement to whoever writes first
+ * (include/shm_memory.h:6-23).                                                            */
+#define SHMT_NUMA_INTERLEAVE 1
+#define SHMT_NUMA_BIND 2
+int shmt_host_numa_nodes(void); /* memory nodes of this machine (>= 1) */
+int shmt_host_numa_place(void* ptr, int64_t nbytes, int policy, int node);
 
 /* ---- device buffers shared between ranks (partitioned cache) ---------------
  * cudaMalloc'ed so that a CUDA IPC handle maps the buffer itself.  No
@@ -301,6 +326,12 @@ int shmt_ipc_close_handle(void* mapped_ptr);
  * ceilings: sums `bytes` of memory at `src` (16-byte loads) into *sink.       */
 int shmt_stream_read(const void* src, int64_t bytes, void* sink_8_bytes,
                      void* stream);
+/* Random-read probe for the kernels that are bound by a rate of small reads rather than by
+ * bytes (hash probes, row-offset pairs, short adjacency lists): n_reads independent reads of
+ * read_bytes (16, 32, 64 or 128) at pseudo-random aligned offsets inside [src, src+bytes),
+ * which may be HBM, pinned host memory or a peer's buffer.  No counterpart in the reference. */
+int shmt_random_read(const void* src, int64_t bytes, int64_t n_reads, int read_bytes,
+                     uint64_t seed, void* sink_8_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -78,18 +78,23 @@ SIGNATURES = {
     "shmt_subcsr_fill": (_i, [_vp, _i, _vp, _i, _vp, _i, _i64, _vp, _vp, _vp]),
     "shmt_shm_create": (_i, [_s, _i64, _i, _pi64, _pi64]),
     "shmt_shm_open": (_i, [_s, _i64, _i, _pi64, _pi64]),
+    "shmt_shm_create_excl": (_i, [_s, _i64, _i, _pi64, _pi64]),
+    "shmt_shm_unlink": (_i, [_s]),
     "shmt_shm_release": (_i, [_s, _i64, _i64, _i64, _i]),
     "shmt_shm_exists": (_i, [_s]),
     "shmt_npy_open": (_i, [_s, _i, C.POINTER(NpyInfo)]),
     "shmt_npy_close": (_i, [_i64, _i64, _i64, _i]),
     "shmt_host_register": (_i, [_vp, _i64]),
     "shmt_host_unregister": (_i, [_vp]),
+    "shmt_host_numa_nodes": (_i, []),
+    "shmt_host_numa_place": (_i, [_vp, _i64, _i, _i]),
     "shmt_dev_alloc": (_i, [_i64, _pvp]),
     "shmt_dev_free": (_i, [_vp]),
     "shmt_ipc_get_handle": (_i, [_vp, _vp]),
     "shmt_ipc_open_handle": (_i, [_vp, _pvp]),
     "shmt_ipc_close_handle": (_i, [_vp]),
     "shmt_stream_read": (_i, [_vp, _i64, _vp, _vp]),
+    "shmt_random_read": (_i, [_vp, _i64, _i64, _i, _u64, _vp, _vp]),
 }
 
 

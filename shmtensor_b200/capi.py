@@ -34,6 +34,9 @@ _NPY_DTYPES = {
     "<f2": torch.float16, "<f4": torch.float32, "<f8": torch.float64, "|u1": torch.uint8,
     "|i1": torch.int8, "<i2": torch.int16, "<i4": torch.int32, "<i8": torch.int64,
     "|b1": torch.bool,
+    # numpy has no bfloat16; writers that know the type (ml_dtypes, torch -> view(int16).numpy()
+    # saved through a void view) store it as an opaque 2-byte item
+    "<V2": torch.bfloat16, "|V2": torch.bfloat16,
 }
 
 
@@ -103,11 +106,37 @@ def set_sampling_seed(seed: int) -> None:
 
 
 # --------------------------------------------------------------------------- host memory
-def create_shared_mem(name: str, size: int, pin_memory: bool = False) -> Tuple[int, int]:
-    """include/shm_memory.h:6-23 — returns ``(ptr, fd)``."""
+def create_shared_mem(name: str, size: int, pin_memory: bool = False,
+                      exclusive: bool = False) -> Tuple[int, int]:
+    """include/shm_memory.h:6-23 — returns ``(ptr, fd)``.  Extension: ``exclusive=True`` fails
+    (``ShmtError``, code ``ERR_OS``) if a segment of that name already exists, in one atomic
+    step instead of ``file_exist`` followed by a create."""
     p, fd = C.c_int64(), C.c_int64()
-    check(lib.shmt_shm_create(name.encode(), size, int(pin_memory), C.byref(p), C.byref(fd)))
+    fn = lib.shmt_shm_create_excl if exclusive else lib.shmt_shm_create
+    check(fn(name.encode(), size, int(pin_memory), C.byref(p), C.byref(fd)))
     return p.value, fd.value
+
+
+def unlink_shared_mem(name: str) -> None:
+    """Extension: remove the name of a segment (one a killed run left behind, say).  Mappings
+    that exist keep their memory; a name that does not exist is not an error."""
+    check(lib.shmt_shm_unlink(name.encode()))
+
+
+NUMA_INTERLEAVE, NUMA_BIND = 1, 2
+
+
+def numa_nodes() -> int:
+    """Extension: number of memory nodes of this machine."""
+    return lib.shmt_host_numa_nodes()
+
+
+def numa_place(ptr: int, nbytes: int, policy: int = NUMA_INTERLEAVE, node: int = 0) -> None:
+    """Extension: spread a fresh, page-aligned host mapping over all memory nodes
+    (``NUMA_INTERLEAVE``) or put it on ``node`` (``NUMA_BIND``), before it is written and
+    registered.  Decides which memory controllers and inter-socket links the GPUs' reads of a
+    host table load."""
+    check(lib.shmt_host_numa_place(ptr, nbytes, policy, node))
 
 
 def open_shared_mem(name: str, size: int, pin_memory: bool = False) -> Tuple[int, int]:
@@ -143,10 +172,13 @@ def file_exist(filename: str) -> bool:
     return bool(lib.shmt_shm_exists(filename.encode()))
 
 
-def open_mmap_tensor(filename: str, pin_memory: bool):
-    """src/mmap_tensor.cc:10-47 — returns ``(tensor, size, ptr, fd)``."""
+def open_mmap_tensor(filename: str, pin_memory: bool, read_only: bool = False):
+    """src/mmap_tensor.cc:10-47 — returns ``(tensor, size, ptr, fd)``.  Extensions: ``read_only``
+    maps the file without write permission (writing through the tensor then faults, as for any
+    read-only mapping); an opaque 2-byte item (``V2``) is read as bfloat16."""
     info = _lib.NpyInfo()
-    check(lib.shmt_npy_open(filename.encode(), int(pin_memory), C.byref(info)))
+    check(lib.shmt_npy_open(filename.encode(), int(bool(pin_memory)) | (2 if read_only else 0),
+                            C.byref(info)))
     descr = info.descr.decode()
     try:
         if info.fortran_order:
@@ -170,6 +202,10 @@ def pin_memory(data: torch.Tensor) -> None:
     """src/cache_feature_fetch.cu:6-9 — cudaHostRegister(Portable) of a CPU tensor in place."""
     _check_contig(data, "data")
     check(lib.shmt_host_register(data.data_ptr(), data.numel() * data.element_size()))
+
+
+def _register_range(ptr: int, nbytes: int) -> None:
+    check(lib.shmt_host_register(ptr, nbytes))
 
 
 def unpin_memory(data: torch.Tensor) -> None:

@@ -28,6 +28,36 @@ stream_read_kernel(const uint4* __restrict__ src, int64_t n_vec, unsigned long l
   if (acc == 0x9E3779B9u) atomicAdd(sink, 1ULL);  // practically never; keeps the loads alive
 }
 
+// Independent reads of UNIT bytes at pseudo-random UNIT-aligned offsets: the access pattern of
+// a hash probe (16-byte slot), of a row-offset pair or of a short adjacency list.  What it
+// measures is a rate of reads, not bytes: random sectors from HBM, small requests over the
+// host link or NVLink.  Four reads per thread are in flight before the first is used.
+template <int UNIT>
+__global__ void __launch_bounds__(256)
+random_read_kernel(const char* __restrict__ src, uint64_t n_units, int64_t n_reads, uint64_t seed,
+                   unsigned long long* sink) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  uint32_t acc = 0;
+  auto one = [&](int64_t i) {
+    const uint64_t u = __umul64hi(mix64((uint64_t)i * 0x9E3779B97F4A7C15ULL + seed), n_units);
+    const uint4* p = reinterpret_cast<const uint4*>(src + u * UNIT);
+    uint32_t x = 0;
+#pragma unroll
+    for (int q = 0; q < UNIT / 16; ++q) {
+      const uint4 v = ld_stream16(p + q);
+      x ^= v.x ^ v.y ^ v.z ^ v.w;
+    }
+    return x;
+  };
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n_reads; i += 4 * stride) {
+    const uint32_t a = one(i), b = one(i + stride), c = one(i + 2 * stride), d = one(i + 3 * stride);
+    acc ^= a ^ b ^ c ^ d;
+  }
+  for (; i < n_reads; i += stride) acc ^= one(i);
+  if (acc == 0x9E3779B9u) atomicAdd(sink, 1ULL);
+}
+
 }  // namespace shmt
 
 using namespace shmt;
@@ -64,6 +94,31 @@ int shmt_ipc_open_handle(const void* handle_64_bytes, void** out) {
 
 int shmt_ipc_close_handle(void* mapped_ptr) {
   if (mapped_ptr) SHMT_CUDA_TRY(cudaIpcCloseMemHandle(mapped_ptr));
+  return SHMT_OK;
+}
+
+int shmt_random_read(const void* src, int64_t bytes, int64_t n_reads, int read_bytes,
+                     uint64_t seed, void* sink_8_bytes, void* stream) {
+  SHMT_REQUIRE(src && sink_8_bytes && n_reads >= 0, "shmt_random_read: bad argument");
+  SHMT_REQUIRE(read_bytes == 16 || read_bytes == 32 || read_bytes == 64 || read_bytes == 128,
+               "shmt_random_read: read_bytes must be 16, 32, 64 or 128");
+  SHMT_REQUIRE(bytes >= read_bytes && ((uintptr_t)src & 15) == 0,
+               "shmt_random_read: src must be 16-byte aligned and hold at least one read");
+  if (n_reads == 0) return SHMT_OK;
+  const uint64_t n_units = (uint64_t)bytes / (uint64_t)read_bytes;
+  int64_t blocks = (n_reads + 255) / 256 / 4 + 1;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const char* p = static_cast<const char*>(src);
+  unsigned long long* sink = static_cast<unsigned long long*>(sink_8_bytes);
+  switch (read_bytes) {
+    case 16: random_read_kernel<16><<<grid, 256, 0, s>>>(p, n_units, n_reads, seed, sink); break;
+    case 32: random_read_kernel<32><<<grid, 256, 0, s>>>(p, n_units, n_reads, seed, sink); break;
+    case 64: random_read_kernel<64><<<grid, 256, 0, s>>>(p, n_units, n_reads, seed, sink); break;
+    default: random_read_kernel<128><<<grid, 256, 0, s>>>(p, n_units, n_reads, seed, sink); break;
+  }
+  SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;
 }
 

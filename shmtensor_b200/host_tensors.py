@@ -30,13 +30,20 @@ class _HostTensorView:
 class ShmTensor(_HostTensorView):
     """A tensor in a named POSIX shared-memory segment shared by the ranks of one node.
 
-    Rank 0 of ``local_group`` creates the segment while the others wait at a barrier, then
-    they open it.  With ``pin_memory`` every rank registers its mapping with CUDA so kernels
-    can dereference it (UVA).  The segment is unmapped and unlinked when the object dies.
+    Rank 0 of ``local_group`` creates the segment while the others wait, then they open it.
+    With ``pin_memory`` every rank registers its mapping with CUDA so kernels can dereference it
+    (UVA).  The segment is unmapped and unlinked when the object dies.
+
+    Beyond the reference's constructor: the segment is created with ``O_EXCL`` (the reference
+    tests ``file_exist`` on every rank and creates afterwards, so two jobs can both pass the
+    test); ``overwrite_stale=True`` removes a segment of that name first, which is what a job
+    wants whose previous run was killed before its finalizer ran; ``numa`` places the pages
+    before anything is written: ``"interleave"`` over all memory nodes, or a node number.  A
+    failure of the creating rank reaches every rank as an exception instead of a hang.
     """
 
     def __init__(self, name, shape, local_rank, local_world_size, local_group=None,
-                 dtype=torch.float32, pin_memory=False):
+                 dtype=torch.float32, pin_memory=False, overwrite_stale=False, numa=None):
         nbytes = torch.empty((), dtype=dtype).element_size() * math.prod(shape)
         if nbytes <= 0:
             raise Exception("Invalid shape")
@@ -45,14 +52,26 @@ class ShmTensor(_HostTensorView):
         self.cur_rank, self.cur_world_size, self.cur_group = local_rank, local_world_size, local_group
         self.size_ = nbytes
 
-        if capi.file_exist(name):
-            raise Exception("File name is already exist")
-        dist.barrier(local_group)  # nobody creates before everybody has looked
-
         creator = local_rank == 0
+        error = None
         if creator:
-            self.ptr_, self.fd_ = capi.create_shared_mem(name, nbytes, pin_memory)
-        dist.barrier(local_group)  # segment exists from here on
+            try:
+                if overwrite_stale:
+                    capi.unlink_shared_mem(name)
+                # registration waits until the pages are placed (a pinned page cannot move)
+                self.ptr_, self.fd_ = capi.create_shared_mem(name, nbytes, False, exclusive=True)
+                if numa is not None:
+                    if numa == "interleave":
+                        capi.numa_place(self.ptr_, nbytes, capi.NUMA_INTERLEAVE)
+                    else:
+                        capi.numa_place(self.ptr_, nbytes, capi.NUMA_BIND, int(numa))
+                if pin_memory:
+                    capi._register_range(self.ptr_, nbytes)
+            except Exception as exc:  # noqa: BLE001  told to every rank below
+                error = "File name is already exist" if "already exists" in str(exc) else str(exc)
+        error = self._agree(error, local_group)
+        if error is not None:
+            raise Exception(error)
         if not creator:
             self.ptr_, self.fd_ = capi.open_shared_mem(name, nbytes, pin_memory)
 
@@ -61,15 +80,28 @@ class ShmTensor(_HostTensorView):
                                                self.ptr_, self.fd_, pin_memory)
         self.tensor_ = capi.open_shared_tensor(self.ptr_, dtype, shape)
 
+    @staticmethod
+    def _agree(error, group):
+        """The creating rank's outcome, on every rank (also the point the others wait at)."""
+        if not (dist.is_available() and dist.is_initialized()):
+            return error
+        src = dist.get_global_rank(group, 0) if group is not None else 0
+        box = [error]
+        dist.broadcast_object_list(box, src=src, group=group)
+        return box[0]
+
 
 class DiskTensor(_HostTensorView):
     """A ``.npy`` file mapped read/write (``MAP_SHARED``): writes through the tensor reach the
-    file.  With ``pin_memory`` the whole mapping is registered with CUDA."""
+    file.  With ``pin_memory`` the whole mapping is registered with CUDA.  ``read_only=True``
+    (not in the reference, which maps read/write only) opens and maps the file without write
+    permission, for datasets on read-only media or shared between jobs."""
 
-    def __init__(self, filename, pin_memory=False):
+    def __init__(self, filename, pin_memory=False, read_only=False):
         assert os.path.exists(filename)
         assert filename.endswith('.npy')
-        self.filename_, self.pin_memory_ = filename, pin_memory
-        self.tensor_, self.size_, self.ptr_, self.fd_ = capi.open_mmap_tensor(filename, pin_memory)
+        self.filename_, self.pin_memory_, self.read_only_ = filename, pin_memory, read_only
+        self.tensor_, self.size_, self.ptr_, self.fd_ = capi.open_mmap_tensor(filename, pin_memory,
+                                                                              read_only)
         self._disk_finalizer = weakref.finalize(self, capi.close_mmap_tensor, self.size_,
                                                 self.ptr_, self.fd_, pin_memory)

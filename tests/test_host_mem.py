@@ -132,3 +132,116 @@ def test_shm_tensor_refuses_a_taken_name():
             ShmTensor(name + "x", (0,), 0, 1)
     finally:
         capi.release_shared_mem(name, 16, ptr, fd)
+
+
+def test_exclusive_create_and_unlink():
+    from shmtensor_b200 import capi
+    from shmtensor_b200._lib import ERR_OS, ShmtError
+    name = f"shmt_test_{uuid.uuid4().hex[:8]}"
+    ptr, fd = capi.create_shared_mem(name, 4096, exclusive=True)
+    try:
+        with pytest.raises(ShmtError, match="already exists") as err:
+            capi.create_shared_mem(name, 4096, exclusive=True)
+        assert err.value.code == ERR_OS
+        p2, fd2 = capi.create_shared_mem(name, 4096)      # the reference's create: opens what is there
+        capi.open_shared_tensor(ptr, torch.int32, (4,))[:] = 7
+        assert capi.open_shared_tensor(p2, torch.int32, (4,)).tolist() == [7, 7, 7, 7]
+    finally:
+        capi.release_shared_mem(name, 4096, ptr, fd)
+    assert not capi.file_exist(name)
+    capi.unlink_shared_mem(name)                          # absent name: not an error
+
+
+def test_shm_tensor_overwrites_a_stale_segment_when_asked():
+    from shmtensor_b200 import ShmTensor, capi
+    name = f"shmt_test_{uuid.uuid4().hex[:8]}"
+    ptr, fd = capi.create_shared_mem(name, 64)            # what a killed run leaves behind
+    capi.open_shared_tensor(ptr, torch.int64, (8,))[:] = -5
+    t = ShmTensor(name, (8,), 0, 1, None, torch.int64, overwrite_stale=True)
+    assert (t.tensor_ == 0).all()                         # a new segment, not the old bytes
+    t.tensor_[:] = 3
+    assert capi.open_shared_tensor(ptr, torch.int64, (8,)).tolist() == [-5] * 8
+    del t
+    assert not capi.file_exist(name)
+    import ctypes as C
+    from shmtensor_b200._lib import lib                   # drop the stale mapping (name already gone)
+    C.CDLL(None).munmap(C.c_void_p(ptr), C.c_size_t(64))
+    os.close(fd)
+
+
+def test_numa_placement_of_a_fresh_segment():
+    from shmtensor_b200 import ShmTensor, capi
+    assert capi.numa_nodes() >= 1
+    name = f"shmt_test_{uuid.uuid4().hex[:8]}"
+    t = ShmTensor(name, (1 << 20,), 0, 1, None, torch.float32, numa="interleave")
+    t.tensor_[:] = 1.5
+    assert float(t.tensor_.sum()) == 1.5 * (1 << 20)
+    del t
+    u = ShmTensor(name, (1 << 20,), 0, 1, None, torch.float32, numa=0)
+    u.tensor_[:] = 2.0
+    assert float(u.tensor_[-1]) == 2.0
+    del u
+    with pytest.raises(Exception, match="holds no memory"):
+        ShmTensor(name, (1 << 20,), 0, 1, None, torch.float32, numa=977)
+    capi.unlink_shared_mem(name)
+
+
+def test_disk_tensor_read_only_and_bfloat16(tmp_path):
+    from shmtensor_b200 import DiskTensor
+    arr = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    path = str(tmp_path / "ro.npy")
+    np.save(path, arr)
+    os.chmod(path, 0o444)
+    t = DiskTensor(path, read_only=True)                  # a file this process may not write
+    assert torch.equal(t.tensor_, torch.from_numpy(arr))
+    del t
+    os.chmod(path, 0o644)
+    # bfloat16 rows saved as opaque 2-byte items, the form numpy can carry them in
+    rows = torch.randn(5, 8).to(torch.bfloat16)
+    path2 = str(tmp_path / "bf16.npy")
+    np.save(path2, rows.view(torch.int16).numpy().view("V2"))
+    b = DiskTensor(path2)
+    assert b.dtype == torch.bfloat16 and torch.equal(b.tensor_.view(torch.int16), rows.view(torch.int16))
+
+
+TAKEN_WORKER = textwrap.dedent("""
+    import sys, torch, torch.distributed as dist
+    sys.path.insert(0, {root!r})
+    from shmtensor_b200 import ShmTensor
+    dist.init_process_group(backend='gloo', init_method='env://')
+    try:
+        ShmTensor({name!r}, (8,), dist.get_rank(), dist.get_world_size(), None, torch.int16)
+    except Exception as exc:
+        assert 'already exist' in str(exc), exc
+        print('rank', dist.get_rank(), 'refused')
+    else:
+        raise SystemExit('a taken name was accepted')
+    t = ShmTensor({name!r}, (8,), dist.get_rank(), dist.get_world_size(), None, torch.int16,
+                  overwrite_stale=True)
+    dist.barrier()
+    del t
+""")
+
+
+def test_a_taken_name_fails_on_every_rank_instead_of_hanging(tmp_path):
+    from shmtensor_b200 import capi
+    name = f"shmt_test_{uuid.uuid4().hex[:8]}"
+    ptr, fd = capi.create_shared_mem(name, 16)
+    try:
+        script = tmp_path / "worker.py"
+        script.write_text(TAKEN_WORKER.format(root=str(ROOT), name=name))
+        port = 31500 + os.getpid() % 2000
+        procs = []
+        for rank in range(2):
+            env = dict(os.environ, RANK=str(rank), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1",
+                       MASTER_PORT=str(port), OMP_NUM_THREADS="1")
+            procs.append(subprocess.Popen([sys.executable, str(script)], env=env,
+                                          stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+        outs = [p.communicate(timeout=120)[0] for p in procs]
+        assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+        assert all("refused" in o for o in outs)
+    finally:
+        import ctypes as C
+        C.CDLL(None).munmap(C.c_void_p(ptr), C.c_size_t(16))
+        os.close(fd)
+        capi.unlink_shared_mem(name)
