@@ -20,6 +20,7 @@ on the host cores.  Data is synthetic and seeded.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import statistics
@@ -40,6 +41,7 @@ CACHE_FRACTION, LOAD_FACTOR, ZIPF_ALPHA, UNIFORM_SHARE = 0.20, 0.5, 1.1, 0.21
 ROW_BYTES = DIM * 4
 N_BATCHES = 8
 METRIC, UNIT = "fetched feature GB/s", "GB/s"
+PG_TIMEOUT = datetime.timedelta(minutes=6)  # a rank that failed ends the others' next collective
 NCU_DRAM_BYTES_PER_LAUNCH = 210_300_000  # 63.8 MB read + 146.5 MB written (ncu, headline batch)
 WORKLOAD = ("1-GPU cached feature fetch: pinned 2,400,000x100 f32 host table, top 20% rows cached "
             "behind int64->int32 map (load 0.5), 500,000 int64 ids/batch Zipf(1.1), ~80% hits, misses via UVA")
@@ -128,6 +130,72 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
+class PcieSampler:
+    """Polls NVML's PCIe receive counter (bytes the GPU took in over its host link, averaged by
+    the driver over 20 ms windows) while a loop runs.  Read-only."""
+
+    def __init__(self, index: int, period_s: float = 0.03):
+        self.kbs, self._stop, self._thread = [], threading.Event(), None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv, self._h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._thread = threading.Thread(target=self._run, args=(period_s,), daemon=True)
+        except Exception:  # noqa: BLE001
+            self._nv = None
+
+    def _run(self, period_s):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.kbs.append(nv.nvmlDeviceGetPcieThroughput(self._h, nv.NVML_PCIE_UTIL_RX_BYTES))
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop.wait(period_s)
+
+    def start(self):
+        if self._thread:
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+        busy = [k for k in self.kbs if k > 1e6]  # windows in which the loop was running (> 1 GB/s)
+        if not busy:
+            return None
+        return {"median_gbs": round(statistics.median(busy) * 1e3 / 1e9, 2), "max_gbs": round(max(busy) * 1e3 / 1e9, 2),
+                "samples": len(busy)}
+
+
+def measure_read_rate_ceilings(host_table: torch.Tensor, stream) -> dict:
+    """Rates of independent small reads this GPU sustains, by the random-read probe: random
+    32-byte sectors of a 4 GiB HBM buffer (what bounds hash probes and relabel tables beyond L2),
+    of a 128 MiB buffer (a table that L2 largely holds), and random 16/32-byte reads of the pinned
+    host table (what bounds sampling on rows whose adjacency is in host memory)."""
+    from shmtensor_b200._lib import check, lib
+    sink = torch.zeros(1, dtype=torch.int64, device="cuda")
+    out = {}
+    big = torch.empty(1 << 32, dtype=torch.uint8, device="cuda")
+    def rate(ptr, nbytes, n_reads, unit):
+        fn = lambda c=[0]: (check(lib.shmt_random_read(ptr, nbytes, n_reads, unit, c[0], sink.data_ptr(),
+                                                       stream.cuda_stream)), c.__setitem__(0, c[0] + 1))
+        fn()
+        ms = min(time_launches(fn, 1, stream) for _ in range(5))
+        return round(n_reads / (ms * 1e-3) / 1e9, 3)
+    out["hbm_random_32B_reads_G_per_s_4GiB"] = rate(big.data_ptr(), 1 << 32, 1 << 26, 32)
+    out["hbm_random_64B_reads_G_per_s_4GiB"] = rate(big.data_ptr(), 1 << 32, 1 << 26, 64)
+    out["hbm_random_64B_reads_G_per_s_128MiB"] = rate(big.data_ptr(), 1 << 27, 1 << 26, 64)
+    out["hbm_random_16B_reads_G_per_s_16MiB"] = rate(big.data_ptr(), 1 << 24, 1 << 26, 16)
+    del big
+    nbytes = host_table.numel() * host_table.element_size()
+    out["host_link_random_16B_reads_G_per_s"] = rate(host_table.data_ptr(), nbytes, 1 << 22, 16)
+    out["host_link_random_32B_reads_G_per_s"] = rate(host_table.data_ptr(), nbytes, 1 << 22, 32)
+    out["host_link_random_128B_reads_G_per_s"] = rate(host_table.data_ptr(), nbytes, 1 << 22, 128)
+    out["how"] = "shmt_random_read: independent reads at pseudo-random aligned offsets, 4 per thread in flight, best of 5"
+    return out
+
+
 # --------------------------------------------------------------------------- helpers
 def measured_peaks() -> tuple:
     p = ROOT / "MEASURED_PEAKS.json"
@@ -197,19 +265,82 @@ def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
 
 
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1 to its workers; a CPU arm timed that way uses one core
+    of the box.  Give torch (and OpenMP libraries loaded later) every core this process may run on."""
+    n = len(os.sched_getaffinity(0))
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    torch.set_num_threads(n)
+    return n
+
+
+def replicated_rows(n_cached: int, world: int) -> int:
+    """Rows of the cached set that every GPU keeps (bench policy, both arms name it in `config`):
+    the smallest head of the hotness ranking that takes half of the cached lookups of a batch,
+    but at least the library's default."""
+    if world <= 1:
+        return 0
+    from shmtensor_b200.partition import default_replication, head_for_mass
+    w = 1.0 / np.arange(1, n_cached + 1, dtype=np.float64) ** ZIPF_ALPHA
+    return max(default_replication(n_cached, world), head_for_mass(torch.from_numpy(w), 0.5))
+
+
+def fetch_config(world: int, hit_rate: float, numa: str) -> dict:
+    """`config` of the headline workload; both arms print exactly this."""
+    n_cached = int(ROWS * CACHE_FRACTION)
+    return {"workload": WORKLOAD, "rows": ROWS, "dim": DIM, "batch": BATCH, "cached_rows": n_cached,
+            "hit_rate": round(hit_rate, 4),
+            "l2": "inputs larger than L2: 192 MB cached rows + 200 MB output per launch, "
+                  f"{N_BATCHES} distinct query batches rotated",
+            "partition": "single GPU" if world == 1 else
+            f"hash-partitioned over {world} GPUs, NVLink P2P loads; the {replicated_rows(n_cached, world)} "
+            f"hottest rows on every GPU; host table pages: {numa}"}
+
+
+def host_numa_mode(world: int) -> str:
+    """Where the shared host table's pages go when several GPUs read it."""
+    return "one rank's first touch" if world == 1 else os.environ.get("SHMT_BENCH_NUMA", "interleave")
+
+
+def gpu_numa_node(index: int):
+    """Memory node the GPU's PCIe root port hangs off (None if the kernel does not say)."""
+    try:
+        p = torch.cuda.get_device_properties(index)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        return int(Path(f"/sys/bus/pci/devices/{bdf}/numa_node").read_text())
+    except Exception:  # noqa: BLE001
+        return None
+
+
+def pages_per_node(ptr: int) -> dict:
+    """Pages of the mapping that starts at `ptr`, per memory node (/proc/self/numa_maps)."""
+    try:
+        want = f"{ptr:012x}"
+        for ln in Path("/proc/self/numa_maps").read_text().splitlines():
+            if ln.split(" ", 1)[0].rjust(12, "0") == want:
+                return {tok.split("=")[0]: int(tok.split("=")[1]) for tok in ln.split() if tok[0] == "N" and "=" in tok}
+    except Exception:  # noqa: BLE001
+        pass
+    return {}
+
+
 # --------------------------------------------------------------------------- reference arm
 def run_reference(args) -> None:
     """The reference's CPU path for this fetch, on the host cores: torch.index_select over the
-    host table (its ``cpu_fetch`` line).  Rank 0 only; no GPU work."""
+    host table (its ``cpu_fetch`` line).  Rank 0 only."""
     rank, _, world = dist_env()
     if rank != 0:
         return
     from oracle import oracle
+    cores = use_all_host_threads()
     table = torch.empty(ROWS, DIM)
     fill_table(table)
     scores = make_scores()
     ranking = np.argsort(-scores, kind="stable")
     batches = make_batches(ranking, N_BATCHES, seed=100)
+    cached = np.zeros(ROWS, dtype=bool)
+    cached[ranking[:int(ROWS * CACHE_FRACTION)]] = True
+    hit_rate = float(np.mean([cached[b.numpy()].mean() for b in batches]))
     for i in range(args.warmup):
         oracle.cpu_fetch_reference(table, batches[i % N_BATCHES])
     t0 = time.perf_counter()
@@ -217,24 +348,71 @@ def run_reference(args) -> None:
         out = oracle.cpu_fetch_reference(table, batches[i % N_BATCHES])
     dt = time.perf_counter() - t0
     value = args.steps * BATCH * ROW_BYTES / dt / 1e9
-    cores = torch.get_num_threads()
+    # the reference's own script line ends on the GPU: `data[q.cpu()].cuda()`
+    # (example/test_cache_fetch.py:138); timed as well when this box has a GPU
+    gpu_resident = None
+    if torch.cuda.is_available():
+        n = max(3, min(args.steps, 10))
+        oracle.cpu_fetch_reference(table, batches[0]).cuda()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(n):
+            res = oracle.cpu_fetch_reference(table, batches[i % N_BATCHES]).cuda()
+        torch.cuda.synchronize()
+        gpu_resident = n * BATCH * ROW_BYTES / (time.perf_counter() - t0) / 1e9
+        del res
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 3), "unit": UNIT,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(dt / args.steps * 1e3, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 rows, int64 ids (byte copy)", "data": "synthetic (seeded)",
-        "config": {"workload": WORKLOAD, "rows": ROWS, "dim": DIM, "batch": BATCH},
+        "config": fetch_config(args.gpus, hit_rate, host_numa_mode(args.gpus)),
         "cpu_baseline": {"value": round(value, 3), "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{args.steps} full batches of 500,000 ids; torch.index_select on the host "
                                    "table = the reference's cpu_fetch (example/test_cache_fetch.py:138), "
                                    f"{cores} threads of {os.cpu_count()} logical cores"},
-        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "e2e": {"value": round(value, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "result_in": "host memory"},
+        "e2e_gpu_resident": None if gpu_resident is None else {
+            "value": round(gpu_resident, 3), "unit": UNIT, "h2d_bytes_per_step": BATCH * ROW_BYTES,
+            "what": "data[q].cuda(): index_select on the host cores, then the 200 MB result copied to the GPU "
+                    "(the line example/test_cache_fetch.py:138 times)"},
     }
     assert out.shape == (BATCH, DIM)
     emit(line)
 
 
 # --------------------------------------------------------------------------- our arm
+def bind_to_gpu_node(local_rank: int):
+    """Run this rank's host threads on the cores of its GPU's memory node (where the kernel
+    says which that is and the process may run there).  Returns (node, cores now allowed)."""
+    node = gpu_numa_node(local_rank)
+    try:
+        if node is not None and node >= 0:
+            txt = Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip()
+            cpus = set()
+            for part in txt.split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+            cpus &= os.sched_getaffinity(0)
+            if cpus:
+                os.sched_setaffinity(0, cpus)
+    except Exception:  # noqa: BLE001  placement of host threads is an optimisation only
+        pass
+    return node, len(os.sched_getaffinity(0))
+
+
+def all_gather_floats(values, world, dev):
+    """[rank][i] of a small list of floats."""
+    import torch.distributed as dist
+    t = torch.tensor(values, device=dev, dtype=torch.float64)
+    if world == 1:
+        return [t.tolist()]
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [o.tolist() for o in out]
+
+
 def run_ours(args) -> None:
     rank, local_rank, world = dist_env()
     if world != args.gpus and world > 1:
@@ -246,22 +424,22 @@ def run_ours(args) -> None:
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # stdout carries the one JSON line only
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=PG_TIMEOUT)
+    node, n_cores = bind_to_gpu_node(local_rank) if world > 1 else (gpu_numa_node(local_rank), len(os.sched_getaffinity(0)))
 
     import shmtensor_b200 as st
     from shmtensor_b200 import capi
-    from shmtensor_b200.partition import PartitionedFeatureCache
+    from shmtensor_b200._lib import check, lib
+    from shmtensor_b200.partition import OWNER_SHIFT, PartitionedFeatureCache
 
     stream = torch.cuda.current_stream()
+    numa_mode = host_numa_mode(world)
 
     # ---- data: host table shared by the ranks of the node, pinned; cache; batches
     if world > 1:
         name = f"shmt_bench_{os.environ.get('MASTER_PORT', '0')}"
-        if rank == 0 and capi.file_exist(name):  # stale segment of a killed run
-            p, fd = capi.open_shared_mem(name, ROWS * ROW_BYTES)
-            capi.release_shared_mem(name, ROWS * ROW_BYTES, p, fd)
-        dist.barrier()
-        shm = st.ShmTensor(name, (ROWS, DIM), rank, world, None, torch.float32, pin_memory=True)
+        shm = st.ShmTensor(name, (ROWS, DIM), rank, world, None, torch.float32, pin_memory=True,
+                           overwrite_stale=True, numa="interleave" if numa_mode == "interleave" else None)
         table = shm.tensor_
         if rank == 0:
             fill_table(table)
@@ -287,7 +465,8 @@ def run_ours(args) -> None:
         query = hmap.query
         pcache = None
     else:
-        pcache = PartitionedFeatureCache(table, cached_ids, load_factor=LOAD_FACTOR)
+        pcache = PartitionedFeatureCache(table, cached_ids, load_factor=LOAD_FACTOR,
+                                         replicate=replicated_rows(n_cached, world))
         fetch = pcache.fetch
         query = pcache.directory.query
     hit_counts = [int((query(b) >= 0).sum().item()) for b in batches]
@@ -295,9 +474,8 @@ def run_ours(args) -> None:
 
     # ---- set-up, not timed: one streaming pass over the whole host table from this GPU, so that
     #      every page of it has been translated once (GPU TLB / IOMMU) before any step is timed
-    from shmtensor_b200._lib import check as _check, lib as _lib_
     _sink = torch.zeros(1, dtype=torch.int64, device=dev)
-    _check(_lib_.shmt_stream_read(table.data_ptr(), ROWS * ROW_BYTES, _sink.data_ptr(), stream.cuda_stream))
+    check(lib.shmt_stream_read(table.data_ptr(), ROWS * ROW_BYTES, _sink.data_ptr(), stream.cuda_stream))
     torch.cuda.synchronize()
 
     # ---- parity on one batch before timing anything (bit-exact vs the host table)
@@ -336,6 +514,7 @@ def run_ours(args) -> None:
     print(f"[rank {rank}] timed region {region_ms:.3f} ms, launches min/median/max "
           f"{min(per_launch):.3f}/{statistics.median(per_launch):.3f}/{max(per_launch):.3f} ms, "
           f"first five {[round(x, 3) for x in per_launch[:5]]}", file=sys.stderr, flush=True)
+    my_kernel_ms, my_hit_rate = kernel_ms, hit_rate
     if world > 1:
         t = torch.tensor([region_ms, kernel_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -344,55 +523,131 @@ def run_ours(args) -> None:
     value = world * BATCH * ROW_BYTES / (ms_per_step * 1e6)
 
     # ---- end to end through the public call: ids from pinned host memory each step, the last
-    #      fetched row read back to pinned host memory
+    #      fetched row read back to pinned host memory (the rows stay on the GPU, as the
+    #      reference's result does) ...
     ids_dev = torch.empty(BATCH, dtype=torch.int64, device=dev)
     tail = torch.empty(DIM, dtype=torch.float32).pin_memory()
-    e2e_steps = args.steps
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    region[0].record(stream)
-    for i in range(e2e_steps):
-        ids_dev.copy_(batches_host[i % N_BATCHES], non_blocking=True)
-        out = fetch(ids_dev)
-        tail.copy_(out[-1], non_blocking=True)
-        stream.synchronize()
-    region[1].record(stream)
-    torch.cuda.synchronize()
-    e2e_ms = region[0].elapsed_time(region[1]) / e2e_steps
-    e2e_wall_ms = (time.perf_counter() - t0) * 1e3 / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = t.item()
+
+    def e2e_loop(read_back, steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        region[0].record(stream)
+        for i in range(steps):
+            ids_dev.copy_(batches_host[i % N_BATCHES], non_blocking=True)
+            res = fetch(ids_dev)
+            read_back(res)
+            stream.synchronize()
+        region[1].record(stream)
+        torch.cuda.synchronize()
+        ms = region[0].elapsed_time(region[1]) / steps
+        wall = (time.perf_counter() - t0) * 1e3 / steps
+        if world > 1:
+            t_ = torch.tensor([ms], device=dev)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            ms = t_.item()
+        return ms, wall
+
+    e2e_ms, e2e_wall_ms = e2e_loop(lambda res: tail.copy_(res[-1], non_blocking=True), args.steps)
     e2e_value = world * BATCH * ROW_BYTES / (e2e_ms * 1e6)
+    # ... and with the whole 200 MB result copied out to pinned host memory, which is where the
+    # CPU arm's result lies
+    full_host = torch.empty(BATCH, DIM, dtype=torch.float32).pin_memory()
+    host_steps = max(3, min(args.steps, 20))
+    e2e_loop(lambda res: full_host.copy_(res, non_blocking=True), 2)
+    e2e_host_ms, _ = e2e_loop(lambda res: full_host.copy_(res, non_blocking=True), host_steps)
+    assert torch.equal(full_host.view(torch.int32),
+                       torch.index_select(table, 0, batches_host[(host_steps - 1) % N_BATCHES]).view(torch.int32))
+    del full_host
 
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 rows, int64 ids (byte copy)",
         "data": "synthetic (seeded)",
-        "config": {"workload": WORKLOAD, "rows": ROWS, "dim": DIM, "batch": BATCH, "cached_rows": n_cached,
-                   "hit_rate": round(hit_rate, 4),
-                   "l2": "inputs larger than L2: 192 MB cached rows + 200 MB output per launch, "
-                         f"{N_BATCHES} distinct query batches rotated",
-                   "partition": "single GPU" if world == 1 else
-                   f"hash-partitioned over {world} GPUs, NVLink P2P loads; the {pcache.replicated} hottest rows on every GPU"},
+        "config": fetch_config(world, hit_rate, numa_mode),
         "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": BATCH * 8,
                 "d2h_bytes_per_step": DIM * 4, "ms_per_step": round(e2e_ms, 5),
-                "wall_ms_per_step": round(e2e_wall_ms, 5)},
+                "wall_ms_per_step": round(e2e_wall_ms, 5),
+                "result_in": "GPU memory (as the reference's cache_fetch returns it); one row read back"},
+        "e2e_host_result": {"value": round(world * BATCH * ROW_BYTES / (e2e_host_ms * 1e6), 2), "unit": UNIT,
+                            "h2d_bytes_per_step": BATCH * 8, "d2h_bytes_per_step": BATCH * ROW_BYTES,
+                            "ms_per_step": round(e2e_host_ms, 5), "steps": host_steps,
+                            "result_in": "pinned host memory: the whole fetched batch copied out every step, "
+                                         "checked bit-exact"},
         "gpu_launches": args.steps,
         "clocks": clocks,
     }
 
-    # ---- N > 1: the NVLink regime -- ids all cached, (N-1)/N of the rows on a peer GPU
+    # ---- N > 1: what every rank saw, the host link under concurrent load, the NVLink regime
     if world > 1:
-        from shmtensor_b200._lib import check, lib
         from shmtensor_b200.partition import _DeviceBuffer, share_device_buffer
+        sink = torch.zeros(1, dtype=torch.int64, device=dev)
+        n_hit = sum(hit_counts[i % N_BATCHES] for i in range(args.steps)) / args.steps
+        # rows by where they came from (first batch): own shard, a peer's shard, the host table
+        v = query(batches[0])
+        n_local = int(((v >= 0) & ((v >> OWNER_SHIFT) == rank)).sum().item())
+        n_remote = int(((v >= 0) & ((v >> OWNER_SHIFT) != rank)).sum().item())
+
+        # host link with every GPU of the job reading at once: a streaming pass over the shared
+        # table (the ceiling), then the same kernel as the headline on ids that all miss
+        nbytes = ROWS * ROW_BYTES
+        def timed_together(fn, reps):
+            best = 1e30
+            for _ in range(reps):
+                dist.barrier()
+                torch.cuda.synchronize()
+                best = min(best, time_launches(fn, 1, stream))
+            return best
+        conc_ms = timed_together(lambda: check(lib.shmt_stream_read(table.data_ptr(), nbytes, sink.data_ptr(),
+                                                                     stream.cuda_stream)), 4)
+        cold_ids = torch.from_numpy(ranking[n_cached:].copy())
+        g = torch.Generator().manual_seed(500 + rank)
+        cold_batches = [cold_ids[torch.randint(0, cold_ids.numel(), (BATCH,), generator=g)].to(dev) for _ in range(2)]
+        fetch(cold_batches[0])
+        miss_ms = timed_together(lambda c=[0]: (fetch(cold_batches[c[0] % 2]), c.__setitem__(0, c[0] + 1)), 3)
+        # one GPU at a time (rank 0, then the last rank: the two ends of the PCIe tree)
+        solo = {}
+        for r in sorted({0, world - 1}):
+            dist.barrier()
+            if rank == r:
+                torch.cuda.synchronize()
+                solo_ms = min(time_launches(lambda: check(lib.shmt_stream_read(
+                    table.data_ptr(), nbytes, sink.data_ptr(), stream.cuda_stream)), 1, stream) for _ in range(3))
+            else:
+                solo_ms = 0.0
+            t_ = torch.tensor([solo_ms], device=dev)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            solo[r] = round(nbytes / (t_.item() * 1e6), 2)
+        per_rank = all_gather_floats([my_kernel_ms, BATCH - n_hit, float(node if node is not None else -1),
+                                      nbytes / (conc_ms * 1e6), BATCH * ROW_BYTES / (miss_ms * 1e6),
+                                      float(n_local), float(n_remote), float(n_cores)], world, dev)
+        line["per_rank"] = [{
+            "rank": r, "gpu_numa_node": int(p[2]), "host_cores_bound": int(p[7]), "kernel_ms": round(p[0], 4),
+            "miss_rows_per_step": round(p[1]), "miss_gbs": round(p[1] * ROW_BYTES / (p[0] * 1e6), 2),
+            "link_ceiling_concurrent_gbs": round(p[3], 2),
+            "miss_frac_of_concurrent_ceiling": round(p[1] * ROW_BYTES / (p[0] * 1e6) / p[3], 4),
+            "all_miss_concurrent_gbs": round(p[4], 2),
+            "rows_local_remote_host_first_batch": [int(p[5]), int(p[6]), BATCH - int(p[5]) - int(p[6])],
+        } for r, p in enumerate(per_rank)]
+        line["roofline_link"] = {
+            "bound": "host_link", "unit": "GB/s",
+            "concurrent_peak_gbs": [round(p[3], 2) for p in per_rank],
+            "concurrent_peak_total_gbs": round(sum(p[3] for p in per_rank), 1),
+            "solo_peak_gbs": solo,
+            "achieved": [round(p[1] * ROW_BYTES / (p[0] * 1e6), 2) for p in per_rank],
+            "frac": [round(p[1] * ROW_BYTES / (p[0] * 1e6) / p[3], 4) for p in per_rank],
+            "peak_source": "shmt_stream_read over the shared pinned host table, all ranks at the same time, "
+                           "best of 4 (solo: one rank alone)",
+            "host_table_pages_per_node": pages_per_node(table.data_ptr()), "numa_nodes": capi.numa_nodes(),
+            "host_table_placement": numa_mode,
+            "note": "the headline batch is bound by its misses over the host link; frac = a rank's miss bytes per "
+                    "kernel time / what the same rank reads from the same table when all ranks stream from it"}
+
+        # the NVLink regime: ids all cached, most rows on a peer
         probe = _DeviceBuffer(256 << 20)
         ptrs, opened = share_device_buffer(probe)
-        sink = torch.zeros(1, dtype=torch.int64, device=dev)
         peer = ptrs[(rank + 1) % world]
         peer_ms = min(time_launches(lambda: check(lib.shmt_stream_read(peer, 256 << 20, sink.data_ptr(),
                                                                         stream.cuda_stream)), 1, stream)
@@ -408,8 +663,8 @@ def run_ours(args) -> None:
         ms_hit, peer_ms = t.tolist()
         peer_gbs = (256 << 20) / (peer_ms * 1e6)
         # rows that really came from a peer (the hottest ids are replicated on every rank)
-        n_remote = sum(int(((pcache.directory.query(b) >> 40) != rank).sum().item()) for b in hot_batches) / 4
-        t = torch.tensor([n_remote], device=dev)
+        n_rem = sum(int(((pcache.directory.query(b) >> OWNER_SHIFT) != rank).sum().item()) for b in hot_batches) / 4
+        t = torch.tensor([n_rem], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
         remote_bytes = t.item() * ROW_BYTES
         line["roofline_all_hit_partitioned"] = {
@@ -421,26 +676,11 @@ def run_ours(args) -> None:
             "what": "ids uniform over the cached set: about 1/N of the rows local, the rest read from peers over "
                     "NVLink; achieved = remote row bytes per rank (the least over ranks) / slowest rank's kernel time",
             "replicated_rows_per_gpu": pcache.replicated}
-        # the batched alternative (NCCL all-to-all of ids, then of rows) on the same batches
-        a2a = pcache.fetch_alltoall(batches[0])
-        assert torch.equal(a2a.view(torch.int32), fetch(batches[0]).view(torch.int32)), "all-to-all route differs"
-        def a2a_ms(bs, reps):
-            for b in bs[:2]:
-                pcache.fetch_alltoall(b)
-            dist.barrier()
-            t_ = time_launches(lambda c=[0]: (pcache.fetch_alltoall(bs[c[0] % len(bs)]), c.__setitem__(0, c[0] + 1)),
-                               reps, stream)
-            t_ = torch.tensor([t_], device=dev)
-            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
-            return t_.item()
-        line["alltoall_route"] = {"mixed_ms": round(a2a_ms(batches, 10), 4), "all_hit_ms": round(a2a_ms(hot_batches, 10), 4),
-                                  "p2p_mixed_ms": round(ms_per_step, 4), "p2p_all_hit_ms": round(ms_hit, 4),
-                                  "what": "PartitionedFeatureCache.fetch_alltoall (ids bucketed by owner, NCCL all-to-all of "
-                                          "ids and of rows, misses read locally) against the fused peer-load kernel"}
         # the other way to spend N GPUs: every GPU keeps the cache budget of the 1-GPU run (480,000 rows),
         # so the partitioned cache holds N times as many ids and fewer rows cross the host link
         n_grown = min(world * n_cached, ROWS)
-        grown = PartitionedFeatureCache(table, torch.from_numpy(ranking[:n_grown].copy()), load_factor=LOAD_FACTOR)
+        grown = PartitionedFeatureCache(table, torch.from_numpy(ranking[:n_grown].copy()), load_factor=LOAD_FACTOR,
+                                        replicate=replicated_rows(n_cached, world))
         got = grown.fetch(batches[0])
         assert torch.equal(got.cpu().view(torch.int32),
                            torch.index_select(table, 0, batches_host[0]).view(torch.int32)), "grown cache differs"
@@ -492,7 +732,8 @@ def run_ours(args) -> None:
         line["roofline_link"] = {
             "bound": "host_link", "achieved": round(link_bytes / (kernel_ms * 1e6), 2), "peak": link["peak_gbs"],
             "unit": "GB/s", "frac": round(link_bytes / (kernel_ms * 1e6) / link["peak_gbs"], 4),
-            "peak_source": "measured in this run", **link}
+            "peak_source": "measured in this run", **link, "gpu_numa_node": node,
+            "host_table_pages_per_node": pages_per_node(table.data_ptr())}
         # same kernel, all ids cached (HBM-bound regime) and no cache at all (link-bound regime)
         hot_batches = [cached_ids[torch.randint(0, n_cached, (BATCH,), generator=torch.Generator().manual_seed(s))].to(dev)
                        for s in range(4)]
@@ -510,12 +751,21 @@ def run_ours(args) -> None:
                         for s in range(4)]
         for b in cold_batches[:2]:
             fetch(b)
-        ms_miss = time_launches(lambda c=[0]: (fetch(cold_batches[c[0] % 4]), c.__setitem__(0, c[0] + 1)), 10, stream)
+        pcie = PcieSampler(local_rank)
+        pcie.start()
+        ms_miss = time_launches(lambda c=[0]: (fetch(cold_batches[c[0] % 4]), c.__setitem__(0, c[0] + 1)), 40, stream)
+        rx = pcie.stop()
         line["roofline_all_miss"] = {"bound": "host_link", "achieved": round(BATCH * ROW_BYTES / (ms_miss * 1e6), 2),
                                      "peak": link["peak_gbs"], "unit": "GB/s",
                                      "frac": round(BATCH * ROW_BYTES / (ms_miss * 1e6) / link["peak_gbs"], 4),
                                      "kernel_ms": round(ms_miss, 5),
-                                     "ids": "uniform over the 1,920,000 uncached rows, probed and missed"}
+                                     "ids": "uniform over the 1,920,000 uncached rows, probed and missed",
+                                     # bytes the GPU received over PCIe while that loop ran, by NVML's counter
+                                     "nvml_pcie_rx_gbs": rx,
+                                     "link_bytes_per_row_by_nvml": None if not rx or not rx.get("median_gbs") else
+                                     round(rx["median_gbs"] * 1e9 * (ms_miss * 1e-3) / BATCH, 1)}
+        # ceilings of the kernels that are bound by a rate of small reads, not by bytes
+        line["ceilings"] = measure_read_rate_ceilings(table, stream)
         # the reference's own fetch kernel on the same GPU and batches, when oracle/_ref was built
         try:
             from oracle import build_ref
@@ -555,19 +805,40 @@ def run_ours(args) -> None:
                       f"table (the reference's cpu_fetch, example/test_cache_fetch.py:138); {cores} threads of "
                       f"{os.cpu_count()} logical cores"}
 
-    if rank == 0:
-        emit(line)
-
-    # ---- orderly teardown: nothing in flight, peers unmapped before any shard is freed
+    # ---- orderly teardown of the fetch workload: nothing in flight, peers unmapped before any
+    #      shard is freed
     torch.cuda.synchronize()
     if pcache is not None:
         pcache.close()
     if world == 1:
         capi.unpin_memory(table)
+        del gpu_rows, hmap
     else:
         dist.barrier()
-        del table, pcache
+        del pcache
         shm = None
+    del table, batches, out, fetch, query
+    torch.cuda.empty_cache()
+
+    # ---- the rest of the metric, in the same line: sampled edges/s and the cache update on one
+    #      GPU; the end-to-end mini-batch over the partitioned cache on several
+    if os.environ.get("SHMT_BENCH_ONLY_FETCH") != "1":
+        sub_steps = max(5, min(args.steps, 50))
+        def guarded(fn, *a):
+            # a failure here must not cost the headline its line
+            try:
+                return fn(*a)
+            except Exception as exc:  # noqa: BLE001
+                import traceback
+                traceback.print_exc(file=sys.stderr)
+                return {"error": f"{type(exc).__name__}: {exc}"[:500]}
+        if world == 1:
+            line["sampling"] = guarded(sampling_object, sub_steps, local_rank, True)
+            line["update"] = guarded(update_object, max(3, min(args.steps, 10)), local_rank)
+        line["minibatch_c4"] = guarded(minibatch_object, max(5, min(args.steps, 20)), rank, local_rank, world)
+    if rank == 0:
+        emit(line)
+    if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
@@ -629,342 +900,578 @@ def minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds):
     return sum(h[1].numel() for h in hops), frontier
 
 
-def run_sampling(args) -> None:
-    rank, local_rank, world = dist_env()
-    if rank != 0:
-        return
+def cpu_minibatch(lib, indptr_n, indices_n, seeds32):
+    """One 3-hop mini-batch by the threaded C++ restatement of the reference's sampler and
+    relabel (the reference has no CPU sampler of its own)."""
+    seeds = seeds32.astype(np.int64)
+    edges = 0
+    for k in reversed(FANOUT):
+        sp = np.empty(seeds.size + 1, np.int64)
+        so = np.empty(seeds.size * k, np.int32)
+        nnz = lib.oracle_sample_hop(indptr_n.ctypes.data, indices_n.ctypes.data, 0, seeds.ctypes.data,
+                                    seeds.size, k, 0, 7777, sp.ctypes.data, so.ctypes.data)
+        cat = np.concatenate([seeds, so[:nnz].astype(np.int64)])
+        uniq, rel = np.empty(cat.size, np.int64), np.empty(cat.size, np.int64)
+        nu = lib.oracle_relabel(cat.ctypes.data, cat.size, uniq.ctypes.data, rel.ctypes.data)
+        seeds = uniq[:nu].copy()
+        edges += int(nnz)
+    return edges, seeds
+
+
+def sampling_reference_line(args, line, indptr_n, indices_n, seed_batches) -> None:
+    from oracle import build_oracle
+    use_all_host_threads()
+    lib = build_oracle.load_cpu()
+    for i in range(max(args.warmup, 1)):
+        cpu_minibatch(lib, indptr_n, indices_n, seed_batches[i % 32])
+    t0 = time.perf_counter()
+    edges = sum(cpu_minibatch(lib, indptr_n, indices_n, seed_batches[i % 32])[0] for i in range(args.steps))
+    dt = time.perf_counter() - t0
+    v = edges / dt
+    line.update({"impl": "reference", "value": round(v, 1), "ms_per_step": round(dt / args.steps * 1e3, 4),
+                 "cpu_baseline": {"value": round(v, 1), "unit": "edges/s", "cores": lib.oracle_num_threads(),
+                                  "kind": "port", "sample": f"{args.steps} full 3-hop mini-batches; threaded C++ "
+                                  "restatement of the reference's sampler (seeds split over threads) + serial relabel"},
+                 "e2e": {"value": round(v, 1), "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    emit(line)
+
+
+def sampling_object(steps: int, local_rank: int, full: bool = True) -> dict:
+    """Config 3 on one GPU: sampled edges/s of the cached 3-hop mini-batch with relabel, its
+    roofline, the reference's own CUDA kernels and the CPU restatement beside it."""
+    dev = torch.device("cuda", local_rank)
+    from shmtensor_b200 import capi
+    from shmtensor_b200._lib import check, lib as shm_lib
     indptr_n, indices_n, deg = make_graph()
     rng = np.random.default_rng(11)
     seed_batches = [rng.integers(0, G_NODES, size=N_SEEDS).astype(np.int32) for _ in range(32)]
-    cores = torch.get_num_threads()
-    line = {"metric": "sampled edges/s", "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int64 indptr, int32 indices (integer / byte work)", "data": "synthetic (seeded)",
-            "config": {"workload": SAMPLING_WORKLOAD, "nodes": G_NODES, "edges": int(indptr_n[-1]),
-                       "fanout": FANOUT, "seeds": N_SEEDS, "hop_order": "reversed(fan-out), as the reference"}}
-
-    if args.impl == "reference":
-        # the reference has no CPU sampler (it compares against DGL): time the threaded CPU
-        # restatement of its CUDA algorithm
-        from oracle import build_oracle
-        lib = build_oracle.load_cpu()
-        def cpu_batch(seeds32):
-            seeds = seeds32.astype(np.int64)
-            edges = 0
-            for k in reversed(FANOUT):
-                sp = np.empty(seeds.size + 1, np.int64)
-                so = np.empty(seeds.size * k, np.int32)
-                nnz = lib.oracle_sample_hop(indptr_n.ctypes.data, indices_n.ctypes.data, 0, seeds.ctypes.data,
-                                            seeds.size, k, 0, 7777, sp.ctypes.data, so.ctypes.data)
-                cat = np.concatenate([seeds, so[:nnz].astype(np.int64)])
-                uniq, rel = np.empty(cat.size, np.int64), np.empty(cat.size, np.int64)
-                nu = lib.oracle_relabel(cat.ctypes.data, cat.size, uniq.ctypes.data, rel.ctypes.data)
-                seeds = uniq[:nu].copy()
-                edges += int(nnz)
-            return edges
-        for i in range(max(args.warmup, 1)):
-            cpu_batch(seed_batches[i % 32])
-        t0 = time.perf_counter()
-        edges = sum(cpu_batch(seed_batches[i % 32]) for i in range(args.steps))
-        dt = time.perf_counter() - t0
-        v = edges / dt
-        line.update({"impl": "reference", "value": round(v, 1), "ms_per_step": round(dt / args.steps * 1e3, 4),
-                     "cpu_baseline": {"value": round(v, 1), "unit": "edges/s", "cores": lib.oracle_num_threads(),
-                                      "kind": "port", "sample": f"{args.steps} full 3-hop mini-batches; threaded C++ "
-                                      "restatement of the reference's sampler (seeds split over threads) + serial relabel"},
-                     "e2e": {"value": round(v, 1), "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
-        emit(line)
-        return
-
-    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    from shmtensor_b200 import capi
+    obj = {"metric": "sampled edges/s", "unit": "edges/s", "steps": steps,
+           "dtype": "int64 indptr, int32 indices (integer / byte work)",
+           "config": {"workload": SAMPLING_WORKLOAD, "nodes": G_NODES, "edges": int(indptr_n[-1]),
+                      "fanout": FANOUT, "seeds": N_SEEDS, "hop_order": "reversed(fan-out), as the reference"}}
     indptr, indices = torch.from_numpy(indptr_n), torch.from_numpy(indices_n)
     capi.pin_memory(indptr)
     capi.pin_memory(indices)
     n_cached = G_NODES // 5
-    hot = torch.from_numpy(np.argsort(-deg, kind="stable")[:n_cached].copy()).to(dev)
+    hot_n = np.argsort(-deg, kind="stable")[:n_cached].copy()
+    hot = torch.from_numpy(hot_n).to(dev)
     gp, gi = capi.create_subcsr(indptr, indices, hot)
     hmap = capi.CUCOStaticHashmap(hot.int(), torch.arange(n_cached, dtype=torch.int32, device=dev), 0.8)
     seeds_host = [torch.from_numpy(b).pin_memory() for b in seed_batches]
     seeds_dev = [b.to(dev) for b in seeds_host]
     stream = torch.cuda.current_stream()
     capi.set_sampling_seed(7777)
-    for i in range(max(args.warmup, 3)):  # results held as in the timed loop, so its blocks get cached
-        e, frontier = minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
-    sampler = ClockSampler(local_rank, period_s=0.1)
-    region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-    torch.cuda.synchronize()
-    sampler.start()
-    region[0].record(stream)
-    edges = 0
-    for i in range(args.steps):
-        e, frontier = minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32])
-        edges += e
-    region[1].record(stream)
-    torch.cuda.synchronize()
-    clocks = sampler.stop()
-    ms = region[0].elapsed_time(region[1]) / args.steps
-    value = edges / args.steps / (ms * 1e-3)
-    # end to end: seeds start in pinned host memory, the frontier size is read back
-    seeds_buf = torch.empty(N_SEEDS, dtype=torch.int32, device=dev)
-    torch.cuda.synchronize()
-    region[0].record(stream)
-    e2e_edges = 0
-    for i in range(args.steps):
-        seeds_buf.copy_(seeds_host[i % 32], non_blocking=True)
-        e, frontier = minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_buf)
-        e2e_edges += e
-        _ = frontier[-1].item()
-    region[1].record(stream)
-    torch.cuda.synchronize()
-    e2e_ms = region[0].elapsed_time(region[1]) / args.steps
-    # uncached (every row over UVA) and fully GPU-resident graph, for the cache's effect
-    extra = {}
-    variants = {"uva_only": (minibatch_fused, indptr, indices, None, None, None),
-                "all_in_hbm": (minibatch_fused, indptr.to(dev), indices.to(dev), None, None, None),
-                "call_per_hop_cached": (minibatch, indptr, indices, gp, gi, hmap),
-                # not the configured workload: the whole indptr (19 MB) mirrored in HBM, so a cold
-                # row costs one trip over the host link instead of two
-                "cached_plus_indptr_in_hbm": (minibatch_fused, indptr.to(dev), indices, gp, gi, hmap)}
-    for name, (fn, ip, ix, a, b, m) in variants.items():
-        for i in range(3):
-            fn(capi, ip, ix, a, b, m, seeds_dev[i])
+
+    # parity of one full mini-batch before anything is timed: every hop a legal outcome of the
+    # reference's sampler, relabel bit-equal to the oracle's (python/shmtensor/sampling.py:117-147)
+    from oracle import oracle
+    frontier, hops = capi.sample_minibatch(indptr, indices, seeds_dev[0], list(reversed(FANOUT)), False, gp, gi, hmap)
+    cur = seed_batches[0]
+    for (sp, sx, rel, nxt), k in zip(hops, reversed(FANOUT)):
+        oracle.check_sample_bulk(indptr_n, indices_n, cur, k, False, sp.cpu().numpy(), sx.cpu().numpy(),
+                                 distinct_rows=True)
+        wu, (ws, wx) = oracle.tensor_relabel([cur.astype(np.int32), sx.cpu().numpy()])
+        assert np.array_equal(nxt.cpu().numpy(), wu) and np.array_equal(rel.cpu().numpy(), wx), "relabel differs"
+        cur = wu
+    del frontier, hops
+
+    def timed(fn, n, warm=3):
+        for i in range(warm):
+            keep = fn(i)
+        region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
         torch.cuda.synchronize()
         region[0].record(stream)
-        ee = sum(fn(capi, ip, ix, a, b, m, seeds_dev[i % 32])[0] for i in range(50))
+        edges = 0
+        for i in range(n):
+            e, keep = fn(i)
+            edges += e
         region[1].record(stream)
         torch.cuda.synchronize()
-        extra[name] = round(ee / (region[0].elapsed_time(region[1]) * 1e-3), 1)
+        ms = region[0].elapsed_time(region[1]) / n
+        return ms, edges / n
+
+    sampler = ClockSampler(local_rank, period_s=0.1)
+    sampler.start()
+    ms, edges_per_step = timed(lambda i: minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_dev[i % 32]), steps)
+    obj["clocks"] = sampler.stop()
+    value = edges_per_step / (ms * 1e-3)
+    # end to end: seeds start in pinned host memory, the frontier size is read back
+    seeds_buf = torch.empty(N_SEEDS, dtype=torch.int32, device=dev)
+    def e2e_step(i):
+        seeds_buf.copy_(seeds_host[i % 32], non_blocking=True)
+        e, frontier = minibatch_fused(capi, indptr, indices, gp, gi, hmap, seeds_buf)
+        _ = frontier[-1].item()
+        return e, frontier
+    e2e_ms, e2e_edges = timed(e2e_step, steps)
+    obj.update({"value": round(value, 1), "ms_per_step": round(ms, 5), "edges_per_step": round(edges_per_step),
+                "e2e": {"value": round(e2e_edges / (e2e_ms * 1e-3), 1), "unit": "edges/s",
+                        "h2d_bytes_per_step": N_SEEDS * 4, "d2h_bytes_per_step": 9 * 8 + 4,
+                        "ms_per_step": round(e2e_ms, 5)},
+                "gpu_launches": steps * 9, "api": "capi.sample_minibatch (all hops in one native call)"})
+
+    # like with like against the reference, which needs indptr and indices of one dtype: int64 / int64
+    indices64 = torch.from_numpy(indices_n.astype(np.int64))
+    capi.pin_memory(indices64)
+    gp64, gi64 = capi.create_subcsr(indptr, indices64, hot)
+    seeds64 = [b.long() for b in seeds_dev]
+    ms64, e64 = timed(lambda i: minibatch_fused(capi, indptr, indices64, gp64, gi64, hmap, seeds64[i % 32]), steps)
+    obj["int64_indices"] = {"value": round(e64 / (ms64 * 1e-3), 1), "ms_per_step": round(ms64, 5),
+                            "what": "the same mini-batch with int64 indices, the only layout the reference accepts"}
+
+    # roofline of the dominant kernel: the last hop's sampling kernel.  What bounds it is the rate
+    # of small reads over the host link (row-offset pairs and picked neighbours of rows that are
+    # not cached), so the ceiling is the random-read probe on the same pinned array.
+    hop_seeds = []
+    for i in range(8):
+        s_ = seeds_dev[i]
+        for k in list(reversed(FANOUT))[:-1]:
+            _, sx = capi.csr_cache_sampling(indptr, indices, gp, gi, hmap, s_, k, False)
+            s_, _ = capi.tensor_relabel([s_, sx])
+        hop_seeds.append(s_)
+    k_last = list(reversed(FANOUT))[-1]
+    def last_hop(i):
+        sp, sx = capi.csr_cache_sampling(indptr, indices, gp, gi, hmap, hop_seeds[i % 8], k_last, False)
+        return sx.numel(), sx
+    hop_ms, hop_edges = timed(last_hop, max(20, steps))
+    fr = hop_seeds[0].cpu().numpy().astype(np.int64)
+    is_hot = np.zeros(G_NODES, dtype=bool)
+    is_hot[hot_n] = True
+    cold = fr[~is_hot[fr]]
+    d_cold = deg[cold].astype(np.float64)
+    begin_cold = indptr_n[cold]
+    # requests over the link per cold row: one for the row-offset pair, then one per distinct
+    # 128-byte line of its adjacency list that is touched -- all lines of a row copied whole,
+    # the expected number of distinct lines among k uniform picks otherwise
+    lines = np.maximum(((begin_cold * 4) % 128 + d_cold * 4 + 127) // 128, 1)
+    touched = np.where(d_cold <= k_last, lines, lines * (1.0 - (1.0 - 1.0 / lines) ** k_last))
+    link_reads = int(cold.size + touched[d_cold > 0].sum())
+    sink = torch.zeros(1, dtype=torch.int64, device=dev)
+    n_probe = 1 << 21
+    probe = lambda c=[0]: (check(shm_lib.shmt_random_read(indices.data_ptr(), indices.numel() * 4, n_probe, 16, c[0],
+                                                          sink.data_ptr(), stream.cuda_stream)), c.__setitem__(0, c[0] + 1))
+    probe()
+    probe_ms = min(time_launches(probe, 1, stream) for _ in range(5))
+    ceiling = n_probe / (probe_ms * 1e-3)
+    peak, peak_src = measured_peaks()
+    sizes = [(N_SEEDS, 0)]
+    alg = 0
+    cur_n = N_SEEDS
+    frontier, hops = capi.sample_minibatch(indptr, indices, seeds_dev[0], list(reversed(FANOUT)), False, gp, gi, hmap)
+    for sp, sx, rel, nxt in hops:
+        nnz, nu = sx.numel(), nxt.numel()
+        # per seed: id 4 + probe 12 + row offsets 16 + offset written 8; per edge: 4 read + 4 written;
+        # relabel: ids read twice, slot + new id written and read, unique ids written
+        alg += cur_n * (4 + 12 + 16 + 8) + nnz * 8 + (cur_n + nnz) * (4 + 4 + 4 * 3) + nu * 4
+        cur_n = nu
+    obj["roofline"] = {
+        "bound": "host link, rate of small reads (not bytes)", "kernel": "sample_hop_kernel<int,16> (the last hop of reversed [15,10,5]: fan-out 15)",
+        "kernel_ms": round(hop_ms, 5), "kernel_share_of_step": round(hop_ms / ms, 3),
+        "link_reads_per_launch": link_reads, "achieved": round(link_reads / (hop_ms * 1e-3) / 1e9, 4),
+        "peak": round(ceiling / 1e9, 4), "unit": "G reads/s", "frac": round(link_reads / (hop_ms * 1e-3) / ceiling, 4),
+        "peak_source": "shmt_random_read: independent 16-byte reads (one request each) of the same pinned indices "
+                       "array, 4 per thread in flight, measured in this run",
+        "cold_rows_per_launch": int(cold.size), "frontier_rows_per_launch": int(fr.size),
+        "algorithmic_bytes": int(alg), "hbm_achieved_gbs": round(alg / (ms * 1e6), 1), "hbm_peak": peak,
+        "hbm_frac": round(alg / (ms * 1e6) / peak, 5), "hbm_peak_source": peak_src, "traffic": None,
+        "note": "a cold row of the frontier costs one request for its row-offset pair and then one per 128-byte line of "
+                "its adjacency list that a pick falls in, the second depending on the first; the link serves about 0.3 G "
+                "such requests per second whatever their size, so bytes do not matter here"}
+
+    if full:
+        # uncached (every row over UVA) and fully GPU-resident graph, for the cache's effect
+        extra = {}
+        variants = {"uva_only": (minibatch_fused, indptr, indices, None, None, None),
+                    "all_in_hbm": (minibatch_fused, indptr.to(dev), indices.to(dev), None, None, None),
+                    "call_per_hop_cached": (minibatch, indptr, indices, gp, gi, hmap),
+                    # not the configured workload: the whole indptr (19 MB) mirrored in HBM, so a cold
+                    # row costs one trip over the host link instead of two
+                    "cached_plus_indptr_in_hbm": (minibatch_fused, indptr.to(dev), indices, gp, gi, hmap)}
+        for name, (fn, ip, ix, a, b, m) in variants.items():
+            vms, ve = timed(lambda i: fn(capi, ip, ix, a, b, m, seeds_dev[i % 32]), min(steps, 30))
+            extra[name] = round(ve / (vms * 1e-3), 1)
+        obj["variants_edges_per_s"] = extra
+
     # same-box numbers of the reference's own CUDA kernels, when oracle/_ref was built
     ref_line = None
     try:
         from oracle import build_ref
         ref = build_ref.load_reference()
+        if ref is None:
+            ref_line = {"unavailable": "oracle/_ref has not been built"}
     except Exception as exc:  # noqa: BLE001
         ref, ref_line = None, {"unavailable": f"reference build not loadable: {exc}"}
     if ref is not None:
-        indices64 = torch.from_numpy(indices_n.astype(np.int64))
-        ref.pin_memory(indices64)
         rgp, rgi = ref.create_subcsr(indptr, indices64, hot)
         rmap = ref.CUCOStaticHashmap(hot.int(), torch.arange(n_cached, dtype=torch.int32, device=dev), 0.8)
-        def ref_batch(seeds):
-            ed = 0
+        def ref_batch(i):
+            seeds, ed = seeds_dev[i % 32], 0
             for k in reversed(FANOUT):
                 sp, so = ref.csr_cache_sampling(indptr, indices64, rgp, rgi, rmap, seeds, k, False)
                 seeds, _ = ref.tensor_relabel([seeds.long(), so])
                 ed += so.numel()
-            return ed
-        for i in range(3):
-            ref_batch(seeds_dev[i])
-        torch.cuda.synchronize()
-        region[0].record(stream)
-        ee = sum(ref_batch(seeds_dev[i % 32]) for i in range(50))
-        region[1].record(stream)
-        torch.cuda.synchronize()
-        ref_ms = region[0].elapsed_time(region[1]) / 50
-        ref_line = {"edges_per_s": round(ee / 50 / (ref_ms * 1e-3), 1), "ms_per_step": round(ref_ms, 4),
+            return ed, seeds
+        ref_ms, ref_e = timed(ref_batch, min(steps, 30))
+        ref_line = {"edges_per_s": round(ref_e / (ref_ms * 1e-3), 1), "ms_per_step": round(ref_ms, 4),
+                    "ours_over_reference_int32_indices": round(value / (ref_e / (ref_ms * 1e-3)), 3),
+                    "ours_over_reference_int64_indices": round(e64 / (ms64 * 1e-3) / (ref_e / (ref_ms * 1e-3)), 3),
                     "what": "the reference's own sampling + relabel kernels (compiled unmodified, int64 indices as it "
                             "requires equal dtypes) over a stand-in for its cuCollections map"}
-        ref.unpin_memory(indices64)
+    obj["reference_cuda"] = ref_line
+    capi.unpin_memory(indices64)
     # CPU baseline beside it (bounded sample)
     from oracle import build_oracle
-    lib = build_oracle.load_cpu()
-    def cpu_batch(seeds32):
-        seeds = seeds32.astype(np.int64)
-        ed = 0
-        for k in reversed(FANOUT):
-            sp = np.empty(seeds.size + 1, np.int64)
-            so = np.empty(seeds.size * k, np.int32)
-            nnz = lib.oracle_sample_hop(indptr_n.ctypes.data, indices_n.ctypes.data, 0, seeds.ctypes.data,
-                                        seeds.size, k, 0, 7777, sp.ctypes.data, so.ctypes.data)
-            cat = np.concatenate([seeds, so[:nnz].astype(np.int64)])
-            uniq, rel = np.empty(cat.size, np.int64), np.empty(cat.size, np.int64)
-            nu = lib.oracle_relabel(cat.ctypes.data, cat.size, uniq.ctypes.data, rel.ctypes.data)
-            seeds = uniq[:nu].copy()
-            ed += int(nnz)
-        return ed
-    cpu_batch(seed_batches[0])
+    use_all_host_threads()
+    cpu = build_oracle.load_cpu()
+    cpu_minibatch(cpu, indptr_n, indices_n, seed_batches[0])
     t0 = time.perf_counter()
-    ce = sum(cpu_batch(seed_batches[i]) for i in range(10))
+    ce = sum(cpu_minibatch(cpu, indptr_n, indices_n, seed_batches[i])[0] for i in range(10))
     cpu_dt = time.perf_counter() - t0
-    line.update({"value": round(value, 1), "ms_per_step": round(ms, 5), "edges_per_step": edges // args.steps,
-                 "e2e": {"value": round(e2e_edges / args.steps / (e2e_ms * 1e-3), 1), "unit": "edges/s",
-                         "h2d_bytes_per_step": N_SEEDS * 4, "d2h_bytes_per_step": 6 * 8 + 4, "ms_per_step": round(e2e_ms, 5)},
-                 "gpu_launches": args.steps * 3 * 4, "api": "capi.sample_minibatch (all hops in one native call)", "clocks": clocks, "variants_edges_per_s": extra,
-                 "reference_cuda": ref_line,
-                 "cpu_baseline": {"value": round(ce / cpu_dt, 1), "unit": "edges/s", "cores": lib.oracle_num_threads(),
-                                  "kind": "port", "sample": "10 full 3-hop mini-batches; threaded C++ restatement of the "
-                                  "reference's sampler + serial relabel (the reference has no CPU sampler)"}})
-    emit(line)
+    obj["cpu_baseline"] = {"value": round(ce / cpu_dt, 1), "unit": "edges/s", "cores": cpu.oracle_num_threads(),
+                           "kind": "port", "sample": "10 full 3-hop mini-batches; threaded C++ restatement of the "
+                           "reference's sampler + serial relabel (the reference has no CPU sampler)"}
     capi.unpin_memory(indptr)
     capi.unpin_memory(indices)
+    del gp, gi, gp64, gi64, hmap, hops, frontier
+    torch.cuda.empty_cache()
+    return obj
+
+
+def run_sampling(args) -> None:
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return
+    line = {"metric": "sampled edges/s", "unit": "edges/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int64 indptr, int32 indices (integer / byte work)", "data": "synthetic (seeded)"}
+    if args.impl == "reference":
+        indptr_n, indices_n, deg = make_graph()
+        rng = np.random.default_rng(11)
+        seed_batches = [rng.integers(0, G_NODES, size=N_SEEDS).astype(np.int32) for _ in range(32)]
+        line["config"] = {"workload": SAMPLING_WORKLOAD, "nodes": G_NODES, "edges": int(indptr_n[-1]),
+                          "fanout": FANOUT, "seeds": N_SEEDS, "hop_order": "reversed(fan-out), as the reference"}
+        sampling_reference_line(args, line, indptr_n, indices_n, seed_batches)
+        return
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    line.update(sampling_object(args.steps, local_rank, full=True))
+    emit(line)
 
 
 # --------------------------------------------------------------------------- end-to-end mini-batch
-MB_DIM = 128
-MB_CACHE_FRACTION = 0.40
-MINIBATCH_WORKLOAD = ("end-to-end mini-batch over a partitioned cache, config 4 scaled 1:46 to fit a short run: power-law "
-                      "CSR 2,400,000 nodes / 62,000,000 edges, 128-d float32 features (1.2 GB) in pinned host memory; "
-                      "the top 40% of nodes by degree have their adjacency cached on every GPU and their features "
-                      "hash-partitioned over the GPUs; per GPU and step 1,024 seeds, fan-out [15,10,5], then the features "
-                      "of every sampled node are fetched (remote hits over NVLink, misses over UVA)")
+C4_NODES, C4_EDGES, C4_DIM, C4_CAP, C4_CACHE_FRACTION = 111_000_000, 1_600_000_000, 128, 10_000, 0.40
+C4_STEPS = [7, 11, 13, 17, 19, 23, 29, 31, 41, 43, 47, 53, 59, 61, 67, 71]  # coprime to 111,000,000 / 2^s
 
 
-def run_minibatch(args) -> None:
-    rank, local_rank, world = dist_env()
-    indptr_n, indices_n, deg = make_graph()
-    rng = np.random.default_rng(100 + rank)
-    seed_batches = [rng.integers(0, G_NODES, size=N_SEEDS).astype(np.int32) for _ in range(32)]
-    line = {"metric": "mini-batches/s (sampled edges/s, fetched feature GB/s)", "unit": "mini-batches/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int32 ids, f32 rows (integer / byte work)",
-            "data": "synthetic (seeded)",
-            "config": {"workload": MINIBATCH_WORKLOAD, "nodes": G_NODES, "edges": int(indptr_n[-1]), "dim": MB_DIM,
-                       "fanout": FANOUT, "seeds_per_gpu": N_SEEDS}}
+def c4_scale() -> tuple:
+    """Config 4 needs 64 GB of host memory for its graph and features (111,000,000 x (8 + 512) bytes
+    + 1,600,000,000 x 4 bytes), in shared memory that every rank maps.  Returns (divisor, why):
+    1 when the box holds that, else the smallest power of two that makes it fit."""
+    forced = os.environ.get("SHMT_BENCH_C4_SCALE")
+    if forced:
+        return int(forced), f"forced by SHMT_BENCH_C4_SCALE={forced}"
+    limits = {}
+    try:
+        st_ = os.statvfs("/dev/shm")
+        limits["/dev/shm free"] = st_.f_bavail * st_.f_frsize * 0.85
+    except OSError:
+        pass
+    try:
+        for ln in Path("/proc/meminfo").read_text().splitlines():
+            if ln.startswith("MemAvailable:"):
+                limits["MemAvailable"] = int(ln.split()[1]) * 1024 * 0.6
+    except OSError:
+        pass
+    try:
+        raw = Path("/sys/fs/cgroup/memory.max").read_text().strip()
+        if raw != "max":
+            limits["cgroup memory.max"] = int(raw) * 0.6
+    except (OSError, ValueError):
+        pass
+    need = lambda d: (C4_NODES // d) * (8 + C4_DIM * 4) + (C4_EDGES // d) * 4
+    limit_name, limit = min(limits.items(), key=lambda kv: kv[1]) if limits else ("unknown", float("inf"))
+    d = 1
+    while need(d) > limit and d < 1024:
+        d *= 2
+    gb = {k: round(v / 1e9, 1) for k, v in limits.items()}
+    return d, (f"needs {need(1) / 1e9:.1f} GB of shared host memory; usable here {gb} (fractions of what the box reports)"
+               + ("" if d == 1 else f"; bound by {limit_name}"))
 
-    if args.impl == "reference":
-        if rank != 0:
-            return
-        from oracle import build_oracle, oracle
-        lib = build_oracle.load_cpu()
-        feats = torch.empty(G_NODES, MB_DIM)
-        fill_table(feats)
-        def cpu_step(seeds32):
-            seeds = seeds32.astype(np.int64)
-            edges = 0
-            for k in reversed(FANOUT):
-                sp = np.empty(seeds.size + 1, np.int64)
-                so = np.empty(seeds.size * k, np.int32)
-                nnz = lib.oracle_sample_hop(indptr_n.ctypes.data, indices_n.ctypes.data, 0, seeds.ctypes.data,
-                                            seeds.size, k, 0, 7777, sp.ctypes.data, so.ctypes.data)
-                cat = np.concatenate([seeds, so[:nnz].astype(np.int64)])
-                uniq, rel = np.empty(cat.size, np.int64), np.empty(cat.size, np.int64)
-                nu = lib.oracle_relabel(cat.ctypes.data, cat.size, uniq.ctypes.data, rel.ctypes.data)
-                seeds = uniq[:nu].copy()
-                edges += int(nnz)
-            out = oracle.cpu_fetch_reference(feats, torch.from_numpy(seeds))
-            return edges, out.shape[0]
-        for i in range(max(args.warmup, 1)):
-            cpu_step(seed_batches[i % 32])
-        t0 = time.perf_counter()
-        tot = [cpu_step(seed_batches[i % 32]) for i in range(args.steps)]
-        dt = (time.perf_counter() - t0) / args.steps
-        line.update({"impl": "reference", "value": round(1 / dt, 2), "ms_per_step": round(dt * 1e3, 3),
-                     "edges_per_s": round(sum(t[0] for t in tot) / args.steps / dt, 1),
-                     "fetched_gbs": round(sum(t[1] for t in tot) / args.steps * MB_DIM * 4 / dt / 1e9, 3),
-                     "cpu_baseline": {"value": round(1 / dt, 2), "unit": "mini-batches/s",
-                                      "cores": lib.oracle_num_threads(), "kind": "port",
-                                      "sample": f"{args.steps} full mini-batches: threaded C++ sampler + serial relabel "
-                                                "+ torch.index_select on the host feature table"},
-                     "e2e": {"value": round(1 / dt, 2), "unit": "mini-batches/s", "h2d_bytes_per_step": 0,
-                             "d2h_bytes_per_step": 0}})
-        emit(line)
-        return
 
-    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
+def c4_degrees(n_nodes: int, n_edges: int, dev) -> torch.Tensor:
+    """Out-degrees with a Zipf(2.0) tail: the integer part of a Pareto(1) draw, P(k) = 1/(k(k+1)),
+    capped at 10,000 and rescaled so that they sum to the edge count.  Same on every rank (seeded
+    generator of the same GPU model)."""
+    g = torch.Generator(device=dev).manual_seed(404)
+    u = torch.rand(n_nodes, generator=g, device=dev, dtype=torch.float64).clamp_(min=1.0 / (C4_CAP + 1))
+    raw = torch.floor(1.0 / u).clamp_(max=C4_CAP)
+    lo, hi = 0.1, 50.0
+    for _ in range(60):
+        mid = 0.5 * (lo + hi)
+        if torch.floor(raw * mid).clamp_(max=C4_CAP).sum().item() > n_edges:
+            hi = mid
+        else:
+            lo = mid
+    deg = torch.floor(raw * lo).clamp_(max=C4_CAP).to(torch.int64)
+    short = n_edges - int(deg.sum().item())
+    bump = torch.nonzero(deg < C4_CAP).flatten()[:short]
+    deg[bump] += 1
+    return deg
+
+
+def c4_fill_graph(indices_host: torch.Tensor, indptr_dev: torch.Tensor, n_nodes: int, lo_row: int, hi_row: int, dev) -> None:
+    """Neighbours of rows [lo_row, hi_row): an arithmetic progression modulo the node count from a
+    hashed start with a hashed prime step (distinct within a row, spread uniformly over the nodes),
+    made on the GPU in pieces and copied into the shared host array."""
+    steps = torch.tensor(C4_STEPS, device=dev, dtype=torch.int64)
+    piece = 8_000_000
+    for a in range(lo_row, hi_row, piece):
+        b = min(a + piece, hi_row)
+        e0, e1 = int(indptr_dev[a].item()), int(indptr_dev[b].item())
+        if e1 == e0:
+            continue
+        rows = torch.arange(a, b, device=dev, dtype=torch.int64)
+        deg = indptr_dev[a + 1:b + 1] - indptr_dev[a:b]
+        row = torch.repeat_interleave(rows, deg)
+        j = torch.arange(e0, e1, device=dev, dtype=torch.int64) - indptr_dev[row]
+        base = (row * 2654435761 + 12345) % n_nodes
+        step = steps[(row * 40503 >> 3) % len(C4_STEPS)]
+        indices_host[e0:e1].copy_(((base + j * step) % n_nodes).to(torch.int32))
+        del rows, deg, row, j, base, step
+
+
+def c4_fill_features(feats_host: torch.Tensor, lo_row: int, hi_row: int, dev) -> None:
+    """N(0,1) rows made on the GPU (one seeded generator per piece) and copied to the shared table."""
+    piece = 2_000_000
+    for a in range(lo_row, hi_row, piece):
+        b = min(a + piece, hi_row)
+        g = torch.Generator(device=dev).manual_seed(9000 + a // piece)
+        feats_host[a:b].copy_(torch.randn(b - a, C4_DIM, generator=g, device=dev))
+
+
+def minibatch_workload(n_nodes, n_edges, divisor) -> str:
+    return ("end-to-end mini-batch over a partitioned cache (config 4" + ("" if divisor == 1 else f", scaled 1:{divisor}")
+            + f"): power-law CSR {n_nodes:,} nodes / {n_edges:,} edges (degree tail Zipf(2.0), int64 indptr, int32 "
+            f"indices), {C4_DIM}-d float32 features ({n_nodes * C4_DIM * 4 / 1e9:.1f} GB), graph and features in POSIX shared "
+            "memory mapped and pinned by every rank; the top 40% of nodes by degree have their adjacency cached on "
+            "every GPU and their features hash-partitioned over the GPUs; per GPU and step 1,024 seeds, fan-out "
+            "[15,10,5], then the features of every sampled node are fetched (remote hits over NVLink, misses over UVA)")
+
+
+def minibatch_object(steps: int, rank: int, local_rank: int, world: int) -> dict:
+    """Config 4: sampling + relabel + feature fetch of every sampled node, per GPU and step, over
+    a cache partitioned across the GPUs of the job.  Assumes the process group exists when
+    world > 1.  Every rank returns the same object."""
     import torch.distributed as dist
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
     import shmtensor_b200 as st
     from shmtensor_b200 import capi
+    from shmtensor_b200._lib import check, lib as shm_lib
     from shmtensor_b200.partition import PartitionedFeatureCache
+    dev = torch.device("cuda", local_rank)
     stream = torch.cuda.current_stream()
+    t_setup = time.perf_counter()
+    divisor, why = c4_scale()
+    n_nodes, n_edges = C4_NODES // divisor, C4_EDGES // divisor
+    numa_mode = host_numa_mode(world) if world > 1 else None
+    obj = {"metric": "mini-batches/s (sampled edges/s, fetched feature GB/s)", "unit": "mini-batches/s",
+           "n_gpus": world, "steps": steps, "scaling": "weak",
+           "dtype": "int32 ids, f32 rows (integer / byte work)",
+           "config": {"workload": minibatch_workload(n_nodes, n_edges, divisor), "nodes": n_nodes, "edges": n_edges,
+                      "dim": C4_DIM, "fanout": FANOUT, "seeds_per_gpu": N_SEEDS, "scale_divisor": divisor,
+                      "scale_reason": why, "host_table_placement": numa_mode or "one rank's first touch"}}
+
+    # ---- host side: three shared segments, pages placed, then pinned by every rank
+    tag = os.environ.get("MASTER_PORT", str(os.getpid()))
+    numa = "interleave" if numa_mode == "interleave" else None
+    def shared(name, shape, dtype):
+        if world > 1:
+            return st.ShmTensor(f"shmt_c4_{name}_{tag}", shape, rank, world, None, dtype, pin_memory=True,
+                                overwrite_stale=True, numa=numa)
+        return st.ShmTensor(f"shmt_c4_{name}_{tag}", shape, 0, 1, None, dtype, pin_memory=True, overwrite_stale=True)
+    shm_ptr, shm_idx, shm_feat = (shared("indptr", (n_nodes + 1,), torch.int64),
+                                  shared("indices", (n_edges,), torch.int32),
+                                  shared("feats", (n_nodes, C4_DIM), torch.float32))
+    indptr, indices, feats = shm_ptr.tensor_, shm_idx.tensor_, shm_feat.tensor_
+    t_mapped = time.perf_counter()
+
+    deg = c4_degrees(n_nodes, n_edges, dev)
+    indptr_dev = torch.zeros(n_nodes + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(deg, 0, out=indptr_dev[1:])
+    if rank == 0:
+        indptr.copy_(indptr_dev)
+    # every rank writes its share of the edges (split by edge count) and of the feature rows
+    cuts = torch.searchsorted(indptr_dev, torch.arange(world + 1, device=dev) * (n_edges // world)).tolist()
+    cuts[0], cuts[-1] = 0, n_nodes
+    c4_fill_graph(indices, indptr_dev, n_nodes, cuts[rank], cuts[rank + 1], dev)
+    c4_fill_features(feats, rank * n_nodes // world, (rank + 1) * n_nodes // world, dev)
+    torch.cuda.synchronize()
     if world > 1:
-        name = f"shmt_bench_mb_{os.environ.get('MASTER_PORT', '0')}"
-        if rank == 0 and capi.file_exist(name):
-            p, fd = capi.open_shared_mem(name, G_NODES * MB_DIM * 4)
-            capi.release_shared_mem(name, G_NODES * MB_DIM * 4, p, fd)
         dist.barrier()
-        shm = st.ShmTensor(name, (G_NODES, MB_DIM), rank, world, None, torch.float32, pin_memory=True)
-        feats = shm.tensor_
-        if rank == 0:
-            fill_table(feats)
-        dist.barrier()
-    else:
-        shm = None
-        feats = torch.empty(G_NODES, MB_DIM)
-        fill_table(feats)
-        capi.pin_memory(feats)
-    indptr, indices = torch.from_numpy(indptr_n), torch.from_numpy(indices_n)
-    capi.pin_memory(indptr)
-    capi.pin_memory(indices)
-    n_cached = int(G_NODES * MB_CACHE_FRACTION)
-    hot_n = np.argsort(-deg, kind="stable")[:n_cached].copy()
-    hot = torch.from_numpy(hot_n).to(dev)
-    gp, gi = capi.create_subcsr(indptr, indices, hot)
+    t_filled = time.perf_counter()
+
+    # ---- caches: adjacency of the top 40 % by degree on every GPU (built from a temporary GPU copy
+    #      of the edge array), their features partitioned over the GPUs
+    n_cached = int(n_nodes * C4_CACHE_FRACTION)
+    hot = torch.sort(deg, descending=True, stable=True).indices[:n_cached].contiguous()
+    del deg
+    indices_dev = indices.to(dev, non_blocking=True)
+    gp, gi = capi.create_subcsr(indptr_dev, indices_dev, hot)
+    del indices_dev, indptr_dev
     gmap = capi.CUCOStaticHashmap(hot.int(), torch.arange(n_cached, dtype=torch.int32, device=dev), 0.8)
-    fcache = PartitionedFeatureCache(feats, torch.from_numpy(hot_n))
+    fcache = PartitionedFeatureCache(feats, hot, replicate=0)   # neighbours are uniform over the nodes: no hot head
+    del hot
+    torch.cuda.empty_cache()
+    t_cached = time.perf_counter()
+
+    rng = np.random.default_rng(100 + rank)
+    seed_batches = [rng.integers(0, n_nodes, size=N_SEEDS).astype(np.int32) for _ in range(32)]
     seeds_host = [torch.from_numpy(b).pin_memory() for b in seed_batches]
     seeds_buf = torch.empty(N_SEEDS, dtype=torch.int32, device=dev)
-    tail = torch.empty(MB_DIM, dtype=torch.float32).pin_memory()
+    tail = torch.empty(C4_DIM, dtype=torch.float32).pin_memory()
     capi.set_sampling_seed(7777 + rank)
+    fan = list(reversed(FANOUT))
 
     def step(i):
         seeds_buf.copy_(seeds_host[i % 32], non_blocking=True)
-        frontier, hops = capi.sample_minibatch(indptr, indices, seeds_buf, list(reversed(FANOUT)), False, gp, gi, gmap)
+        frontier, hops = capi.sample_minibatch(indptr, indices, seeds_buf, fan, False, gp, gi, gmap)
         rows = fcache.fetch(frontier)
-        return sum(h[1].numel() for h in hops), frontier, rows
+        return sum(h[1].numel() for h in hops), frontier, rows, hops
 
-    # parity of one full step: the fetched rows are the host rows of the frontier, bit for bit
-    _, frontier, rows = step(0)
-    assert torch.equal(rows.cpu().view(torch.int32), feats[frontier.cpu().long()].view(torch.int32))
-    for i in range(max(args.warmup, 3)):
-        e, frontier, rows = step(i)
+    # ---- parity of one full step on every rank: each hop a legal outcome of the reference's sampler,
+    #      relabel as the oracle's, fetched rows the host rows of the frontier bit for bit
+    from oracle import oracle
+    _, frontier, rows, hops = step(0)
+    indptr_n, indices_n = indptr.numpy(), indices.numpy()
+    cur = seed_batches[0]
+    for (sp, sx, rel, nxt), k in zip(hops, fan):
+        oracle.check_sample_bulk(indptr_n, indices_n, cur, k, False, sp.cpu().numpy(), sx.cpu().numpy(), distinct_rows=True)
+        wu, (ws, wx) = oracle.tensor_relabel([cur.astype(np.int32), sx.cpu().numpy()])
+        assert np.array_equal(nxt.cpu().numpy(), wu) and np.array_equal(rel.cpu().numpy(), wx), "relabel differs"
+        cur = wu
+    assert torch.equal(rows.cpu().view(torch.int32), feats[frontier.cpu().long()].view(torch.int32)), "fetched rows differ"
+    hits = int((fcache.directory.query(frontier.long()) >= 0).sum().item())
+    hit_rate = hits / frontier.numel()
+    del hops
+
+    for i in range(3):
+        e, frontier, rows, _ = step(i)
     sampler = ClockSampler(local_rank, period_s=0.1)
     region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    mid = [torch.cuda.Event(enable_timing=True) for _ in range(2 * steps)]
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     sampler.start()
     region[0].record(stream)
     edges = n_rows = 0
-    for i in range(args.steps):
-        e, frontier, rows = step(i)
+    for i in range(steps):
+        seeds_buf.copy_(seeds_host[i % 32], non_blocking=True)
+        frontier, hops = capi.sample_minibatch(indptr, indices, seeds_buf, fan, False, gp, gi, gmap)
+        mid[2 * i].record(stream)
+        rows = fcache.fetch(frontier)
+        mid[2 * i + 1].record(stream)
         tail.copy_(rows[-1], non_blocking=True)
-        edges += e
+        edges += sum(h[1].numel() for h in hops)
         n_rows += rows.shape[0]
     region[1].record(stream)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     clocks = sampler.stop()
-    ms = region[0].elapsed_time(region[1]) / args.steps
-    t = torch.tensor([ms, float(edges), float(n_rows)], device=dev, dtype=torch.float64)
-    if world > 1:
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        ms, edges, n_rows = tmax[0].item(), t[1].item(), t[2].item()
-    else:
-        edges, n_rows = float(edges), float(n_rows)
-    hits = int((fcache.directory.query(frontier.long()) >= 0).sum().item())
-    v = world / (ms * 1e-3)
-    line.update({"value": round(v, 1), "ms_per_step": round(ms, 5),
-                 "edges_per_s": round(edges / args.steps / (ms * 1e-3), 1),
-                 "fetched_gbs": round(n_rows / args.steps * MB_DIM * 4 / (ms * 1e6), 2),
-                 "rows_fetched_per_gpu_step": round(n_rows / args.steps / world), "feature_hit_rate": round(hits / frontier.numel(), 4),
-                 "e2e": {"value": round(v, 1), "unit": "mini-batches/s", "h2d_bytes_per_step": N_SEEDS * 4,
-                         "d2h_bytes_per_step": MB_DIM * 4 + 9 * 8, "ms_per_step": round(ms, 5),
-                         "note": "the timed loop is already end to end: seeds from pinned host memory, sizes and the "
-                                 "last fetched row read back"},
-                 "gpu_launches": args.steps * 10, "clocks": clocks})
+    ms = region[0].elapsed_time(region[1]) / steps
+    fetch_ms = sum(mid[2 * i].elapsed_time(mid[2 * i + 1]) for i in range(steps)) / steps
+    per_rank = all_gather_floats([ms, float(edges), float(n_rows), fetch_ms, hit_rate], world, dev)
+    ms_max = max(p[0] for p in per_rank)
+    edges_all, rows_all = sum(p[1] for p in per_rank), sum(p[2] for p in per_rank)
+
+    # the host link while every rank streams from the shared feature table at once: the ceiling
+    # of the fetch's miss leg, which is what bounds a step
+    sink = torch.zeros(1, dtype=torch.int64, device=dev)
+    probe_bytes = min(feats.numel() * 4, 1 << 30)
+    best = 1e30
+    for _ in range(3):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        best = min(best, time_launches(lambda: check(shm_lib.shmt_stream_read(feats.data_ptr(), probe_bytes, sink.data_ptr(),
+                                                                              stream.cuda_stream)), 1, stream))
+    link = all_gather_floats([probe_bytes / (best * 1e6)], world, dev)
+    miss_bytes = [(1 - p[4]) * p[2] / steps * C4_DIM * 4 for p in per_rank]
+
+    obj.update({
+        "value": round(world / (ms_max * 1e-3), 1), "ms_per_step": round(ms_max, 5),
+        "edges_per_s": round(edges_all / steps / (ms_max * 1e-3), 1),
+        "fetched_gbs": round(rows_all / steps * C4_DIM * 4 / (ms_max * 1e6), 2),
+        "rows_fetched_per_gpu_step": round(rows_all / steps / world), "feature_hit_rate": round(hit_rate, 4),
+        "per_rank_ms": [round(p[0], 4) for p in per_rank], "per_rank_fetch_ms": [round(p[3], 4) for p in per_rank],
+        "e2e": {"value": round(world / (ms_max * 1e-3), 1), "unit": "mini-batches/s", "h2d_bytes_per_step": N_SEEDS * 4,
+                "d2h_bytes_per_step": C4_DIM * 4 + 9 * 8, "ms_per_step": round(ms_max, 5),
+                "note": "the timed loop is end to end: seeds from pinned host memory, sizes and the last fetched "
+                        "row read back"},
+        "roofline": {"bound": "host_link", "kernel": "row_gather_bulk_kernel<2> (feature fetch of the frontier)",
+                     "kernel_ms": [round(p[3], 4) for p in per_rank],
+                     "achieved": [round(b / (p[3] * 1e6), 2) for b, p in zip(miss_bytes, per_rank)],
+                     "peak": [round(l[0], 2) for l in link], "unit": "GB/s",
+                     "frac": [round(b / (p[3] * 1e6) / l[0], 4) for b, p, l in zip(miss_bytes, per_rank, link)],
+                     "peak_source": "shmt_stream_read over the shared pinned feature table, all ranks at once, this run",
+                     "algorithmic_bytes": "rows x 512 B written + hit rows x 512 B read (HBM / NVLink) + miss rows x 512 B (host link)",
+                     "traffic": None},
+        "gpu_launches": steps * 10, "clocks": clocks,
+        "setup_s": {"map_and_pin": round(t_mapped - t_setup, 1), "generate": round(t_filled - t_mapped, 1),
+                    "build_caches": round(t_cached - t_filled, 1)},
+        "host_pages_per_node": {"feats": pages_per_node(feats.data_ptr()), "indices": pages_per_node(indices.data_ptr())},
+    })
+    # CPU beside it, on rank 0, bounded: the threaded C++ sampler + relabel, then index_select on the table
     if rank == 0:
-        emit(line)
+        from oracle import build_oracle
+        use_all_host_threads()
+        cpu = build_oracle.load_cpu()
+        def cpu_step(seeds32):
+            e, fr = cpu_minibatch(cpu, indptr_n, indices_n, seeds32)
+            return e, oracle.cpu_fetch_reference(feats, torch.from_numpy(fr)).shape[0]
+        cpu_step(seed_batches[0])
+        t0 = time.perf_counter()
+        n_cpu = 3
+        for i in range(n_cpu):
+            cpu_step(seed_batches[1 + i])
+        cpu_dt = (time.perf_counter() - t0) / n_cpu
+        obj["cpu_baseline"] = {"value": round(1 / cpu_dt, 2), "unit": "mini-batches/s", "cores": cpu.oracle_num_threads(),
+                               "kind": "port", "ms_per_step": round(cpu_dt * 1e3, 2),
+                               "sample": f"{n_cpu} full mini-batches of one rank: threaded C++ sampler + serial relabel + "
+                                         "torch.index_select on the shared feature table"}
+    if world > 1:
+        box = [obj.get("cpu_baseline")]
+        dist.broadcast_object_list(box, src=0)
+        obj["cpu_baseline"] = box[0]
     torch.cuda.synchronize()
     fcache.close()
-    capi.unpin_memory(indptr)
-    capi.unpin_memory(indices)
-    if world == 1:
-        capi.unpin_memory(feats)
-    else:
-        dist.barrier()
-        del feats, fcache
-        shm = None
+    del fcache, gp, gi, gmap, indptr, indices, feats, indptr_n, indices_n, rows, frontier
+    shm_ptr = shm_idx = shm_feat = None
+    torch.cuda.empty_cache()
+    return obj
+
+
+def run_minibatch(args) -> None:
+    rank, local_rank, world = dist_env()
+    if args.impl == "reference":
+        if rank == 0:
+            emit({"impl": "reference", "unavailable": "the CPU line of this workload is the cpu_baseline object of the "
+                  "GPU arm's own run (it needs the same 64 GB of generated graph and features)"})
+        return
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=PG_TIMEOUT)
+        bind_to_gpu_node(local_rank)
+    obj = minibatch_object(args.steps, rank, local_rank, world)
+    line = {"metric": obj.pop("metric"), "value": obj.pop("value"), "unit": obj.pop("unit"), "n_gpus": world,
+            "steps": args.steps, "warmup": 3, "ms_per_step": obj.pop("ms_per_step"), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "data": "synthetic (seeded)", **obj}
+    if rank == 0:
+        emit(line)
+    if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
@@ -976,59 +1483,65 @@ UPDATE_WORKLOAD = ("cache update path: fused insert/overwrite of 4,000,000 uniqu
                    "half present, half absent")
 
 
-def run_update(args) -> None:
-    rank, local_rank, world = dist_env()
-    if rank != 0:
-        return
-    row_bytes = U_DIM * 2
-    line = {"metric": "inserted+looked-up keys/s", "unit": "keys/s", "n_gpus": 1, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int64 keys, int32 slots, bf16 rows (byte copy)", "data": "synthetic (seeded)",
-            "config": {"workload": UPDATE_WORKLOAD, "keys": U_KEYS, "row_bytes": row_bytes, "lookups": U_LOOKUPS}}
+def update_keys():
     rng = np.random.default_rng(5)
     keys_n = np.unique(rng.integers(0, 1 << 40, size=U_KEYS + 100_000))
     keys_n = rng.permutation(keys_n)[:U_KEYS].astype(np.int64)
     req_n = np.concatenate([keys_n[rng.integers(0, U_KEYS, size=U_LOOKUPS // 2)],
                             rng.integers(1 << 40, 1 << 41, size=U_LOOKUPS // 2)]).astype(np.int64)
     rng.shuffle(req_n)
+    return keys_n, req_n
 
-    if args.impl == "reference":
-        # CPU path: row write data[ids] = upd (example/test_cache_set.py:183-184) + an open-addressing
-        # map built and queried on all cores (the reference's map is GPU-only)
-        from oracle import build_oracle
-        lib = build_oracle.load_cpu()
-        rows = np.zeros((U_KEYS, row_bytes), np.uint8)
-        rows[:] = np.arange(row_bytes, dtype=np.uint8)
-        table_rows = np.empty_like(rows)
-        slots = np.arange(U_KEYS, dtype=np.int64)
-        cap = 1 << 23
-        table = np.empty(2 * cap, np.int64)
-        out = np.empty(U_LOOKUPS, np.int32)
-        def step():
-            lib.oracle_map_build_query(keys_n.ctypes.data, U_KEYS, table.ctypes.data, cap, req_n.ctypes.data,
-                                       U_LOOKUPS, out.ctypes.data)
-            lib.oracle_scatter(table_rows.ctypes.data, slots.ctypes.data, U_KEYS, row_bytes, rows.ctypes.data)
-        for _ in range(max(args.warmup, 1)):
-            step()
-        t0 = time.perf_counter()
-        for _ in range(args.steps):
-            step()
-        dt = (time.perf_counter() - t0) / args.steps
-        v = (U_KEYS + U_LOOKUPS) / dt
-        line.update({"impl": "reference", "value": round(v, 1), "ms_per_step": round(dt * 1e3, 3),
-                     "cpu_baseline": {"value": round(v, 1), "unit": "keys/s", "cores": lib.oracle_num_threads(),
-                                      "kind": "port", "sample": f"{args.steps} full passes: threaded open-addressing "
-                                      "build + query and a threaded row scatter"},
-                     "e2e": {"value": round(v, 1), "unit": "keys/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
-        emit(line)
-        return
 
-    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
-    torch.cuda.set_device(local_rank)
+def update_cpu(steps: int, warmup: int, keys_n, req_n, sample: int = 1) -> dict:
+    """CPU path: row write data[ids] = upd (example/test_cache_set.py:183-184) + an open-addressing
+    map built and queried on all cores (the reference's map is GPU-only).  `sample` > 1 times the
+    first 1/sample of the keys and lookups."""
+    from oracle import build_oracle
+    use_all_host_threads()
+    lib = build_oracle.load_cpu()
+    row_bytes = U_DIM * 2
+    n_keys, n_req = U_KEYS // sample, U_LOOKUPS // sample
+    rows = np.zeros((n_keys, row_bytes), np.uint8)
+    rows[:] = np.arange(row_bytes, dtype=np.uint8)
+    table_rows = np.empty_like(rows)
+    slots = np.arange(n_keys, dtype=np.int64)
+    cap = 1 << 23
+    while cap // 2 >= 2 * n_keys:
+        cap //= 2
+    table = np.empty(2 * cap, np.int64)
+    out = np.empty(n_req, np.int32)
+    def step():
+        lib.oracle_map_build_query(keys_n.ctypes.data, n_keys, table.ctypes.data, cap, req_n.ctypes.data,
+                                   n_req, out.ctypes.data)
+        lib.oracle_scatter(table_rows.ctypes.data, slots.ctypes.data, n_keys, row_bytes, rows.ctypes.data)
+    for _ in range(max(warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    v = (n_keys + n_req) / dt
+    return {"value": round(v, 1), "unit": "keys/s", "cores": lib.oracle_num_threads(), "kind": "port",
+            "ms_per_step": round(dt * 1e3, 3),
+            "sample": f"{steps} passes over {'all' if sample == 1 else f'the first 1/{sample} of'} the keys and lookups: "
+                      "threaded open-addressing build + query and a threaded row scatter"}
+
+
+def update_object(steps: int, local_rank: int) -> dict:
+    """Config 5 on one GPU: fused insert/overwrite of 4,000,000 keys with 512-byte rows into an
+    empty cache, then 1,000,000 lookups; rooflines, the reference's map and the CPU beside it."""
     dev = torch.device("cuda", local_rank)
     from shmtensor_b200 import capi
-    keys = torch.from_numpy(keys_n).to(dev)
-    req = torch.from_numpy(req_n).to(dev)
+    from shmtensor_b200._lib import check, lib as shm_lib
+    row_bytes = U_DIM * 2
+    obj = {"metric": "inserted+looked-up keys/s", "unit": "keys/s", "steps": steps,
+           "dtype": "int64 keys, int32 slots, bf16 rows (byte copy)",
+           "config": {"workload": UPDATE_WORKLOAD, "keys": U_KEYS, "row_bytes": row_bytes, "lookups": U_LOOKUPS}}
+    keys_n, req_n = update_keys()
+    keys_host, req_host = torch.from_numpy(keys_n).pin_memory(), torch.from_numpy(req_n).pin_memory()
+    keys = keys_host.to(dev)
+    req = req_host.to(dev)
     g = torch.Generator(device=dev).manual_seed(5)
     rows = torch.randn(U_KEYS, U_DIM, generator=g, device=dev).to(torch.bfloat16)
     slots = torch.arange(U_KEYS, dtype=torch.int32, device=dev)
@@ -1041,14 +1554,17 @@ def run_update(args) -> None:
         capi.cache_insert_set(gpu, keys, slots, rows, m)
         return m, m.query(req)
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(3):
         m, out = one_pass()
+    # parity at full size: rows and slots bit-exact, absent keys -1
     assert torch.equal(gpu.view(torch.int16), rows.view(torch.int16)) and m.size() == U_KEYS
     assert int((out >= 0).sum().item()) == U_LOOKUPS // 2
+    hit = out >= 0
+    assert torch.equal(keys[out[hit].long()], req[hit]) and bool((req[~hit] >= (1 << 40)).all())
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     t_ins = t_q = 0.0
     torch.cuda.synchronize()
-    for _ in range(args.steps):
+    for _ in range(steps):
         m = capi.CUCOStaticHashmap.empty(2 * U_KEYS, torch.int64, torch.int32, dev)
         ev[0].record(stream)
         capi.cache_insert_set(gpu, keys, slots, rows, m)
@@ -1058,16 +1574,35 @@ def run_update(args) -> None:
         torch.cuda.synchronize()
         t_ins += ev[0].elapsed_time(ev[1])
         t_q += ev[1].elapsed_time(ev[2])
-    t_ins /= args.steps
-    t_q /= args.steps
+    t_ins /= steps
+    t_q /= steps
+    # end to end: keys and lookups start in pinned host memory, the found slots go back to it
+    # (the rows to insert are produced on the GPU, as the outputs of a training step are)
+    keys_buf, req_buf = torch.empty_like(keys), torch.empty_like(req)
+    out_host = torch.empty(U_LOOKUPS, dtype=torch.int32).pin_memory()
+    e2e_n = max(3, min(steps, 5))
+    torch.cuda.synchronize()
+    ev[0].record(stream)
+    for _ in range(e2e_n):
+        keys_buf.copy_(keys_host, non_blocking=True)
+        req_buf.copy_(req_host, non_blocking=True)
+        mm = capi.CUCOStaticHashmap.empty(2 * U_KEYS, torch.int64, torch.int32, dev)
+        capi.cache_insert_set(gpu, keys_buf, slots, rows, mm)
+        out_host.copy_(mm.query(req_buf), non_blocking=True)
+        stream.synchronize()
+    ev[1].record(stream)
+    torch.cuda.synchronize()
+    e2e_ms = ev[0].elapsed_time(ev[1]) / e2e_n
+    del mm, keys_buf, req_buf
     # the reference-named overwrite of the same rows through the finished map (all hits)
     for _ in range(2):
         capi.cache_set(None, gpu, keys, rows, m)
     t_set = time_launches(lambda: capi.cache_set(None, gpu, keys, rows, m), 10, stream)
     b_set = U_KEYS * (8 + 12 + 2 * row_bytes)
-    line["cache_set"] = {"ms": round(t_set, 4), "keys_per_s": round(U_KEYS / (t_set * 1e-3), 1),
-                         "roofline": {"bound": "hbm", "achieved": round(b_set / (t_set * 1e6), 1), "peak": peak,
-                                      "unit": "GB/s", "frac": round(b_set / (t_set * 1e6) / peak, 4)}}
+    obj["cache_set"] = {"ms": round(t_set, 4), "keys_per_s": round(U_KEYS / (t_set * 1e-3), 1),
+                        "roofline": {"bound": "hbm", "kernel": "row_scatter_bulk_kernel<2>",
+                                     "achieved": round(b_set / (t_set * 1e6), 1), "peak": peak,
+                                     "unit": "GB/s", "frac": round(b_set / (t_set * 1e6) / peak, 4)}}
     # plain map construction + query (CUCOStaticHashmap(keys, values, 0.5), the reference's flow),
     # and the reference's own map on the same GPU when oracle/_ref was built
     def build_query(mod):
@@ -1081,7 +1616,7 @@ def run_update(args) -> None:
         return t0[0].elapsed_time(t0[1]), t0[1].elapsed_time(t0[2]), r
     build_query(capi)
     b_ms, q_ms, r_ours = build_query(capi)
-    line["map_build_query"] = {"build_ms": round(b_ms, 4), "query_ms": round(q_ms, 4)}
+    obj["map_build_query"] = {"build_ms": round(b_ms, 4), "query_ms": round(q_ms, 4)}
     try:
         from oracle import build_ref
         ref = build_ref.load_reference()
@@ -1091,8 +1626,18 @@ def run_update(args) -> None:
         build_query(ref)
         rb_ms, rq_ms, r_ref = build_query(ref)
         assert torch.equal(r_ours, r_ref), "map query differs from the reference's"
-        line["map_build_query"]["reference_cuda"] = {"build_ms": round(rb_ms, 4), "query_ms": round(rq_ms, 4),
-                                                     "what": "the reference's wrapper over a stand-in for cuCollections"}
+        # the reference's cache_set kernel on the same rows (bf16 viewed as int16: it rejects bf16)
+        rm = ref.CUCOStaticHashmap(keys, slots, 0.5)
+        g16, r16 = gpu.view(torch.int16), rows.view(torch.int16)
+        for _ in range(2):
+            ref.cache_set(g16, g16, keys, r16, rm)
+        r_set = time_launches(lambda: ref.cache_set(g16, g16, keys, r16, rm), 5, stream)
+        obj["reference_cuda"] = {"build_ms": round(rb_ms, 4), "query_ms": round(rq_ms, 4),
+                                 "cache_set_ms": round(r_set, 4),
+                                 "build_plus_set_plus_query_ms": round(rb_ms + r_set + rq_ms, 4),
+                                 "what": "the reference's map wrapper (over a stand-in for cuCollections) and its "
+                                         "MultiDimCacheSetKernel, compiled unmodified: build, overwrite all rows, query"}
+        del rm
     # cache turnover on the finished map: evict 10 % of the ids, admit as many new ones into the freed
     # rows (erased slots are taken again, so the table never fills); then the same back again
     n_turn = U_KEYS // 10
@@ -1109,22 +1654,66 @@ def run_update(args) -> None:
         t_er, t_ad = t0[0].elapsed_time(t0[1]), t0[1].elapsed_time(t0[2])
         assert m.size() == U_KEYS and torch.equal(m.query(b), freed) and bool((m.query(a) == -1).all())
     assert torch.equal(m.query(keys), slots)
-    line["cache_turnover"] = {"ids": n_turn, "erase_ms": round(t_er, 4), "admit_ms": round(t_ad, 4),
-                              "what": "shmt_map_erase of 10 % of the keys, then shmt_map_insert of as many new ids "
-                                      "with the freed row numbers (host-synchronous calls, device time)"}
+    obj["cache_turnover"] = {"ids": n_turn, "erase_ms": round(t_er, 4), "admit_ms": round(t_ad, 4),
+                             "what": "shmt_map_erase of 10 % of the keys, then shmt_map_insert of as many new ids "
+                                     "with the freed row numbers (host-synchronous calls, device time)"}
+    # what bounds the lookups is the rate of random 64-byte window reads from a 256 MB table
+    sink = torch.zeros(1, dtype=torch.int64, device=dev)
+    tbl = torch.empty(m.memory_usage(), dtype=torch.uint8, device=dev)
+    n_probe = 1 << 24
+    probe = lambda c=[0]: (check(shm_lib.shmt_random_read(tbl.data_ptr(), tbl.numel(), n_probe, 64, c[0], sink.data_ptr(),
+                                                          stream.cuda_stream)), c.__setitem__(0, c[0] + 1))
+    probe()
+    win_rate = n_probe / (min(time_launches(probe, 1, stream) for _ in range(5)) * 1e-3)
+    del tbl
     # algorithmic bytes: insert+set per key 8 (key) + 4 (slot) + 16 (claim) + row read + row written;
     # lookup per key 8 + 12 + 4
     b_ins = U_KEYS * (8 + 4 + 16 + 2 * row_bytes)
     b_q = U_LOOKUPS * (8 + 12 + 4)
-    line.update({"value": round((U_KEYS + U_LOOKUPS) / ((t_ins + t_q) * 1e-3), 1), "ms_per_step": round(t_ins + t_q, 4),
-                 "insert_set": {"ms": round(t_ins, 4), "keys_per_s": round(U_KEYS / (t_ins * 1e-3), 1),
-                                "roofline": {"bound": "hbm", "achieved": round(b_ins / (t_ins * 1e6), 1), "peak": peak,
-                                             "unit": "GB/s", "frac": round(b_ins / (t_ins * 1e6) / peak, 4),
-                                             "peak_source": peak_src}},
-                 "lookup": {"ms": round(t_q, 4), "keys_per_s": round(U_LOOKUPS / (t_q * 1e-3), 1),
-                            "roofline": {"bound": "hbm", "achieved": round(b_q / (t_q * 1e6), 1), "peak": peak,
-                                         "unit": "GB/s", "frac": round(b_q / (t_q * 1e6) / peak, 4)}},
-                 "gpu_launches": args.steps * 2})
+    obj.update({"value": round((U_KEYS + U_LOOKUPS) / ((t_ins + t_q) * 1e-3), 1), "ms_per_step": round(t_ins + t_q, 4),
+                "roofline": {"bound": "hbm", "kernel": "insert_set_kernel<16,8> (probe-or-claim + row write)",
+                             "kernel_ms": round(t_ins, 5), "algorithmic_bytes": b_ins,
+                             "achieved": round(b_ins / (t_ins * 1e6), 1), "peak": peak, "unit": "GB/s",
+                             "frac": round(b_ins / (t_ins * 1e6) / peak, 4), "peak_source": peak_src,
+                             "traffic": 4_500_000_000,
+                             "traffic_source": "profiles/insert_set_and_map_query.md (ncu, bytes per launch)"},
+                "insert_set": {"ms": round(t_ins, 4), "keys_per_s": round(U_KEYS / (t_ins * 1e-3), 1)},
+                "lookup": {"ms": round(t_q, 4), "keys_per_s": round(U_LOOKUPS / (t_q * 1e-3), 1),
+                           "roofline": {"bound": "hbm, rate of random 64-byte window reads", "kernel": "map_query_kernel",
+                                        "achieved": round(U_LOOKUPS / (t_q * 1e-3) / 1e9, 3),
+                                        "peak": round(win_rate / 1e9, 3), "unit": "G reads/s",
+                                        "frac": round(U_LOOKUPS / (t_q * 1e-3) / win_rate, 4),
+                                        "peak_source": "shmt_random_read, 64-byte reads over a buffer of the table's "
+                                                       "size, measured in this run",
+                                        "hbm_bytes_frac": round(b_q / (t_q * 1e6) / peak, 4)}},
+                "e2e": {"value": round((U_KEYS + U_LOOKUPS) / (e2e_ms * 1e-3), 1), "unit": "keys/s",
+                        "h2d_bytes_per_step": (U_KEYS + U_LOOKUPS) * 8, "d2h_bytes_per_step": U_LOOKUPS * 4,
+                        "ms_per_step": round(e2e_ms, 4), "steps": e2e_n},
+                "gpu_launches": steps * 2})
+    del m, gpu, rows, keys, req
+    torch.cuda.empty_cache()
+    obj["cpu_baseline"] = update_cpu(2, 1, keys_n, req_n, sample=4)
+    return obj
+
+
+def run_update(args) -> None:
+    rank, local_rank, world = dist_env()
+    if rank != 0:
+        return
+    line = {"metric": "inserted+looked-up keys/s", "unit": "keys/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int64 keys, int32 slots, bf16 rows (byte copy)", "data": "synthetic (seeded)",
+            "config": {"workload": UPDATE_WORKLOAD, "keys": U_KEYS, "row_bytes": U_DIM * 2, "lookups": U_LOOKUPS}}
+    if args.impl == "reference":
+        keys_n, req_n = update_keys()
+        cpu = update_cpu(args.steps, args.warmup, keys_n, req_n)
+        line.update({"impl": "reference", "value": cpu["value"], "ms_per_step": cpu["ms_per_step"], "cpu_baseline": cpu,
+                     "e2e": {"value": cpu["value"], "unit": "keys/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        emit(line)
+        return
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    line.update(update_object(args.steps, local_rank))
     emit(line)
 
 
@@ -1208,6 +1797,11 @@ def run_scan_relabel(args) -> None:
     del first
     t32 = scan_ms(capi.thrust_scan, src32, work32, steps)
     t64 = scan_ms(capi.thrust_scan, src64, work64, steps)
+    # the scan on the reference's hot path is CUB's (src/cache_graph_sampling.cu:30-45); torch.cumsum is
+    # CUB's DeviceScan as well: same bytes read and written (out of place, into a second buffer)
+    cub32 = statistics.median(time_launches(lambda: torch.cumsum(src32, 0, dtype=torch.int32, out=work32), 1, stream)
+                              for _ in range(steps))
+    cub64 = statistics.median(time_launches(lambda: torch.cumsum(src64, 0, out=work64), 1, stream) for _ in range(steps))
     for _ in range(3):
         capi.tensor_relabel([ids])
     t_rel = statistics.median(time_launches(lambda: capi.tensor_relabel([ids]), 1, stream) for _ in range(steps))
@@ -1232,6 +1826,10 @@ def run_scan_relabel(args) -> None:
                                  "frac": round(b_rel / (t_rel * 1e6) / peak, 4),
                                  "note": "streamed bytes only; the random 12-byte table accesses (one sector each) "
                                          "are what bounds it"}},
+        "cub_scan": {"int32_ms": round(cub32, 4), "int64_ms": round(cub64, 4),
+                     "int32_gbs": round(b32 / (cub32 * 1e6), 1), "int64_gbs": round(b64 / (cub64 * 1e6), 1),
+                     "what": "torch.cumsum (cub::DeviceScan::InclusiveSum, out of place) on the same inputs: the "
+                             "library scan the reference's hot path calls"},
         "roofline": {"bound": "hbm", "kernel": "scan_kernel (decoupled look-back, one pass)",
                      "achieved": round(b32 / (t32 * 1e6), 1), "peak": peak, "unit": "GB/s",
                      "frac": round(b32 / (t32 * 1e6) / peak, 4), "peak_source": peak_src, "traffic": None},

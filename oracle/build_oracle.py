@@ -31,6 +31,10 @@ def load_cpu() -> C.CDLL:
     lib = C.CDLL(str(build_cpu()))
     vp, i64, i, u64 = C.c_void_p, C.c_int64, C.c_int, C.c_uint64
     lib.oracle_num_threads.restype = i
+    lib.oracle_set_threads.restype = None
+    lib.oracle_set_threads.argtypes = [i]
+    import os
+    lib.oracle_set_threads(len(os.sched_getaffinity(0)))  # whatever OMP_NUM_THREADS the launcher exported
     lib.oracle_gather.restype = None
     lib.oracle_gather.argtypes = [vp, vp, i64, i64, vp]
     lib.oracle_sample_hop.restype = i64

@@ -69,6 +69,12 @@ extern "C" {
 
 int oracle_num_threads(void) { return omp_get_max_threads(); }
 
+// The launcher of a multi-process job may export OMP_NUM_THREADS=1; the CPU baseline is meant to
+// use every core the process may run on, so the caller says how many.
+void oracle_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+}
+
 void oracle_gather(const char* table, const int64_t* idx, int64_t n, int64_t row_bytes, char* out) {
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < n; ++i)

@@ -301,6 +301,47 @@ def check_sample(indptr, indices, seeds, num_picks: int, replace: bool, got_indp
             assert np.unique(got).size == got.size, f"seed {i}: duplicate pick"
 
 
+def check_sample_bulk(indptr, indices, seeds, num_picks: int, replace: bool, got_indptr, got_indices,
+                      distinct_rows: bool = False) -> None:
+    """The assertions of ``check_sample`` as whole-array numpy operations, for full-size
+    workloads (a frontier of 100,000 seeds takes a second instead of minutes).  Rows are looked
+    up in the host CSR only: a cached copy made by ``create_subcsr`` holds the same rows
+    (src/cache_graph_sampling.cu:468-487), so membership in the host row is the same test.
+    ``distinct_rows``: the values of every row are distinct, so a value taken twice without
+    replacement is a position taken twice."""
+    indptr = np.asarray(indptr)
+    indices = np.asarray(indices)
+    seeds = np.asarray(seeds).astype(np.int64)
+    got_indptr, got_indices = np.asarray(got_indptr), np.asarray(got_indices)
+    n = seeds.size
+    begin = indptr[seeds].astype(np.int64)
+    deg = indptr[seeds + 1].astype(np.int64) - begin
+    cnt = np.where(deg > 0, num_picks, 0) if replace else np.minimum(deg, num_picks)
+    want_ptr = np.concatenate([[0], np.cumsum(cnt)]).astype(indptr.dtype)
+    assert got_indptr.dtype == want_ptr.dtype, (got_indptr.dtype, want_ptr.dtype)
+    assert np.array_equal(got_indptr, want_ptr), "sub_indptr differs"
+    nnz = int(want_ptr[-1])
+    assert got_indices.size == nnz
+    owner = np.repeat(np.arange(n, dtype=np.int64), cnt)            # seed index of every output
+    within = np.arange(nnz, dtype=np.int64) - want_ptr[owner].astype(np.int64)
+    exact = np.zeros(nnz, dtype=bool) if replace else deg[owner] <= num_picks
+    assert np.array_equal(got_indices[exact], indices[begin[owner[exact]] + within[exact]]), \
+        "a row with deg <= k was not copied exactly"
+    rest = ~exact
+    if not rest.any():
+        return
+    picked_from = np.unique(owner[rest])                            # seeds whose row was sampled
+    d = deg[picked_from]
+    row_owner = np.repeat(picked_from, d)
+    start = np.concatenate([[0], np.cumsum(d)])[:-1]
+    j = np.arange(int(d.sum()), dtype=np.int64) - np.repeat(start, d)
+    row_keys = (row_owner << 32) | indices[np.repeat(begin[picked_from], d) + j].astype(np.int64)
+    got_keys = (owner[rest] << 32) | got_indices[rest].astype(np.int64)
+    assert np.isin(got_keys, row_keys).all(), "a sampled value lies outside its row"
+    if distinct_rows and not replace:
+        assert np.unique(got_keys).size == got_keys.size, "a position was picked twice"
+
+
 # --------------------------------------------------------------------------- timed CPU lines
 def cpu_fetch_reference(data, indices):
     """The reference's own CPU path for a feature fetch, ``data[q.cpu()]``

@@ -311,7 +311,7 @@ class CUCOStaticHashmap:
 
 
 # --------------------------------------------------------------------------- fetch / set
-def _fetch(uva_data, gpu_data, indices, hashmap, mask, who):
+def _fetch(uva_data, gpu_data, indices, hashmap, mask, who, out=None):
     _check_cuda(indices, "indices")
     indices = indices.contiguous()
     idt = _int_code(indices, who)
@@ -321,7 +321,13 @@ def _fetch(uva_data, gpu_data, indices, hashmap, mask, who):
         _check_cuda(gpu_data, "gpu_data")
         _check_contig(gpu_data, "gpu_data")
     n = indices.numel()
-    out = torch.empty((n, *shape_src.shape[1:]), dtype=shape_src.dtype, device=indices.device)
+    if out is None:
+        out = torch.empty((n, *shape_src.shape[1:]), dtype=shape_src.dtype, device=indices.device)
+    else:
+        _check_cuda(out, "out")
+        _check_contig(out, "out")
+        if out.dtype != shape_src.dtype or tuple(out.shape) != (n, *shape_src.shape[1:]):
+            raise RuntimeError(f"{who}: out must be a {(n, *shape_src.shape[1:])} tensor of {shape_src.dtype}")
     mdt = 0
     if mask is not None:
         _check_cuda(mask, "mask")
@@ -347,9 +353,10 @@ def device_fault() -> int:
     return code.value
 
 
-def uva_fetch(data: torch.Tensor, indices: torch.Tensor) -> torch.Tensor:
-    """src/cache_feature_fetch.cu:47-87 — ``data[indices]`` read over UVA, result on the GPU."""
-    return _fetch(data, None, indices, None, None, "uva_fetch")
+def uva_fetch(data: torch.Tensor, indices: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+    """src/cache_feature_fetch.cu:47-87 — ``data[indices]`` read over UVA, result on the GPU.
+    Extension: ``out`` receives the rows instead of a fresh tensor (filling a cache in place)."""
+    return _fetch(data, None, indices, None, None, "uva_fetch", out)
 
 
 def cache_fetch(uva_data: torch.Tensor, gpu_data: torch.Tensor, indices: torch.Tensor,

@@ -113,6 +113,56 @@ __device__ __forceinline__ int64_t lookback_exclusive_prefix(const TileStates& s
   return prefix;
 }
 
+// The same look-back for a tile computed by several CTAs at once (a thread-block cluster that
+// has already added its CTAs' sums up): every CTA of the cluster calls it with the cluster's
+// aggregate and gets the same prefix, but only the one with PUBLISH writes the descriptor.
+// A waiting lane also gives up as soon as another tile has recorded a timeout, so a kernel
+// whose tile order was broken ends after one bounded wait instead of one per tile.
+template <bool PUBLISH>
+__device__ __forceinline__ int64_t lookback_exclusive_prefix_shared(const TileStates& st, int tile,
+                                                                    int64_t aggregate,
+                                                                    int64_t* status_word,
+                                                                    int spin_limit = kLookbackSpinLimit) {
+  const unsigned lane = threadIdx.x & 31;
+  if (tile == 0) {
+    if (PUBLISH && lane == 0) st_desc(st.d, aggregate, kTileInclusive);
+    return 0;
+  }
+  if (PUBLISH && lane == 0) st_desc(st.d + tile, aggregate, kTileAggregate);
+  int64_t prefix = 0;
+  int base = tile - 1;
+  while (true) {
+    const int t = base - (int)lane;
+    unsigned long long f = kTileInclusive;
+    long long v = 0;
+    if (t >= 0) {
+      int spins = 0;
+      ld_desc(st.d + t, &v, &f);
+      while (f == 0ULL && spins < spin_limit) {
+        __nanosleep(20);
+        ld_desc(st.d + t, &v, &f);
+        if ((++spins & 1023) == 0 && ld_relaxed64(status_word) != DEV_OK) spins = spin_limit;
+      }
+      if (f == 0ULL) {
+        atomicMax(reinterpret_cast<unsigned long long*>(status_word),
+                  (unsigned long long)DEV_TIMEOUT);
+        f = kTileInclusive;
+        v = 0;
+      }
+    }
+    const unsigned known = __ballot_sync(0xffffffffu, f == kTileInclusive);
+    const unsigned upto = known ? (unsigned)(__ffs(known) - 1) : 31u;
+    int64_t part = lane <= upto ? (int64_t)v : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    prefix += part;
+    if (known) break;
+    base -= 32;
+  }
+  if (PUBLISH && lane == 0) st_desc(st.d + tile, prefix + aggregate, kTileInclusive);
+  return prefix;
+}
+
 // Block-wide exclusive scan of one int64 per thread (blockDim.x <= 1024,
 // multiple of 32).  `warp_sums` is 32 int64 of shared memory.  Returns the
 // exclusive prefix of the caller; *total gets the block sum.

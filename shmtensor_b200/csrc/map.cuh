@@ -139,8 +139,10 @@ __device__ __forceinline__ longlong2 cas_slot(Slot* p, longlong2 expect, longlon
 
 // One thread inserts one (key, value): walk the slots from the start of the home window up to the
 // first empty one, which proves the key absent, then claim the first erased slot met on the way,
-// else that empty slot, with a 16-byte CAS.  Occupied slots never change while inserts run, so
-// two threads inserting the same key meet at the same slot and one of them sees the other's key.
+// else that empty slot, with a 16-byte CAS.  A table that was once full has no empty slot left
+// (erasing leaves markers): a whole lap without the key proves it absent just as well, and the
+// first erased slot is claimed then.  Occupied slots never change while inserts run, so two
+// threads inserting the same key meet at the same slot and one of them sees the other's key.
 // Without erased slots this is the placement rule of warp_insert (first empty slot in window
 // order), so both can fill one table.  For bulk builds, where every thread has its own key and
 // nothing else to wait for, this is faster than the cooperative form.  Must not run concurrently
@@ -150,29 +152,32 @@ __device__ __forceinline__ bool thread_insert(const MapView& m, int64_t key, int
   key = narrow_key(m, key);
   if (reserved_key(key)) return false;
   const uint64_t n_slots = m.n_windows * kWindow, none = ~0ULL;
-  uint64_t pos = home_window(m, key) * kWindow, erased_at = none;
-  // a lost race restarts the walk behind the lost slot, so allow two laps
-  for (uint64_t step = 0; step < 2 * n_slots; ++step) {
-    const long long cur = __ldcg(&m.slots[pos].key);
-    if (cur == key) {
-      if (assign) m.slots[pos].val = val;
-      return false;
-    }
-    if (cur == kErasedKey && erased_at == none) erased_at = pos;
-    if (cur == kEmptyKey) {
-      const uint64_t at = erased_at != none ? erased_at : pos;
-      const long long expect = erased_at != none ? kErasedKey : kEmptyKey;
-      const longlong2 old = cas_slot(m.slots + at, make_longlong2(expect, -1), make_longlong2(key, val));
-      if (old.x == expect) return true;
-      if (old.x == key) {
-        if (assign) m.slots[at].val = val;
+  // a lost race starts the walk again; a few restarts cover any realistic contention
+  for (int attempt = 0; attempt < 16; ++attempt) {
+    uint64_t pos = home_window(m, key) * kWindow, erased_at = none, target = none;
+    for (uint64_t step = 0; step < n_slots; ++step) {
+      const long long cur = __ldcg(&m.slots[pos].key);
+      if (cur == key) {
+        if (assign) m.slots[pos].val = val;
         return false;
       }
-      // another key took the slot first: go on behind it
-      pos = at;
-      erased_at = none;
+      if (cur == kErasedKey && erased_at == none) erased_at = pos;
+      if (cur == kEmptyKey) {
+        target = erased_at != none ? erased_at : pos;
+        break;
+      }
+      pos = pos + 1 == n_slots ? 0 : pos + 1;
     }
-    pos = pos + 1 == n_slots ? 0 : pos + 1;
+    if (target == none) target = erased_at;  // a whole lap: no empty slot anywhere
+    if (target == none) break;               // nor an erased one: the table is full
+    const long long expect = target == erased_at ? kErasedKey : kEmptyKey;
+    const longlong2 old = cas_slot(m.slots + target, make_longlong2(expect, -1), make_longlong2(key, val));
+    if (old.x == expect) return true;
+    if (old.x == key) {
+      if (assign) m.slots[target].val = val;
+      return false;
+    }
+    // another key took the slot first: walk again
   }
   *overflow = true;
   return false;
@@ -208,11 +213,14 @@ __device__ __forceinline__ int64_t thread_erase(const MapView& m, int64_t key) {
 // the table keeps its slot; its value is replaced only if `assign`.  Returns
 // the value now stored for the key (-1 for invalid lanes or on overflow) and
 // counts newly stored keys in *n_new (warp total, same on every lane).
+// Placement is thread_insert's: the first erased slot met before the first empty one (or, in a
+// table without empty slots, in a whole lap), else that empty slot.
 __device__ __forceinline__ int64_t warp_insert(const MapView& m, int64_t key, int64_t val,
                                                bool valid, bool assign, int64_t* status_word,
                                                int* n_new) {
   const unsigned full = 0xffffffffu;
   const unsigned lane = threadIdx.x & 31, sub = lane & 3, tile = lane >> 2;
+  const uint64_t none = ~0ULL;
   key = narrow_key(m, key);
   if (reserved_key(key)) valid = false;
   int64_t result = -1;
@@ -224,7 +232,8 @@ __device__ __forceinline__ int64_t warp_insert(const MapView& m, int64_t key, in
     const int64_t v = __shfl_sync(full, val, src);
     bool done = !__shfl_sync(full, (int)valid, src);
     uint64_t w = done ? 0 : home_window(m, k);
-    uint64_t steps = 0;
+    uint64_t steps = 0, erased_slot = none;  // same on the four lanes of a tile
+    int restarts = 0;
     int64_t res = -1;
     bool newly = false;
     while (__any_sync(full, !done)) {
@@ -233,17 +242,34 @@ __device__ __forceinline__ int64_t warp_insert(const MapView& m, int64_t key, in
       if (!done) s = __ldcg(reinterpret_cast<const longlong2*>(p));
       const bool match = !done && s.x == k;
       const bool empty = !done && s.x == kEmptyKey;
+      const bool erased = !done && s.x == kErasedKey;
       const unsigned mb = (__ballot_sync(full, match) >> (tile * 4)) & 0xFu;
       const unsigned eb = (__ballot_sync(full, empty) >> (tile * 4)) & 0xFu;
-      bool ok = false;
-      if (!done && !mb && eb && (int)sub == __ffs(eb) - 1) {
-        const longlong2 old =
-            cas_slot(p, make_longlong2(kEmptyKey, -1), make_longlong2(k, v));
-        ok = old.x == kEmptyKey;
+      const unsigned rb = (__ballot_sync(full, erased) >> (tile * 4)) & 0xFu;
+      if (!done && !mb && erased_slot == none && rb) {
+        // only an erased slot in front of the window's first empty one counts
+        const unsigned first_r = (unsigned)__ffs(rb) - 1u;
+        if (!eb || first_r < (unsigned)__ffs(eb) - 1u) erased_slot = w * kWindow + first_r;
       }
-      const unsigned okb = (__ballot_sync(full, ok) >> (tile * 4)) & 0xFu;
-      const int from = mb ? (int)(tile * 4 + __ffs(mb) - 1) : (int)lane;
-      const int64_t exist = __shfl_sync(full, s.y, from);
+      const bool lap = !done && !mb && !eb && steps + 1 >= m.n_windows;  // the last window of a lap
+      // absent for sure (an empty slot, or the whole table seen): pick the slot to claim
+      uint64_t target = none;
+      long long expect = kEmptyKey;
+      if (!done && !mb && (eb || lap)) {
+        if (erased_slot != none) {
+          target = erased_slot;
+          expect = kErasedKey;
+        } else if (eb) {
+          target = w * kWindow + (unsigned)__ffs(eb) - 1u;
+        }
+      }
+      longlong2 old = make_longlong2(0, 0);
+      const bool try_claim = target != none && sub == 0;
+      if (try_claim) old = cas_slot(m.slots + target, make_longlong2(expect, -1), make_longlong2(k, v));
+      const unsigned okb = (__ballot_sync(full, try_claim && old.x == expect) >> (tile * 4)) & 0xFu;
+      const unsigned sameb = (__ballot_sync(full, try_claim && old.x == k) >> (tile * 4)) & 0xFu;
+      const int from = mb ? (int)(tile * 4 + __ffs(mb) - 1) : (int)(tile * 4);
+      const int64_t exist = __shfl_sync(full, mb ? s.y : old.y, from);
       if (!done) {
         if (mb) {
           if (assign && (int)sub == __ffs(mb) - 1) p->val = v;
@@ -253,16 +279,32 @@ __device__ __forceinline__ int64_t warp_insert(const MapView& m, int64_t key, in
           res = v;
           newly = true;
           done = true;
-        } else if (!eb) {
-          w = w + 1 == m.n_windows ? 0 : w + 1;
-          if (++steps >= m.n_windows) {
+        } else if (sameb) {
+          // another warp stored this very key into the slot a moment ago
+          if (assign && sub == 0) m.slots[target].val = v;
+          res = assign ? v : exist;
+          done = true;
+        } else if (target != none) {
+          // the slot went to another key first: walk again from the home window
+          w = home_window(m, k);
+          steps = 0;
+          erased_slot = none;
+          if (++restarts > 16) {
             if (sub == 0)
               atomicMax(reinterpret_cast<unsigned long long*>(status_word),
                         (unsigned long long)DEV_OVERFLOW);
             done = true;
           }
+        } else if (lap) {
+          // a whole lap, no empty and no erased slot: the table is full
+          if (sub == 0)
+            atomicMax(reinterpret_cast<unsigned long long*>(status_word),
+                      (unsigned long long)DEV_OVERFLOW);
+          done = true;
+        } else {
+          w = w + 1 == m.n_windows ? 0 : w + 1;
+          ++steps;
         }
-        // else: the claimed slot went to another key first; re-read this window
       }
     }
     added += __popc(__ballot_sync(full, newly && sub == 0));

@@ -15,7 +15,10 @@
 //      t_p ~ U[0, deg-k+p] with Philox4x32-10 and the group resolves Floyd's
 //      subset algorithm with k shuffle+ballot steps (O(k) work, exact uniform
 //      k-subset; the reference draws O(deg) numbers and uses global atomics).
-//      k > 32 falls back to the warp-parallel reservoir on the output row.
+//      k > 32: one warp per seed draws positions into a shared-memory set until k distinct
+//      ones (or, for rows shorter than 2k, the deg-k to leave out) are held: O(k) draws, no
+//      global atomics.  Only beyond 1024 picks per seed does it fall back to the reference's
+//      reservoir on the output row.
 #include "ctx.cuh"
 #include "lookback.cuh"
 #include "map.cuh"
@@ -48,6 +51,7 @@ struct HopJob {
   int64_t* result;        // receives nnz
   const int64_t* n_dev;   // if set, the seed count is read here (it was produced on the device)
   int seeds_per_tile;
+  uint32_t set_slots;     // fan-out > 32: words of the per-warp set of chosen positions (0: none)
   // Fused relabel insert (multi-hop path): the kernel also claims a relabel-table slot for
   // every seed and every sampled neighbour, at its index in [seeds | neighbours], and
   // records the slot in rel_out -- the work of relabel's first kernel, done while this
@@ -268,29 +272,45 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
     return;
   }
 
-  // k > 32 (G == 32, one warp per seed): rows are walked k lanes at a time
+  // k > 32 (G == 32): one warp per seed
+  extern __shared__ uint32_t s_sets[];  // per warp: a set of chosen positions (job.set_slots words)
+  const uint32_t set_slots = job.set_slots;
+  uint32_t* set = s_sets + (size_t)(tid >> 5) * set_slots;
   for (int j0 = 0; j0 < rows; j0 += kGroups) {
     const int j = j0 + group;
     const bool active = j < rows;
     const int64_t deg = active ? s_deg[j] : 0;
     const IxT* in = nullptr;
-    IxT* out = nullptr;
+    int64_t out_at = 0;
     if (active) {
       in = static_cast<const IxT*>(s_hit[j] ? job.gpu_indices : job.indices) + s_begin[j];
-      out = out_all + prefix + s_off[j];
+      out_at = prefix + s_off[j];
     }
     const uint32_t seed_idx = (uint32_t)(first + j);
+    // one output element: the neighbour at `pos` of the row goes to slot `o` of the output
+    auto emit = [&](int64_t o, int64_t pos) {
+      const IxT val = __ldg(in + pos);
+      out_all[o] = val;
+      if (relabel) {
+        const uint32_t slot = relabel_insert_one(job.rel_slots, rel_mask, (long long)val,
+                                                 (unsigned)(n + o), job.status);
+        store_int(job.rel_out, sizeof(IxT) == 8, n + o, (int64_t)slot);
+      }
+    };
     if (job.replace) {
       if (deg > 0)
-        for (int64_t p = gl; p < k; p += G)
-          out[p] = in[draw_below(rng, seed_idx, (uint32_t)p, job.off_lo, job.off_hi, (uint64_t)deg)];
+        for (int64_t p = gl; p < k; p += 32)
+          emit(out_at + p, (int64_t)draw_below(rng, seed_idx, (uint32_t)p, job.off_lo, job.off_hi, (uint64_t)deg));
       continue;
     }
-    if (active && deg <= k) {
-      for (int64_t p = gl; p < deg; p += G) out[p] = in[p];
+    if (deg <= k) {
+      for (int64_t p = gl; p < deg; p += 32) emit(out_at + p, p);
+      continue;
     }
-    // reservoir on the output row: positions first, then values
-    if (active && deg > k) {
+    if (set_slots == 0 || deg >= 0xFFFFFFFFll) {
+      // fan-outs beyond the shared-memory set (or rows of 2^32 neighbours): the reservoir on the
+      // output row, O(deg) draws (src/cache_graph_sampling.cu:329-345)
+      IxT* out = out_all + out_at;
       for (int64_t p = gl; p < k; p += 32) out[p] = (IxT)p;
       __syncwarp();
       for (int64_t q = k + gl; q < deg; q += 32) {
@@ -301,9 +321,82 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
       __threadfence_block();
       for (int64_t p = gl; p < k; p += 32) {
         const IxT pos = *reinterpret_cast<volatile IxT*>(out + p);
-        out[p] = in[pos];
+        emit(out_at + p, (int64_t)pos);
+      }
+      continue;
+    }
+    // A uniform k-subset in O(k) draws, all in shared memory: positions are drawn independently
+    // and kept if new, until m distinct ones are held (any rule that treats all positions alike
+    // yields every subset with the same probability).  m = k when the row is at least twice the
+    // fan-out; otherwise the deg - k positions to LEAVE OUT are drawn, so at most half of the
+    // draws are ever rejected.  The set is an open-addressing table of 2^x >= 2k words per warp.
+    const bool complement = deg < 2 * k;
+    const uint32_t m = (uint32_t)(complement ? deg - k : k);
+    const uint32_t smask = set_slots - 1;
+    for (uint32_t q = gl; q < set_slots; q += 32) set[q] = 0xFFFFFFFFu;
+    __syncwarp();
+    uint32_t held = 0, draws = 0;
+    // a draw is rejected with probability below 1/2, so a few rounds suffice; the cap only makes
+    // the loop provably finite
+    for (int round = 0; held < m && round < 256 + (int)(m >> 2); ++round) {
+      const bool mine = held + gl < m;
+      bool kept = false;
+      if (mine) {
+        const uint32_t pos = (uint32_t)draw_below(rng, seed_idx, draws + gl, job.off_lo, job.off_hi, (uint64_t)deg);
+        uint32_t at = (pos * 0x9E3779B1u) & smask;
+        while (true) {
+          const uint32_t old = atomicCAS(set + at, 0xFFFFFFFFu, pos);
+          if (old == 0xFFFFFFFFu) { kept = true; break; }
+          if (old == pos) break;
+          at = (at + 1) & smask;
+        }
+      }
+      held += (uint32_t)__popc(__ballot_sync(full, kept));
+      draws += 32;
+    }
+    __syncwarp();
+    if (held < m && gl == 0) {
+      // never reached in practice: complete the set with the lowest positions not in it
+      for (uint32_t pos = 0; held < m && pos < (uint32_t)deg; ++pos) {
+        uint32_t at = (pos * 0x9E3779B1u) & smask;
+        while (set[at] != 0xFFFFFFFFu && set[at] != pos) at = (at + 1) & smask;
+        if (set[at] == 0xFFFFFFFFu) {
+          set[at] = pos;
+          ++held;
+        }
       }
     }
+    __syncwarp();
+    if (!complement) {
+      // the chosen positions, in table order
+      uint32_t done = 0;
+      for (uint32_t q0 = 0; q0 < set_slots; q0 += 32) {
+        const uint32_t pos = set[q0 + gl];
+        const unsigned has = __ballot_sync(full, pos != 0xFFFFFFFFu);
+        if (pos != 0xFFFFFFFFu) emit(out_at + done + __popc(has & ((1u << gl) - 1u)), (int64_t)pos);
+        done += (uint32_t)__popc(has);
+      }
+    } else {
+      // every position that was not drawn, in row order
+      uint32_t done = 0;
+      for (int64_t p0 = 0; p0 < deg; p0 += 32) {
+        const int64_t pos = p0 + gl;
+        bool keep = pos < deg;
+        if (keep) {
+          uint32_t at = ((uint32_t)pos * 0x9E3779B1u) & smask;
+          while (true) {
+            const uint32_t cur = set[at];
+            if (cur == 0xFFFFFFFFu) break;
+            if (cur == (uint32_t)pos) { keep = false; break; }
+            at = (at + 1) & smask;
+          }
+        }
+        const unsigned has = __ballot_sync(full, keep);
+        if (keep) emit(out_at + done + __popc(has & ((1u << gl) - 1u)), pos);
+        done += (uint32_t)__popc(has);
+      }
+    }
+    __syncwarp();  // the set is cleared for the next seed only after every lane has read it
   }
 }
 
@@ -364,15 +457,36 @@ static int pick_seeds_per_tile(int64_t n, int64_t k) {
   return (int)s;
 }
 
+// Fan-outs above 32 keep a set of chosen positions per warp in shared memory: the smallest
+// power of two >= 2k words, for k <= 1024 (64 KB per CTA at most).  0: the fan-out needs none,
+// or is too large for it.
+constexpr int64_t kMaxSetPicks = 1024;
+static uint32_t set_slots_for(int64_t k) {
+  if (k <= 32 || k > kMaxSetPicks) return 0;
+  uint32_t slots = 128;
+  while ((int64_t)slots < 2 * k) slots <<= 1;
+  return slots;
+}
+
 template <typename IxT>
-static void launch_hop(const HopJob& job, int64_t n_tiles, cudaStream_t s, bool pdl = false) {
+static cudaError_t launch_hop(HopJob job, int64_t n_tiles, cudaStream_t s, bool pdl = false) {
   const unsigned grid = (unsigned)n_tiles;
-  if (job.k <= 8)
-    launch_kernel(pdl, sample_hop_kernel<IxT, 8>, grid, kHopThreads, 0, s, job);
-  else if (job.k <= 16)
-    launch_kernel(pdl, sample_hop_kernel<IxT, 16>, grid, kHopThreads, 0, s, job);
-  else
-    launch_kernel(pdl, sample_hop_kernel<IxT, 32>, grid, kHopThreads, 0, s, job);
+  job.set_slots = set_slots_for(job.k);
+  if (job.k <= 8) return launch_kernel(pdl, sample_hop_kernel<IxT, 8>, grid, kHopThreads, 0, s, job);
+  if (job.k <= 16) return launch_kernel(pdl, sample_hop_kernel<IxT, 16>, grid, kHopThreads, 0, s, job);
+  const size_t smem = (size_t)job.set_slots * sizeof(uint32_t) * (kHopThreads / 32);
+  if (smem > 0) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !configured[dev]) {
+      const cudaError_t e = cudaFuncSetAttribute(sample_hop_kernel<IxT, 32>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)(2 * kMaxSetPicks * sizeof(uint32_t) * (kHopThreads / 32)));
+      if (e != cudaSuccess) return e;
+      configured[dev] = true;
+    }
+  }
+  return launch_kernel(pdl, sample_hop_kernel<IxT, 32>, grid, kHopThreads, smem, s, job);
 }
 
 }  // namespace shmt
@@ -436,10 +550,8 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const v
   job.n_dev = nullptr;
   if (nnz_host) job.post = ctx_begin_post(ctx, ctx->d_words(), 4, ctx->d_words() + W_DONE);
   SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + tile_state_bytes(n_tiles), s));
-  if (indices_dtype == SHMT_I64)
-    launch_hop<long long>(job, n_tiles, s);
-  else
-    launch_hop<int>(job, n_tiles, s);
+  SHMT_CUDA_TRY(indices_dtype == SHMT_I64 ? launch_hop<long long>(job, n_tiles, s)
+                                          : launch_hop<int>(job, n_tiles, s));
   SHMT_CUDA_TRY(cudaGetLastError());
   if (nnz_host) {
     if (int rc = ctx_mark_tail(ctx, s)) return rc;
@@ -532,7 +644,7 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     job.ticket = w + 0;
     job.status = status;
     job.result = w + 1;
-    const bool fuse_insert = fanouts[h] <= 32;  // the k > 32 sampler keeps relabel's own kernel
+    const bool fuse_insert = true;  // every sampler claims the relabel slots of what it emits
     if (fuse_insert) {
       RelTable t;
       if (int rc = relabel_table(ctx, cap[h + 1], &t, s)) return rc;
@@ -540,10 +652,8 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
       job.rel_mask = t.mask;
       job.rel_out = out_relabel[h];
     }
-    if (indices_dtype == SHMT_I64)
-      launch_hop<long long>(job, hop_tiles[h], s, /*pdl=*/h > 0);
-    else
-      launch_hop<int>(job, hop_tiles[h], s, /*pdl=*/h > 0);
+    SHMT_CUDA_TRY(indices_dtype == SHMT_I64 ? launch_hop<long long>(job, hop_tiles[h], s, /*pdl=*/h > 0)
+                                            : launch_hop<int>(job, hop_tiles[h], s, /*pdl=*/h > 0));
     SHMT_CUDA_TRY(cudaGetLastError());
 
     Parts ps{};

@@ -2,6 +2,9 @@
 // Semantics follow cub_exclusiveSum (reference src/cache_graph_sampling.cu:30-45)
 // and the intended meaning of thrust_scan (reference src/thrust_scan.cu:9-18,
 // whose own lambda races); integer arithmetic wraps.
+#include <stdlib.h>
+
+#include "bulk.cuh"
 #include "ctx.cuh"
 #include "lookback.cuh"
 
@@ -31,7 +34,8 @@ struct ScanWord<long long> { using type = unsigned long long; };
 // bytes per tile bound the rate of the whole scan.
 template <typename T>
 __global__ void __launch_bounds__(kScanThreads, 2)
-scan_kernel(T* __restrict__ data, int64_t n, int exclusive, int vec_ok, TileStates st, int64_t* words) {
+scan_kernel(T* __restrict__ data, int64_t n, int exclusive, int vec_ok, TileStates st, int64_t* words,
+            const TileDesc* carry) {
   using U = typename ScanWord<T>::type;
   constexpr int VEC = 16 / (int)sizeof(T);
   constexpr int TILE = kScanTileBytes / (int)sizeof(T);
@@ -99,7 +103,9 @@ scan_kernel(T* __restrict__ data, int64_t n, int exclusive, int vec_ok, TileStat
     const U total = __shfl_sync(full, linc, 31);
     // zero-extended aggregate: tile sums add up in 64 bits, of which the low bits are used
     const int64_t p = lookback_exclusive_prefix(st, tile, (int64_t)(uint64_t)total, words + W_STATUS);
-    if (lane == 0) s_prefix = p;
+    // `carry`: this launch continues a scan whose first part another kernel did (its last
+    // descriptor holds the sum of everything before `data`)
+    if (lane == 0) s_prefix = p + (carry ? carry->value : 0);
   }
   __syncthreads();
   const U prefix = (U)(uint64_t)s_prefix;
@@ -121,6 +127,217 @@ scan_kernel(T* __restrict__ data, int64_t n, int exclusive, int vec_ok, TileStat
   }
 }
 
+
+// ---- large inputs: persistent clusters ------------------------------------------------------
+// What bounds the kernel above is not bytes but the time a tile sits in registers: ticket,
+// load latency, local sums, look-back (a prefix crosses 32 tiles per round trip through L2 and
+// ~100 tiles per microsecond are started), store.  This kernel takes the three longest waits off
+// that path.  (1) The grid is persistent (every cluster resident at once, super-tiles dealt
+// round-robin), so there is no ticket: a tile's predecessors belong to clusters that are
+// running and only ever wait for still earlier tiles.  (2) A CTA's next tile is brought into
+// shared memory by one bulk copy while the current one is summed, looked back and stored from
+// registers, so load latency overlaps the rest.  (3) Four CTAs form a cluster, add their sums
+// up through distributed shared memory and look back once for a 256 KB super-tile: a quarter of
+// the descriptors per microsecond, so the nearest known prefix is one round trip away, not three.
+constexpr int kScanCluster = 4;
+constexpr int64_t kScanSuperBytes = (int64_t)kScanCluster * kScanTileBytes;
+constexpr int64_t kScanClusterMinBytes = (int64_t)32 << 20;  // below this the ticketed kernel spreads better
+
+__device__ __forceinline__ unsigned cluster_ctarank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned cluster_id_x() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ unsigned cluster_count_x() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// 8-byte store into the shared memory of CTA `rank` of this cluster, at the address `local`
+// has in the calling CTA (same kernel, same layout).
+__device__ __forceinline__ void st_cluster_u64(void* local, unsigned rank, unsigned long long v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
+  asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(remote), "l"(v) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads, 2)
+scan_cluster_kernel(T* __restrict__ data, int64_t n_super, int exclusive, TileStates st, int64_t* words) {
+  using U = typename ScanWord<T>::type;
+  constexpr int VEC = 16 / (int)sizeof(T);
+  constexpr int PER_LANE = kScanPartials / 32;
+  extern __shared__ __align__(128) unsigned char landing[];  // one tile, filled by the bulk copy
+  __shared__ U partial[kScanPartials];
+  __shared__ unsigned long long s_sum[2][kScanCluster];  // CTA sums of the cluster, by iteration parity
+  __shared__ int64_t s_prefix;
+  __shared__ __align__(8) uint64_t s_bar;
+  const unsigned full = 0xffffffffu;
+  const unsigned tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned rank = cluster_ctarank();
+  const int64_t n_clusters = cluster_count_x();
+  char* bytes = reinterpret_cast<char*>(data);
+  union Pack {
+    uint4 q;
+    U a[VEC];
+  };
+
+  if (tid == 0) mbar_init(&s_bar, 1);
+  mbar_init_fence();
+  __syncthreads();
+  cluster_sync_all();  // every CTA of the cluster is running before anyone writes into its memory
+
+  int64_t super = cluster_id_x();
+  if (tid == 0 && super < n_super) {
+    mbar_arrive_expect_tx(&s_bar, kScanTileBytes);
+    bulk_load(landing, bytes + (super * kScanCluster + rank) * kScanTileBytes, kScanTileBytes, &s_bar);
+  }
+  uint32_t phase = 0;
+  for (int it = 0; super < n_super; super += n_clusters, ++it) {
+    if (!mbar_wait_bounded(&s_bar, phase))
+      atomicMax(reinterpret_cast<unsigned long long*>(words + W_STATUS), (unsigned long long)DEV_TIMEOUT);
+    phase ^= 1u;
+    U v[kScanVecs][VEC], vsum[kScanVecs], inc[kScanVecs];
+#pragma unroll
+    for (int k = 0; k < kScanVecs; ++k) {
+      Pack p;
+      p.q = reinterpret_cast<const uint4*>(landing)[k * kScanThreads + tid];
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) v[k][j] = p.a[j];
+    }
+    __syncthreads();  // the tile is in registers: the landing buffer is free, `partial` too
+    const int64_t next = super + n_clusters;
+    if (tid == 0 && next < n_super) {
+      mbar_arrive_expect_tx(&s_bar, kScanTileBytes);
+      bulk_load(landing, bytes + (next * kScanCluster + rank) * kScanTileBytes, kScanTileBytes, &s_bar);
+    }
+#pragma unroll
+    for (int k = 0; k < kScanVecs; ++k) {
+#pragma unroll
+      for (int j = 1; j < VEC; ++j) v[k][j] += v[k][j - 1];
+      vsum[k] = v[k][VEC - 1];
+      inc[k] = vsum[k];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const U up = __shfl_up_sync(full, inc[k], o);
+        if (lane >= (unsigned)o) inc[k] += up;
+      }
+      if (lane == 31) partial[k * kScanWarps + warp] = inc[k];
+    }
+    __syncthreads();
+    if (warp == 0) {
+      U a[PER_LANE], lsum = 0;
+#pragma unroll
+      for (int q = 0; q < PER_LANE; ++q) {
+        a[q] = partial[lane * PER_LANE + q];
+        lsum += a[q];
+      }
+      U linc = lsum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const U up = __shfl_up_sync(full, linc, o);
+        if (lane >= (unsigned)o) linc += up;
+      }
+      U run = linc - lsum;
+#pragma unroll
+      for (int q = 0; q < PER_LANE; ++q) {
+        partial[lane * PER_LANE + q] = run;
+        run += a[q];
+      }
+      const U total = __shfl_sync(full, linc, 31);
+      // this CTA's sum to every CTA of the cluster (its own copy included)
+      if (lane < kScanCluster) st_cluster_u64(&s_sum[it & 1][rank], lane, (unsigned long long)total);
+    }
+    cluster_sync_all();  // sums delivered; also the CTA-wide barrier behind `partial`
+    if (warp == 0) {
+      unsigned long long before = 0, whole = 0;
+#pragma unroll
+      for (int r = 0; r < kScanCluster; ++r) {
+        const unsigned long long t = s_sum[it & 1][r];
+        whole += t;
+        if ((unsigned)r < rank) before += t;
+      }
+      const int64_t p = rank == 0
+          ? lookback_exclusive_prefix_shared<true>(st, (int)super, (int64_t)whole, words + W_STATUS)
+          : lookback_exclusive_prefix_shared<false>(st, (int)super, (int64_t)whole, words + W_STATUS);
+      if (lane == 0) s_prefix = p + (int64_t)before;
+    }
+    __syncthreads();
+    const U prefix = (U)(uint64_t)s_prefix;
+    T* out = data + (super * kScanCluster + rank) * (kScanTileBytes / (int64_t)sizeof(T));
+#pragma unroll
+    for (int k = 0; k < kScanVecs; ++k) {
+      const U ahead = prefix + partial[k * kScanWarps + warp] + (inc[k] - vsum[k]);
+      Pack p;
+#pragma unroll
+      for (int j = 0; j < VEC; ++j)
+        p.a[j] = ahead + (exclusive ? (j ? v[k][j - 1] : U(0)) : v[k][j]);
+      reinterpret_cast<uint4*>(out)[k * kScanThreads + tid] = p.q;
+    }
+  }
+}
+
+// Clusters of the persistent grid: as many as are resident at once (asked of the runtime once
+// per device and element type), never more than there are super-tiles.
+template <typename T>
+static int scan_cluster_grid(int64_t n_super, unsigned* grid) {
+  static int resident[64] = {0};
+  int dev = 0;
+  SHMT_CUDA_TRY(cudaGetDevice(&dev));
+  SHMT_REQUIRE(dev >= 0 && dev < 64, "scan: device index %d not supported", dev);
+  if (resident[dev] == 0) {
+    SHMT_CUDA_TRY(cudaFuncSetAttribute(scan_cluster_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kScanTileBytes));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kScanCluster * 64);
+    cfg.blockDim = dim3(kScanThreads);
+    cfg.dynamicSmemBytes = kScanTileBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = kScanCluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    SHMT_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, scan_cluster_kernel<T>, &cfg));
+    SHMT_REQUIRE(n >= 1, "scan: no cluster of %d CTAs fits on this device", kScanCluster);
+    resident[dev] = n;
+  }
+  const int64_t c = n_super < resident[dev] ? n_super : resident[dev];
+  *grid = (unsigned)(c * kScanCluster);
+  return SHMT_OK;
+}
+
+template <typename T>
+static int run_scan_clusters(void* data, int64_t n_super, int exclusive, TileStates st, int64_t* words,
+                             cudaStream_t s) {
+  unsigned grid = 0;
+  if (int rc = scan_cluster_grid<T>(n_super, &grid)) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kScanThreads);
+  cfg.dynamicSmemBytes = kScanTileBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kScanCluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  SHMT_CUDA_TRY(cudaLaunchKernelEx(&cfg, scan_cluster_kernel<T>, static_cast<T*>(data), n_super, exclusive, st, words));
+  return SHMT_OK;
+}
+
 template <typename T>
 static int64_t scan_tiles(int64_t n) {
   const int64_t tile = kScanTileBytes / (int64_t)sizeof(T);
@@ -128,10 +345,28 @@ static int64_t scan_tiles(int64_t n) {
 }
 
 template <typename T>
-static void run_scan(void* data, int64_t n, int exclusive, TileStates st, int64_t* words, cudaStream_t s) {
+static void run_scan(void* data, int64_t n, int exclusive, TileStates st, int64_t* words, cudaStream_t s,
+                     const TileDesc* carry = nullptr) {
   const int vec_ok = ((uintptr_t)data & 15) == 0;
   scan_kernel<T><<<(unsigned)scan_tiles<T>(n), kScanThreads, 0, s>>>(static_cast<T*>(data), n, exclusive,
-                                                                      vec_ok, st, words);
+                                                                      vec_ok, st, words, carry);
+}
+
+// Large, 16-byte aligned inputs: whole 256 KB super-tiles by the persistent cluster kernel, what
+// is left (less than one super-tile) by the ticketed kernel, which starts from the sum the
+// last super-tile's descriptor holds.
+template <typename T>
+static int run_scan_large(void* data, int64_t n, int exclusive, char* state_base, int64_t* words, cudaStream_t s) {
+  const int64_t per_super = kScanSuperBytes / (int64_t)sizeof(T);
+  const int64_t n_super = n / per_super;
+  TileStates st = carve_tile_states(state_base, n_super);
+  if (int rc = run_scan_clusters<T>(data, n_super, exclusive, st, words, s)) return rc;
+  const int64_t rest = n - n_super * per_super;
+  if (rest > 0) {
+    TileStates tail = carve_tile_states(state_base + tile_state_bytes(n_super), scan_tiles<T>(rest));
+    run_scan<T>(static_cast<T*>(data) + n_super * per_super, rest, exclusive, tail, words, s, st.d + (n_super - 1));
+  }
+  return SHMT_OK;
 }
 
 // Exercises the give-up path of the look-back on purpose, harmlessly: one warp plays tile 1
@@ -152,10 +387,18 @@ int launch_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
   // status / result / ticket words and the tile descriptors start at zero
   SHMT_CUDA_TRY(cudaMemsetAsync(ctx->d_words(), 0, 256, stream));
   SHMT_CUDA_TRY(cudaMemsetAsync(st.d, 0, tile_state_bytes(n_tiles), stream));
-  if (dtype == SHMT_I64)
+  static const bool no_clusters = getenv("SHMT_SCAN_NO_CLUSTERS") != nullptr;
+  if (!no_clusters && ((uintptr_t)data & 15) == 0 && n * int_itemsize(dtype) >= kScanClusterMinBytes) {
+    // the ticketed kernel's descriptor block is larger than what both kernels need here
+    char* base = reinterpret_cast<char*>(st.d);
+    if (int rc = dtype == SHMT_I64 ? run_scan_large<long long>(data, n, exclusive, base, ctx->d_words(), stream)
+                                   : run_scan_large<int>(data, n, exclusive, base, ctx->d_words(), stream))
+      return rc;
+  } else if (dtype == SHMT_I64) {
     run_scan<long long>(data, n, exclusive, st, ctx->d_words(), stream);
-  else
+  } else {
     run_scan<int>(data, n, exclusive, st, ctx->d_words(), stream);
+  }
   SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;
 }

@@ -53,6 +53,29 @@ def test_scan_tile_edges_views_and_many_tiles(capi, dtype):
     assert capi.device_fault() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.int32, torch.int64])
+def test_scan_large_inputs_through_the_cluster_kernel(capi, dtype):
+    """From 32 MB on, whole 256 KB super-tiles go through the persistent cluster kernel and the
+    rest through the ticketed one, which carries on from the last super-tile's sum: lengths at and
+    around super-tile multiples, more super-tiles than resident clusters (every cluster loops),
+    inclusive and exclusive, values that wrap in int32."""
+    item = 4 if dtype == torch.int32 else 8
+    per_super = (256 << 10) // item
+    g = torch.Generator(device="cuda").manual_seed(123)
+    n_max = 700 * per_super + 12_345
+    big = torch.randint(-(2 ** 20), 2 ** 20, (n_max,), generator=g, device="cuda").to(dtype)
+    for n in (128 * per_super, 128 * per_super + 1, 129 * per_super - 1, 300 * per_super + 5 * 4096 + 3, n_max):
+        for fn, excl in ((capi.thrust_scan, False), (capi.exclusive_scan_, True)):
+            work = big[:n].clone()
+            fn(work)
+            capi.check_async()
+            want = torch.cumsum(big[:n], 0, dtype=dtype)
+            if excl:
+                want = want - big[:n]
+            assert torch.equal(work, want), (n, excl)
+    assert capi.device_fault() == 0
+
+
 def test_scan_int32_wraps_like_the_oracle(capi):
     a = torch.full((5000,), 2**30, dtype=torch.int32, device="cuda")
     want = oracle.scan_inclusive(a.cpu().numpy())

@@ -89,6 +89,13 @@ def test_directory_plan_single_rank_and_default_replication():
     assert default_replication(480_000, 1) == 0
     assert default_replication(480_000, 4) == 15_000 and default_replication(2000, 8) == 1024
     assert default_replication(500, 8) == 500
+    from shmtensor_b200.partition import head_for_mass
+    assert head_for_mass(torch.tensor([5.0, 3.0, 1.0, 1.0]), 0.5) == 1      # 5 of 10 is half
+    assert head_for_mass(torch.tensor([5.0, 3.0, 1.0, 1.0]), 0.8) == 2
+    assert head_for_mass(torch.tensor([5.0, 3.0, 1.0, 1.0]), 1.0) == 4
+    assert head_for_mass(torch.tensor([]), 0.5) == 0 and head_for_mass(torch.ones(7), 0.0) == 0
+    zipf = 1.0 / torch.arange(1, 480_001, dtype=torch.float64) ** 1.1
+    assert head_for_mass(zipf, 0.5) < 200                                   # a skewed stream's head is tiny
     # more replicas than ids: everything is replicated
     values, mine, counts, rep = plan_directory(ids, 4, 2, 10_000)
     assert rep == 3000 and counts == [0, 0, 0, 0] and torch.equal(mine, ids)
