@@ -39,13 +39,23 @@ int shmt_version(void);
  * Owns the per-device scratch every op needs (look-back tile states, relabel
  * table, device/pinned result words).  Scratch grows on demand and is reused,
  * so steady-state calls allocate nothing.  One context serves one stream at a
- * time: two ops on the same context must not overlap on the GPU.
+ * time: two ops on the same context must not overlap on the GPU; callers that
+ * use several streams keep one context per stream.
  * Replaces the reference's per-call torch::empty / raw_allocate temporaries
  * (src/cache_graph_sampling.cu:30-45,50-56; src/tensor_relabel.cu:141-177).   */
 typedef struct shmt_ctx shmt_ctx;
 int shmt_ctx_create(int device, shmt_ctx** out);
 int shmt_ctx_destroy(shmt_ctx* ctx);
 int64_t shmt_ctx_scratch_bytes(const shmt_ctx* ctx);
+/* Size the context before the first call of a new shape, so that no hot call has to free and
+ * allocate device memory (which stalls the device): at least scratch_bytes of look-back state
+ * (16 bytes per tile; a scan of n items of 8 bytes needs n / 512 bytes) and a relabel table for
+ * relabel_ids ids.  shmt_ctx_reserve_minibatch sizes both for shmt_sample_minibatch calls of up
+ * to n_seeds seeds with these fan-outs.  No counterpart in the reference, which allocates
+ * temporaries on every call (src/cache_graph_sampling.cu:50-56).                          */
+int shmt_ctx_reserve(shmt_ctx* ctx, int64_t scratch_bytes, int64_t relabel_ids, void* stream);
+int shmt_ctx_reserve_minibatch(shmt_ctx* ctx, int64_t n_seeds, const int64_t* fanouts,
+                               int n_hops, void* stream);
 /* Wait for `stream` and report what the last asynchronous op on this context (a scan,
  * or a hop / relabel called without a host result pointer) left in its status word:
  * SHMT_OK, SHMT_ERR_TIMEOUT or SHMT_ERR_CAPACITY.  No counterpart in the reference.  */

@@ -49,6 +49,8 @@ SIGNATURES = {
     "shmt_ctx_destroy": (_i, [_vp]),
     "shmt_ctx_scratch_bytes": (_i64, [_vp]),
     "shmt_ctx_check": (_i, [_vp, _vp]),
+    "shmt_ctx_reserve": (_i, [_vp, _i64, _i64, _vp]),
+    "shmt_ctx_reserve_minibatch": (_i, [_vp, _i64, _pi64, _i, _vp]),
     "shmt_map_table_bytes": (_i64, [_i64, _i64]),
     "shmt_map_create": (_i, [_i, _i64, _i64, _i, _i, _vp, _vp, _pvp]),
     "shmt_map_insert": (_i, [_vp, _vp, _vp, _i64, _vp]),

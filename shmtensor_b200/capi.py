@@ -72,14 +72,36 @@ _contexts: dict = {}
 
 
 def _ctx(device: torch.device) -> int:
-    """Per-device libshmt context (scratch + result words), created on first use."""
+    """libshmt context of (device, torch's current stream on it), created on first use.  A
+    context's scratch serves one stream at a time, so every stream gets its own: calls issued
+    from different torch streams can overlap on the GPU without sharing look-back state, result
+    words or the relabel table."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    h = _contexts.get(idx)
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    h = _contexts.get(key)
     if h is None:
         out = C.c_void_p()
         check(lib.shmt_ctx_create(idx, C.byref(out)))
-        h = _contexts[idx] = out.value
+        h = _contexts[key] = out.value
     return h
+
+
+def reserve_minibatch(n_seeds: int, fanouts: Sequence[int], device="cuda") -> None:
+    """Extension: size the current stream's context for ``sample_minibatch`` calls of up to
+    ``n_seeds`` seeds with these fan-outs, so the first mini-batch does not stop to allocate."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    fan = (C.c_int64 * len(fanouts))(*[int(k) for k in fanouts])
+    check(lib.shmt_ctx_reserve_minibatch(_ctx(device), int(n_seeds), fan, len(fanouts), _stream(device)))
+
+
+def context_scratch_bytes(device="cuda") -> int:
+    """Extension: device bytes the current stream's context holds."""
+    device = torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return lib.shmt_ctx_scratch_bytes(_ctx(device))
 
 
 def _row_bytes(data: torch.Tensor) -> int:

@@ -219,6 +219,20 @@ int shmt_ctx_check(shmt_ctx* ctx, void* stream) {
   return ctx_fetch_words(ctx, static_cast<cudaStream_t>(stream), "shmt_ctx_check");
 }
 
+int shmt_ctx_reserve(shmt_ctx* ctx, int64_t scratch_bytes, int64_t relabel_ids, void* stream) {
+  SHMT_REQUIRE(ctx != nullptr, "shmt_ctx_reserve: ctx is null");
+  SHMT_REQUIRE(scratch_bytes >= 0 && relabel_ids >= 0 && relabel_ids < ((int64_t)1 << 30),
+               "shmt_ctx_reserve: sizes out of range");
+  DeviceGuard guard(ctx->device);
+  if (int rc = ctx_reserve(ctx, (size_t)scratch_bytes)) return rc;
+  if (relabel_ids > 0) {
+    uint64_t cap = 64;
+    while (cap < (uint64_t)relabel_ids * 2) cap <<= 1;
+    if (int rc = ctx_reserve_table(ctx, cap * 16, static_cast<cudaStream_t>(stream))) return rc;
+  }
+  return SHMT_OK;
+}
+
 int64_t shmt_ctx_scratch_bytes(const shmt_ctx* ctx) {
   return ctx ? (int64_t)(ctx->scratch_bytes + ctx->table_bytes) : 0;
 }

@@ -489,11 +489,54 @@ static cudaError_t launch_hop(HopJob job, int64_t n_tiles, cudaStream_t s, bool 
   return launch_kernel(pdl, sample_hop_kernel<IxT, 32>, grid, kHopThreads, smem, s, job);
 }
 
+// Scratch layout of a multi-hop mini-batch, from its worst-case sizes (c_0 = n_seeds,
+// c_{h+1} = c_h * (1 + fanouts[h])).
+constexpr int kMaxHops = 8;
+struct MinibatchPlan {
+  int64_t cap[kMaxHops + 1], hop_tiles[kMaxHops], rel_tiles[kMaxHops];
+  int spt[kMaxHops];
+  size_t off_hop[kMaxHops], off_rel[kMaxHops];
+  size_t scratch_bytes;
+};
+
+static int plan_minibatch(int64_t n_seeds, const int64_t* fanouts, int n_hops, MinibatchPlan* p) {
+  SHMT_REQUIRE(n_hops >= 1 && n_hops <= kMaxHops, "mini-batch: 1..%d hops", kMaxHops);
+  SHMT_REQUIRE(n_seeds >= 1 && n_seeds < ((int64_t)1 << 31), "mini-batch: seed count out of range");
+  SHMT_REQUIRE(fanouts != nullptr, "mini-batch: fanouts is null");
+  p->cap[0] = n_seeds;
+  size_t cursor = ((size_t)(n_hops * 8 + 8) * 8 + 255) & ~(size_t)255;
+  for (int h = 0; h < n_hops; ++h) {
+    SHMT_REQUIRE(fanouts[h] >= 1 && fanouts[h] < ((int64_t)1 << 20), "mini-batch: fan-out out of range");
+    p->cap[h + 1] = p->cap[h] * (1 + fanouts[h]);
+    SHMT_REQUIRE(p->cap[h + 1] < ((int64_t)1 << 30), "mini-batch: worst-case frontier too large");
+    p->spt[h] = pick_seeds_per_tile(p->cap[h], fanouts[h]);
+    p->hop_tiles[h] = (p->cap[h] + p->spt[h] - 1) / p->spt[h];
+    p->rel_tiles[h] = (p->cap[h + 1] + kRelTile - 1) / kRelTile;
+    p->off_hop[h] = cursor;
+    cursor += (tile_state_bytes(p->hop_tiles[h]) + 255) & ~(size_t)255;
+    p->off_rel[h] = cursor;
+    cursor += (tile_state_bytes(p->rel_tiles[h]) + 255) & ~(size_t)255;
+  }
+  p->scratch_bytes = cursor;
+  return SHMT_OK;
+}
+
 }  // namespace shmt
 
 using namespace shmt;
 
 extern "C" {
+
+int shmt_ctx_reserve_minibatch(shmt_ctx* ctx, int64_t n_seeds, const int64_t* fanouts, int n_hops,
+                               void* stream) {
+  SHMT_REQUIRE(ctx != nullptr, "shmt_ctx_reserve_minibatch: ctx is null");
+  MinibatchPlan plan;
+  if (int rc = plan_minibatch(n_seeds, fanouts, n_hops, &plan)) return rc;
+  DeviceGuard guard(ctx->device);
+  if (int rc = ctx_reserve(ctx, plan.scratch_bytes)) return rc;
+  RelTable t;
+  return relabel_table(ctx, plan.cap[n_hops], &t, static_cast<cudaStream_t>(stream));
+}
 
 int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
                     int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
@@ -573,7 +616,6 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
                           uint64_t rng_offset, void* const* out_sub_indptr,
                           void* const* out_sub_indices, void* const* out_relabel,
                           void* const* out_frontier, int64_t* sizes_host, void* stream) {
-  constexpr int kMaxHops = 8;
   SHMT_REQUIRE(ctx != nullptr, "shmt_sample_minibatch: ctx is null");
   SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(indices_dtype),
                "shmt_sample_minibatch: ID can only be int32 or int64");
@@ -588,25 +630,16 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
   // worst-case frontier sizes and the scratch plan: [words][per hop: sample tiles | relabel tiles]
-  int64_t cap[kMaxHops + 1], hop_tiles[kMaxHops], rel_tiles[kMaxHops];
-  int spt[kMaxHops];
-  size_t off_hop[kMaxHops], off_rel[kMaxHops];
-  cap[0] = n_seeds;
-  size_t cursor = ((size_t)(n_hops * 8 + 8) * 8 + 255) & ~(size_t)255;
-  for (int h = 0; h < n_hops; ++h) {
-    SHMT_REQUIRE(fanouts[h] >= 1 && fanouts[h] < ((int64_t)1 << 20), "shmt_sample_minibatch: fan-out out of range");
+  MinibatchPlan plan;
+  if (int rc = plan_minibatch(n_seeds, fanouts, n_hops, &plan)) return rc;
+  for (int h = 0; h < n_hops; ++h)
     SHMT_REQUIRE(out_sub_indptr[h] && out_sub_indices[h] && out_relabel[h] && out_frontier[h],
                  "shmt_sample_minibatch: output buffer of hop %d is null", h);
-    cap[h + 1] = cap[h] * (1 + fanouts[h]);
-    SHMT_REQUIRE(cap[h + 1] < ((int64_t)1 << 30), "shmt_sample_minibatch: worst-case frontier too large");
-    spt[h] = pick_seeds_per_tile(cap[h], fanouts[h]);
-    hop_tiles[h] = (cap[h] + spt[h] - 1) / spt[h];
-    rel_tiles[h] = (cap[h + 1] + kRelTile - 1) / kRelTile;
-    off_hop[h] = cursor;
-    cursor += (tile_state_bytes(hop_tiles[h]) + 255) & ~(size_t)255;
-    off_rel[h] = cursor;
-    cursor += (tile_state_bytes(rel_tiles[h]) + 255) & ~(size_t)255;
-  }
+  const int64_t* cap = plan.cap;
+  const int64_t *hop_tiles = plan.hop_tiles, *rel_tiles = plan.rel_tiles;
+  const int* spt = plan.spt;
+  const size_t *off_hop = plan.off_hop, *off_rel = plan.off_rel;
+  const size_t cursor = plan.scratch_bytes;
   if (int rc = ctx_reserve(ctx, cursor)) return rc;
   char* base = ctx->region();
   int64_t* words = reinterpret_cast<int64_t*>(base);

@@ -59,6 +59,10 @@ class GPUSamplingDataloader:
         self.seeds = self.seeds.cuda()
         self._set_len()
         self.curr = 0
+        if self.fused and len(self.num_picks) <= 8:
+            # scratch for the largest mini-batch this loader can issue, before the first one
+            capi.reserve_minibatch(max(1, min(self.batchsize, max(1, self.seeds.numel()))),
+                                   list(reversed(self.num_picks)), self.seeds.device)
 
     # ------------------------------------------------------------------ seed bookkeeping
     def _local_share(self, seeds):

@@ -119,13 +119,17 @@ def test_seed_counts_and_cached_rows(capi, n_seeds):
         capi.unpin_memory(indices)
 
 
-@pytest.mark.parametrize("deg,k", [(20, 5), (40, 15), (17, 16), (100, 32), (300, 40), (1000, 10)])
+@pytest.mark.parametrize("deg,k", [(20, 5), (40, 15), (17, 16), (100, 32), (300, 40), (1000, 10),
+                                   # fan-outs above 32: positions drawn into a shared-memory set; rows shorter
+                                   # than 2k draw what to leave out instead
+                                   (10_000, 64), (1000, 100), (100, 64), (70, 40), (41, 40), (5000, 1024),
+                                   (3000, 1500)])
 def test_without_replacement_is_uniform(capi, deg, k):
     """Chi-square on how often each position of one row is picked (marginal k/deg), p > 0.01,
     plus: every sample is k distinct positions."""
     indptr = torch.tensor([0, deg], dtype=torch.int64, device="cuda")
     indices = torch.arange(deg, dtype=torch.int32, device="cuda")     # value == position
-    reps = 40_000
+    reps = 40_000 if k <= 128 else 4_000
     seeds = torch.zeros(reps, dtype=torch.int64, device="cuda")
     p, x = capi.csr_sampling(indptr, indices, seeds, k, False)
     x = x.cpu().numpy().reshape(reps, k)
@@ -143,6 +147,69 @@ def test_without_replacement_is_uniform(capi, deg, k):
     capi.set_sampling_seed(99)
     _, b = capi.csr_sampling(indptr, indices, seeds, k, False)
     assert torch.equal(a, b)
+
+
+def test_large_fanout_subsets_are_uniform_not_only_their_marginals(capi):
+    """Fan-out 33 of a 35-row goes through the shared-memory set in its leave-out form: the two
+    positions left out must be a uniform pair, all C(35,2) = 595 of them equally likely; fan-out 33
+    of a 70-row through its keep form: pairs of kept positions (0,1), (0,2) ... must occur at the
+    rate k(k-1)/(deg(deg-1))."""
+    indptr = torch.tensor([0, 35], dtype=torch.int64, device="cuda")
+    indices = torch.arange(35, dtype=torch.int32, device="cuda")
+    reps = 120_000
+    _, x = capi.csr_sampling(indptr, indices, torch.zeros(reps, dtype=torch.int32, device="cuda"), 33, False)
+    x = x.cpu().numpy().reshape(reps, 33)
+    present = np.zeros((reps, 35), dtype=bool)
+    present[np.arange(reps)[:, None], x] = True
+    assert (present.sum(1) == 33).all()
+    left = np.argwhere(~present)[:, 1].reshape(reps, 2)
+    counts = np.bincount(left[:, 0] * 35 + left[:, 1], minlength=35 * 35)
+    counts = counts[counts > 0]
+    assert counts.size == 595 and stats.chisquare(counts)[1] > 0.01
+    indptr = torch.tensor([0, 70], dtype=torch.int64, device="cuda")
+    indices = torch.arange(70, dtype=torch.int32, device="cuda")
+    _, y = capi.csr_sampling(indptr, indices, torch.zeros(reps, dtype=torch.int32, device="cuda"), 33, False)
+    y = y.cpu().numpy().reshape(reps, 33)
+    present = np.zeros((reps, 70), dtype=bool)
+    present[np.arange(reps)[:, None], y] = True
+    both = (present[:, :8, None] & present[:, None, :8]).sum(0)[np.triu_indices(8, 1)]
+    expect = reps * 33 * 32 / (70 * 69)
+    # 28 pair counts, each binomial: all within 5 standard deviations of the expectation
+    assert (np.abs(both - expect) < 5 * np.sqrt(expect)).all(), (both, expect)
+
+
+def test_large_fanout_on_a_cached_graph_and_fused_relabel(capi):
+    """Fan-outs 40 and 64 over a partly cached power-law graph, hop by hop and through the fused
+    mini-batch (which claims relabel slots inside the sampling kernel for every fan-out)."""
+    rng = np.random.default_rng(21)
+    deg = np.minimum((rng.pareto(1.0, size=4000) * 20).astype(np.int64), 3000)
+    indptr_n = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices_n = np.concatenate([rng.choice(4000, size=d, replace=False) for d in deg]).astype(np.int32)
+    indptr, indices = torch.from_numpy(indptr_n).cuda(), torch.from_numpy(indices_n).cuda()
+    hot_n = np.argsort(-deg)[:800].copy()
+    hot = torch.from_numpy(hot_n).cuda()
+    gp, gi = capi.create_subcsr(indptr, indices, hot)
+    hmap = capi.CUCOStaticHashmap(hot, torch.arange(800, device="cuda"), 0.5)
+    seeds_n = rng.integers(0, 4000, size=600).astype(np.int32)
+    seeds = torch.from_numpy(seeds_n).cuda()
+    for k in (40, 64):
+        p, x = capi.csr_cache_sampling(indptr, indices, gp, gi, hmap, seeds, k, False)
+        oracle.check_sample_bulk(indptr_n, indices_n, seeds_n, k, False, p.cpu().numpy(), x.cpu().numpy(),
+                                 distinct_rows=True)
+        p, x = capi.csr_cache_sampling(indptr, indices, gp, gi, hmap, seeds, k, True)
+        oracle.check_sample_bulk(indptr_n, indices_n, seeds_n, k, True, p.cpu().numpy(), x.cpu().numpy())
+    capi.set_sampling_seed(77)
+    _, hops = capi.sample_minibatch(indptr, indices, seeds, [40, 3], False, gp, gi, hmap)
+    capi.set_sampling_seed(77)
+    cur = seeds
+    for (sp, sx, rel, nxt), k in zip(hops, (40, 3)):
+        p, x = capi.csr_cache_sampling(indptr, indices, gp, gi, hmap, cur, k, False)
+        want_next, (_, want_rel) = capi.tensor_relabel([cur, x])
+        assert torch.equal(sp, p) and torch.equal(sx, x)
+        assert torch.equal(nxt, want_next) and torch.equal(rel, want_rel)
+        wu, (_, wx) = oracle.tensor_relabel([cur.cpu().numpy(), x.cpu().numpy()])
+        assert np.array_equal(nxt.cpu().numpy(), wu) and np.array_equal(rel.cpu().numpy(), wx)
+        cur = nxt
 
 
 def test_pairs_are_uniform_without_replacement(capi):
