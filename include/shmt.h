@@ -233,6 +233,20 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
                     uint64_t rng_offset, void* out_sub_indptr,
                     void* out_sub_indices, int64_t* nnz_host, void* stream);
 
+/* The same hop that also reports, for every sampled neighbour, its edge id: its position in
+ * the full `indices` array, in the dtype of indptr (out_edge_ids, capacity n*k, parallel to
+ * out_sub_indices).  For a cached graph gpu_edge_base[slot] must hold where the cached row starts
+ * in the full array (shmt_subcsr_edge_base).  The reference hands an empty edge-id tensor to its
+ * block builder (python/shmtensor/sampling.py:9-20,137-142); this is what would fill it.      */
+int shmt_sample_hop_eids(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
+                         const void* indices, int indices_dtype,
+                         const void* gpu_indptr, const void* gpu_indices,
+                         const void* gpu_edge_base, const shmt_map* map,
+                         const void* seeds, int seeds_dtype, int64_t n, int64_t k,
+                         int replace, uint64_t rng_seed, uint64_t rng_offset,
+                         void* out_sub_indptr, void* out_sub_indices,
+                         void* out_edge_ids, int64_t* nnz_host, void* stream);
+
 /* A whole multi-hop mini-batch in one call: for hop h (fan-out fanouts[h]) sample the
  * current frontier, relabel [frontier, sampled neighbours] and make the distinct ids the
  * next frontier -- the loop of GPUSamplingDataloader.__next__
@@ -265,6 +279,11 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
 int shmt_subcsr_count(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
                       const void* seeds, int seeds_dtype, int64_t n,
                       void* out_gpu_indptr, int64_t* nnz_host, void* stream);
+/* out_edge_base[i] = indptr[seeds[i]] (indptr dtype): the start of each selected row in the
+ * full edge array, kept beside a cached sub-CSR so that sampled edges of cached rows can be
+ * named by their global edge ids.  No counterpart in the reference.                        */
+int shmt_subcsr_edge_base(const void* indptr, int indptr_dtype, const void* seeds,
+                          int seeds_dtype, int64_t n, void* out_edge_base, void* stream);
 int shmt_subcsr_fill(const void* indptr, int indptr_dtype, const void* indices,
                      int indices_dtype, const void* seeds, int seeds_dtype,
                      int64_t n, const void* gpu_indptr, void* out_gpu_indices,

@@ -579,6 +579,54 @@ def csr_cache_sampling(uva_indptr: torch.Tensor, uva_indices: torch.Tensor,
                    replace, "csr_cache_sampling")
 
 
+def subcsr_edge_base(uva_indptr: torch.Tensor, seeds: torch.Tensor) -> torch.Tensor:
+    """Extension: ``uva_indptr[seeds]`` on the GPU — where each row of a cached sub-CSR (built from
+    the same ``seeds`` by ``create_subcsr``) starts in the full edge array."""
+    _check_cuda(seeds, "seeds")
+    seeds = seeds.contiguous()
+    _check_contig(uva_indptr, "uva_indptr")
+    out = torch.empty(seeds.numel(), dtype=uva_indptr.dtype, device=seeds.device)
+    check(lib.shmt_subcsr_edge_base(_ptr(uva_indptr), _int_code(uva_indptr, "subcsr_edge_base"), _ptr(seeds),
+                                    _int_code(seeds, "subcsr_edge_base"), seeds.numel(), _ptr(out),
+                                    _stream(seeds.device)))
+    return out
+
+
+def csr_sampling_with_eids(indptr, indices, seeds, num_picks: int, replace: bool, gpu_indptr=None,
+                           gpu_indices=None, gpu_edge_base=None, hashmap: "CUCOStaticHashmap | None" = None):
+    """Extension: one hop like ``csr_sampling`` / ``csr_cache_sampling`` that also returns the edge
+    id of every sampled neighbour (its position in ``indices``, dtype of ``indptr``):
+    ``(sub_indptr, sub_indices, sub_eids)``.  The reference passes an empty edge-id tensor to its
+    block builder (python/shmtensor/sampling.py:9-20).  With a cached graph give ``gpu_edge_base``
+    from ``subcsr_edge_base``."""
+    _check_cuda(seeds, "seeds")
+    seeds = seeds.contiguous()
+    dev = seeds.device
+    who = "csr_sampling_with_eids"
+    for t, nm in ((indptr, "indptr"), (indices, "indices")):
+        _check_contig(t, nm)
+    pdt, xdt, sdt = _int_code(indptr, who), _int_code(indices, who), _int_code(seeds, who)
+    if hashmap is not None:
+        for t, nm in ((gpu_indptr, "gpu_indptr"), (gpu_indices, "gpu_indices"), (gpu_edge_base, "gpu_edge_base")):
+            if t is None:
+                raise RuntimeError(f"{who}: a cached graph needs {nm}")
+            _check_cuda(t, nm)
+        if gpu_indptr.dtype != indptr.dtype or gpu_indices.dtype != indices.dtype or gpu_edge_base.dtype != indptr.dtype:
+            raise RuntimeError(f"{who}: the cached CSR must have the dtypes of the host CSR")
+    n, k = seeds.numel(), int(num_picks)
+    sub_indptr = torch.empty(n + 1, dtype=indptr.dtype, device=dev)
+    sub_indices = torch.empty(n * k, dtype=indices.dtype, device=dev)
+    sub_eids = torch.empty(n * k, dtype=indptr.dtype, device=dev)
+    nnz = C.c_int64(0)
+    _rng["calls"] += 1
+    check(lib.shmt_sample_hop_eids(_ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr),
+                                   _ptr(gpu_indices), _ptr(gpu_edge_base),
+                                   hashmap._handle if hashmap is not None else None, _ptr(seeds), sdt, n, k,
+                                   int(bool(replace)), _rng["seed"], _rng["calls"], sub_indptr.data_ptr(),
+                                   _ptr(sub_indices), _ptr(sub_eids), C.byref(nnz), _stream(dev)))
+    return sub_indptr, sub_indices[:nnz.value], sub_eids[:nnz.value]
+
+
 def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.Tensor,
                      fanouts: Sequence[int], replace: bool = False, gpu_indptr=None,
                      gpu_indices=None, hashmap: "CUCOStaticHashmap | None" = None):

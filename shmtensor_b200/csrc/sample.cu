@@ -52,6 +52,10 @@ struct HopJob {
   const int64_t* n_dev;   // if set, the seed count is read here (it was produced on the device)
   int seeds_per_tile;
   uint32_t set_slots;     // fan-out > 32: words of the per-warp set of chosen positions (0: none)
+  // Edge ids (optional): for every sampled neighbour its position in the full `indices` array,
+  // in the dtype of indptr.  A cached row's position there is gpu_edge_base[slot] + offset in row.
+  void* out_eids;
+  const void* gpu_edge_base;
   // Fused relabel insert (multi-hop path): the kernel also claims a relabel-table slot for
   // every seed and every sampled neighbour, at its index in [seeds | neighbours], and
   // records the slot in rel_out -- the work of relabel's first kernel, done while this
@@ -104,6 +108,7 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
   __shared__ int64_t s_deg[kMaxSeedsPerTile];
   __shared__ int64_t s_off[kMaxSeedsPerTile];
   __shared__ uint8_t s_hit[kMaxSeedsPerTile];
+  __shared__ int64_t s_eshift[kMaxSeedsPerTile];  // edge id = position read from + this (edge ids only)
   __shared__ int64_t warp_sums[32];
   __shared__ int64_t s_total;
   __shared__ int64_t s_prefix;
@@ -143,6 +148,8 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
         load_bounds(job.indptr, job.indptr64, row, &b, &e);
     }
     const int64_t deg = e - b;
+    if (job.out_eids && j < S)
+      s_eshift[j] = (valid && slot >= 0) ? load_int(job.gpu_edge_base, job.indptr64, slot) - b : 0;
     if (j < S) {
       s_begin[j] = b;
       s_deg[j] = deg;
@@ -262,6 +269,9 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
       if (src[u]) {
         const int64_t o = prefix + s_off[j] + gl;
         out_all[o] = v[u];
+        if (job.out_eids)
+          store_int(job.out_eids, job.indptr64, o,
+                    (src[u] - static_cast<const IxT*>(s_hit[j] ? job.gpu_indices : job.indices)) + s_eshift[j]);
         if (relabel) {
           const uint32_t pos = relabel_insert_one(job.rel_slots, rel_mask,
                                                   (long long)v[u], (unsigned)(n + o), job.status);
@@ -291,6 +301,7 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
     auto emit = [&](int64_t o, int64_t pos) {
       const IxT val = __ldg(in + pos);
       out_all[o] = val;
+      if (job.out_eids) store_int(job.out_eids, job.indptr64, o, s_begin[j] + pos + s_eshift[j]);
       if (relabel) {
         const uint32_t slot = relabel_insert_one(job.rel_slots, rel_mask, (long long)val,
                                                  (unsigned)(n + o), job.status);
@@ -416,6 +427,15 @@ __global__ void subcsr_degree_kernel(const void* __restrict__ indptr, int indptr
   }
 }
 
+// out[i] = indptr[seeds[i]]: where each selected row starts in the full edge array.
+__global__ void subcsr_edge_base_kernel(const void* __restrict__ indptr, int indptr64,
+                                        const void* __restrict__ seeds, int seeds64, int64_t n,
+                                        void* __restrict__ out) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    store_int(out, indptr64, i, load_int(indptr, indptr64, load_int(seeds, seeds64, i)));
+}
+
 template <typename IxT>
 __global__ void __launch_bounds__(256)
 subcsr_fill_kernel(const void* __restrict__ indptr, int indptr64, const IxT* __restrict__ indices,
@@ -538,11 +558,12 @@ int shmt_ctx_reserve_minibatch(shmt_ctx* ctx, int64_t n_seeds, const int64_t* fa
   return relabel_table(ctx, plan.cap[n_hops], &t, static_cast<cudaStream_t>(stream));
 }
 
-int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
-                    int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
-                    const shmt_map* map, const void* seeds, int seeds_dtype, int64_t n, int64_t k,
-                    int replace, uint64_t rng_seed, uint64_t rng_offset, void* out_sub_indptr,
-                    void* out_sub_indices, int64_t* nnz_host, void* stream) {
+static int sample_hop_impl(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                           int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
+                           const shmt_map* map, const void* seeds, int seeds_dtype, int64_t n, int64_t k,
+                           int replace, uint64_t rng_seed, uint64_t rng_offset, void* out_sub_indptr,
+                           void* out_sub_indices, int64_t* nnz_host, void* stream, void* out_eids,
+                           const void* gpu_edge_base) {
   SHMT_REQUIRE(ctx != nullptr, "shmt_sample_hop: ctx is null");
   SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(indices_dtype) &&
                    valid_int_dtype(seeds_dtype),
@@ -583,6 +604,8 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const v
   job.off_hi = (uint32_t)(rng_offset >> 32);
   job.sub_indptr = out_sub_indptr;
   job.sub_indices = out_sub_indices;
+  job.out_eids = out_eids;
+  job.gpu_edge_base = gpu_edge_base;
   job.seeds_per_tile = pick_seeds_per_tile(n, k);
   const int64_t n_tiles = (n + job.seeds_per_tile - 1) / job.seeds_per_tile;
   if (int rc = ctx_reserve(ctx, tile_state_bytes(n_tiles))) return rc;
@@ -603,6 +626,30 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const v
     *nnz_host = ctx->h_words[W_RESULT];
   }
   return SHMT_OK;
+}
+
+int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                    int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
+                    const shmt_map* map, const void* seeds, int seeds_dtype, int64_t n, int64_t k,
+                    int replace, uint64_t rng_seed, uint64_t rng_offset, void* out_sub_indptr,
+                    void* out_sub_indices, int64_t* nnz_host, void* stream) {
+  return sample_hop_impl(ctx, indptr, indptr_dtype, indices, indices_dtype, gpu_indptr, gpu_indices, map,
+                         seeds, seeds_dtype, n, k, replace, rng_seed, rng_offset, out_sub_indptr,
+                         out_sub_indices, nnz_host, stream, nullptr, nullptr);
+}
+
+int shmt_sample_hop_eids(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                         int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
+                         const void* gpu_edge_base, const shmt_map* map, const void* seeds,
+                         int seeds_dtype, int64_t n, int64_t k, int replace, uint64_t rng_seed,
+                         uint64_t rng_offset, void* out_sub_indptr, void* out_sub_indices,
+                         void* out_edge_ids, int64_t* nnz_host, void* stream) {
+  SHMT_REQUIRE(n == 0 || k == 0 || out_edge_ids != nullptr, "shmt_sample_hop_eids: out_edge_ids is null");
+  SHMT_REQUIRE(map == nullptr || gpu_edge_base != nullptr,
+               "shmt_sample_hop_eids: a cached graph needs gpu_edge_base (shmt_subcsr_edge_base)");
+  return sample_hop_impl(ctx, indptr, indptr_dtype, indices, indices_dtype, gpu_indptr, gpu_indices, map,
+                         seeds, seeds_dtype, n, k, replace, rng_seed, rng_offset, out_sub_indptr,
+                         out_sub_indices, nnz_host, stream, out_edge_ids, gpu_edge_base);
 }
 
 // Multi-hop mini-batch: every hop's sampling kernel and relabel kernels are queued back
@@ -751,6 +798,21 @@ int shmt_subcsr_count(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const
     if (int rc = ctx_fetch_words(ctx, s, "shmt_subcsr_count")) return rc;
     *nnz_host = indptr_dtype == SHMT_I64 ? last : (int64_t)(int32_t)last;
   }
+  return SHMT_OK;
+}
+
+int shmt_subcsr_edge_base(const void* indptr, int indptr_dtype, const void* seeds, int seeds_dtype,
+                          int64_t n, void* out_edge_base, void* stream) {
+  SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(seeds_dtype),
+               "shmt_subcsr_edge_base: ID can only be int32 or int64");
+  SHMT_REQUIRE(n >= 0, "shmt_subcsr_edge_base: negative count");
+  if (n == 0) return SHMT_OK;
+  SHMT_REQUIRE(indptr && seeds && out_edge_base, "shmt_subcsr_edge_base: null argument");
+  int64_t blocks = (n + 255) / 256;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  subcsr_edge_base_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      indptr, indptr_dtype == SHMT_I64, seeds, seeds_dtype == SHMT_I64, n, out_edge_base);
+  SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;
 }
 

@@ -251,6 +251,44 @@ def test_high_degree_rows_and_power_law_graph(capi):
                             positional=True)
 
 
+@pytest.mark.parametrize("ptr_dt,idx_dt", [(torch.int64, torch.int32), (torch.int32, torch.int32),
+                                           (torch.int64, torch.int64)])
+def test_edge_ids_name_the_sampled_edges(capi, ptr_dt, idx_dt):
+    """Every edge id is the position of its neighbour in the full edge array and lies in the
+    row of its seed, for host rows and for cached rows, and asking for edge ids changes nothing
+    else about the hop."""
+    rng = np.random.default_rng(17)
+    deg = np.minimum((rng.pareto(1.2, size=6000) * 6).astype(np.int64), 900)
+    indptr_n = np.concatenate([[0], np.cumsum(deg)]).astype(DT[ptr_dt])
+    indices_n = rng.integers(0, 6000, size=int(indptr_n[-1])).astype(DT[idx_dt])
+    indptr, indices = torch.from_numpy(indptr_n).cuda(), torch.from_numpy(indices_n).cuda()
+    hot = torch.from_numpy(np.argsort(-deg)[:1500].copy()).cuda()
+    gp, gi = capi.create_subcsr(indptr, indices, hot)
+    base = capi.subcsr_edge_base(indptr, hot)
+    assert torch.equal(base, indptr[hot])
+    hmap = capi.CUCOStaticHashmap(hot, torch.arange(1500, device="cuda"), 0.5)
+    seeds = torch.from_numpy(rng.integers(0, 6000, size=3000)).cuda()
+    for k, replace in ((4, False), (15, False), (40, False), (6, True), (50, True)):
+        for cached in (False, True):
+            extra = dict(gpu_indptr=gp, gpu_indices=gi, gpu_edge_base=base, hashmap=hmap) if cached else {}
+            capi.set_sampling_seed(3)
+            p, x, e = capi.csr_sampling_with_eids(indptr, indices, seeds, k, replace, **extra)
+            capi.set_sampling_seed(3)
+            p0, x0 = (capi.csr_cache_sampling(indptr, indices, gp, gi, hmap, seeds, k, replace) if cached
+                      else capi.csr_sampling(indptr, indices, seeds, k, replace))
+            assert torch.equal(p, p0) and torch.equal(x, x0)
+            assert e.dtype == ptr_dt and e.numel() == x.numel()
+            assert torch.equal(indices[e.long()], x)
+            owner = torch.repeat_interleave(seeds, (p[1:] - p[:-1]).long())
+            assert bool(((e >= indptr[owner]) & (e < indptr[owner + 1])).all())
+            if not replace:   # distinct positions: no edge twice for one seed occurrence
+                occ = torch.repeat_interleave(torch.arange(seeds.numel(), device="cuda"), (p[1:] - p[:-1]).long())
+                key = occ * (int(indptr_n[-1]) + 1) + e.long()
+                assert torch.unique(key).numel() == key.numel()
+    with pytest.raises(RuntimeError, match="needs gpu_edge_base"):
+        capi.csr_sampling_with_eids(indptr, indices, seeds, 4, False, gpu_indptr=gp, gpu_indices=gi, hashmap=hmap)
+
+
 def test_sampling_errors(capi):
     indptr = torch.tensor([0, 2], device="cuda")
     indices = torch.tensor([0, 1], device="cuda")
