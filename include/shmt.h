@@ -247,6 +247,23 @@ int shmt_sample_hop_eids(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
                          void* out_sub_indptr, void* out_sub_indices,
                          void* out_edge_ids, int64_t* nnz_host, void* stream);
 
+/* Weighted hop: neighbours are picked with probabilities proportional to `weights` (one positive
+ * float per edge, parallel to `indices`; gpu_weights parallel to gpu_indices for a cached graph;
+ * a weight that is not positive counts as the smallest positive one).  Without replacement
+ * (fan-out <= 32) by exponential keys -log(u)/w of which the k smallest win (Efraimidis and
+ * Spirakis), i.e. sequential weighted draws without replacement; with replacement k independent
+ * draws.  Rows with deg <= k are copied whole, as in the uniform hop.  out_edge_ids may be NULL.
+ * Not in the reference, whose sampler is uniform only (src/cache_graph_sampling.cu:91-177).    */
+int shmt_sample_hop_weighted(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
+                             const void* indices, int indices_dtype, const float* weights,
+                             const void* gpu_indptr, const void* gpu_indices,
+                             const float* gpu_weights, const void* gpu_edge_base,
+                             const shmt_map* map, const void* seeds, int seeds_dtype,
+                             int64_t n, int64_t k, int replace, uint64_t rng_seed,
+                             uint64_t rng_offset, void* out_sub_indptr,
+                             void* out_sub_indices, void* out_edge_ids, int64_t* nnz_host,
+                             void* stream);
+
 /* A whole multi-hop mini-batch in one call: for hop h (fan-out fanouts[h]) sample the
  * current frontier, relabel [frontier, sampled neighbours] and make the distinct ids the
  * next frontier -- the loop of GPUSamplingDataloader.__next__

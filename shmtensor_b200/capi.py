@@ -627,6 +627,50 @@ def csr_sampling_with_eids(indptr, indices, seeds, num_picks: int, replace: bool
     return sub_indptr, sub_indices[:nnz.value], sub_eids[:nnz.value]
 
 
+def csr_weighted_sampling(indptr, indices, weights, seeds, num_picks: int, replace: bool, gpu_indptr=None,
+                          gpu_indices=None, gpu_weights=None, hashmap: "CUCOStaticHashmap | None" = None,
+                          gpu_edge_base=None, return_eids: bool = False):
+    """Extension: one hop in which neighbours are picked with probabilities proportional to
+    ``weights`` (float32, one per edge, parallel to ``indices``).  Without replacement (fan-out at
+    most 32) this is sequential weighted sampling without replacement; with replacement the picks
+    are independent.  Rows with ``deg <= num_picks`` are copied whole.  For a cached graph pass
+    ``gpu_weights`` — ``create_subcsr(indptr, weights.view(torch.int32), cached_rows)[1]
+    .view(torch.float32)`` makes them.  Returns ``(sub_indptr, sub_indices)`` or, with
+    ``return_eids``, ``(sub_indptr, sub_indices, sub_eids)``.  The reference samples uniformly only."""
+    _check_cuda(seeds, "seeds")
+    seeds = seeds.contiguous()
+    dev = seeds.device
+    who = "csr_weighted_sampling"
+    for t, nm in ((indptr, "indptr"), (indices, "indices"), (weights, "weights")):
+        _check_contig(t, nm)
+    if weights.dtype != torch.float32 or weights.numel() != indices.numel():
+        raise RuntimeError(f"{who}: weights must be float32, one per edge")
+    pdt, xdt, sdt = _int_code(indptr, who), _int_code(indices, who), _int_code(seeds, who)
+    if hashmap is not None:
+        for t, nm in ((gpu_indptr, "gpu_indptr"), (gpu_indices, "gpu_indices"), (gpu_weights, "gpu_weights")):
+            if t is None:
+                raise RuntimeError(f"{who}: a cached graph needs {nm}")
+            _check_cuda(t, nm)
+        if gpu_weights.dtype != torch.float32 or gpu_weights.numel() != gpu_indices.numel():
+            raise RuntimeError(f"{who}: gpu_weights must be float32, one per cached edge")
+        if return_eids and gpu_edge_base is None:
+            raise RuntimeError(f"{who}: edge ids of a cached graph need gpu_edge_base")
+    n, k = seeds.numel(), int(num_picks)
+    sub_indptr = torch.empty(n + 1, dtype=indptr.dtype, device=dev)
+    sub_indices = torch.empty(n * k, dtype=indices.dtype, device=dev)
+    sub_eids = torch.empty(n * k, dtype=indptr.dtype, device=dev) if return_eids else None
+    nnz = C.c_int64(0)
+    _rng["calls"] += 1
+    check(lib.shmt_sample_hop_weighted(_ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(weights),
+                                       _ptr(gpu_indptr), _ptr(gpu_indices), _ptr(gpu_weights), _ptr(gpu_edge_base),
+                                       hashmap._handle if hashmap is not None else None, _ptr(seeds), sdt, n, k,
+                                       int(bool(replace)), _rng["seed"], _rng["calls"], sub_indptr.data_ptr(),
+                                       _ptr(sub_indices), _ptr(sub_eids), C.byref(nnz), _stream(dev)))
+    if return_eids:
+        return sub_indptr, sub_indices[:nnz.value], sub_eids[:nnz.value]
+    return sub_indptr, sub_indices[:nnz.value]
+
+
 def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.Tensor,
                      fanouts: Sequence[int], replace: bool = False, gpu_indptr=None,
                      gpu_indices=None, hashmap: "CUCOStaticHashmap | None" = None):

@@ -56,6 +56,10 @@ struct HopJob {
   // in the dtype of indptr.  A cached row's position there is gpu_edge_base[slot] + offset in row.
   void* out_eids;
   const void* gpu_edge_base;
+  // Weighted sampling (optional): one positive float per edge, parallel to `indices` (and to
+  // gpu_indices for the cached rows).  Always sampled by one warp per seed.
+  const float* weights;
+  const float* gpu_weights;
   // Fused relabel insert (multi-hop path): the kernel also claims a relabel-table slot for
   // every seed and every sampled neighbour, at its index in [seeds | neighbours], and
   // records the slot in rel_out -- the work of relabel's first kernel, done while this
@@ -175,7 +179,7 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
   // to back.
   const IxT* src[U];
   IxT v[U];
-  if (k <= G) {
+  if (k <= G && !job.weights) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int j = u * kGroups + group;
@@ -262,7 +266,7 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
   }
 
   // ---- 4. output
-  if (k <= G) {
+  if (k <= G && !job.weights) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int j = u * kGroups + group;
@@ -308,6 +312,84 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
         store_int(job.rel_out, sizeof(IxT) == 8, n + o, (int64_t)slot);
       }
     };
+    if (job.weights && deg > 0 && (job.replace || deg > k)) {
+      const float* w = (s_hit[j] ? job.gpu_weights : job.weights) + s_begin[j];
+      const float tiny = 1.17549435e-38f;  // a weight that is not positive counts as the smallest one
+      if (!job.replace) {
+        // Efraimidis-Spirakis: every edge gets the key -log(u) / w (an exponential clock of rate
+        // w) and the k smallest keys win, which is sampling without replacement with
+        // probabilities proportional to the weights.  Lanes 0..k-1 hold the k smallest keys seen
+        // so far, ascending; a key below the largest of them is inserted by one shuffle step.
+        float best = __int_as_float(0x7f800000);
+        int64_t bpos = -1;
+        float thr = best;
+        for (int64_t p0 = 0; p0 < deg; p0 += 32) {
+          const int64_t pos = p0 + gl;
+          float key = __int_as_float(0x7f800000);
+          if (pos < deg) {
+            const uint4 r = rng(seed_idx, (uint32_t)pos, job.off_lo, job.off_hi);
+            const float u = ((float)(r.x >> 8) + 1.0f) * (1.0f / 16777216.0f);  // (0, 1]
+            key = -__logf(u) / fmaxf(__ldg(w + pos), tiny);
+          }
+          unsigned cand = __ballot_sync(full, key < thr);
+          while (cand) {
+            const int from = __ffs(cand) - 1;
+            cand &= cand - 1;
+            const float ck = __shfl_sync(full, key, from);
+            const int64_t cp = __shfl_sync(full, pos, from);
+            if (ck < thr) {  // the bound may have dropped since the vote; same on every lane
+              const float left_k = __shfl_up_sync(full, best, 1);
+              const int64_t left_p = __shfl_up_sync(full, bpos, 1);
+              if ((int64_t)gl < k && ck < best) {
+                if (gl == 0 || left_k <= ck) {
+                  best = ck;
+                  bpos = cp;
+                } else {
+                  best = left_k;
+                  bpos = left_p;
+                }
+              }
+              thr = __shfl_sync(full, best, (int)k - 1);
+            }
+          }
+        }
+        if ((int64_t)gl < k) emit(out_at + gl, bpos);
+      } else {
+        // k independent draws proportional to the weights: the row's total, then for 32 draws at
+        // a time a second walk that finds where each draw's share of the total falls
+        double sum = 0.0;
+        for (int64_t p = gl; p < deg; p += 32) sum += (double)fmaxf(__ldg(w + p), tiny);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(full, sum, o);
+        for (int64_t d0 = 0; d0 < k; d0 += 32) {
+          const bool mine = d0 + gl < k;
+          const uint4 r = rng(seed_idx, (uint32_t)(d0 + gl), job.off_lo, job.off_hi);
+          const double target = ((double)r.x + 0.5) * (1.0 / 4294967296.0) * sum;
+          int64_t found = -1;
+          double base = 0.0;
+          for (int64_t p0 = 0; p0 < deg; p0 += 32) {
+            const int64_t pos = p0 + gl;
+            double inc = pos < deg ? (double)fmaxf(__ldg(w + pos), tiny) : 0.0;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+              const double up = __shfl_up_sync(full, inc, o);
+              if (gl >= (unsigned)o) inc += up;
+            }
+            const double chunk_end = base + __shfl_sync(full, inc, 31);
+            const bool here = mine && found < 0 && target < chunk_end;
+            if (__any_sync(full, here)) {
+              for (int q = 0; q < 32; ++q) {
+                const double upto = base + __shfl_sync(full, inc, q);
+                if (here && found < 0 && target < upto && p0 + q < deg) found = p0 + q;
+              }
+            }
+            base = chunk_end;
+          }
+          if (mine) emit(out_at + d0 + gl, found >= 0 ? found : deg - 1);
+        }
+      }
+      continue;
+    }
     if (job.replace) {
       if (deg > 0)
         for (int64_t p = gl; p < k; p += 32)
@@ -492,8 +574,10 @@ template <typename IxT>
 static cudaError_t launch_hop(HopJob job, int64_t n_tiles, cudaStream_t s, bool pdl = false) {
   const unsigned grid = (unsigned)n_tiles;
   job.set_slots = set_slots_for(job.k);
-  if (job.k <= 8) return launch_kernel(pdl, sample_hop_kernel<IxT, 8>, grid, kHopThreads, 0, s, job);
-  if (job.k <= 16) return launch_kernel(pdl, sample_hop_kernel<IxT, 16>, grid, kHopThreads, 0, s, job);
+  if (!job.weights) {
+    if (job.k <= 8) return launch_kernel(pdl, sample_hop_kernel<IxT, 8>, grid, kHopThreads, 0, s, job);
+    if (job.k <= 16) return launch_kernel(pdl, sample_hop_kernel<IxT, 16>, grid, kHopThreads, 0, s, job);
+  }
   const size_t smem = (size_t)job.set_slots * sizeof(uint32_t) * (kHopThreads / 32);
   if (smem > 0) {
     static bool configured[64] = {false};
@@ -563,7 +647,8 @@ static int sample_hop_impl(shmt_ctx* ctx, const void* indptr, int indptr_dtype, 
                            const shmt_map* map, const void* seeds, int seeds_dtype, int64_t n, int64_t k,
                            int replace, uint64_t rng_seed, uint64_t rng_offset, void* out_sub_indptr,
                            void* out_sub_indices, int64_t* nnz_host, void* stream, void* out_eids,
-                           const void* gpu_edge_base) {
+                           const void* gpu_edge_base, const float* weights = nullptr,
+                           const float* gpu_weights = nullptr) {
   SHMT_REQUIRE(ctx != nullptr, "shmt_sample_hop: ctx is null");
   SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(indices_dtype) &&
                    valid_int_dtype(seeds_dtype),
@@ -606,7 +691,9 @@ static int sample_hop_impl(shmt_ctx* ctx, const void* indptr, int indptr_dtype, 
   job.sub_indices = out_sub_indices;
   job.out_eids = out_eids;
   job.gpu_edge_base = gpu_edge_base;
-  job.seeds_per_tile = pick_seeds_per_tile(n, k);
+  job.weights = weights;
+  job.gpu_weights = gpu_weights;
+  job.seeds_per_tile = pick_seeds_per_tile(n, weights ? 33 : k);  // weighted: the warp-per-seed layout
   const int64_t n_tiles = (n + job.seeds_per_tile - 1) / job.seeds_per_tile;
   if (int rc = ctx_reserve(ctx, tile_state_bytes(n_tiles))) return rc;
   job.st = carve_tile_states(ctx->region(), n_tiles);
@@ -636,6 +723,27 @@ int shmt_sample_hop(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const v
   return sample_hop_impl(ctx, indptr, indptr_dtype, indices, indices_dtype, gpu_indptr, gpu_indices, map,
                          seeds, seeds_dtype, n, k, replace, rng_seed, rng_offset, out_sub_indptr,
                          out_sub_indices, nnz_host, stream, nullptr, nullptr);
+}
+
+int shmt_sample_hop_weighted(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                             int indices_dtype, const float* weights, const void* gpu_indptr,
+                             const void* gpu_indices, const float* gpu_weights,
+                             const void* gpu_edge_base, const shmt_map* map, const void* seeds,
+                             int seeds_dtype, int64_t n, int64_t k, int replace, uint64_t rng_seed,
+                             uint64_t rng_offset, void* out_sub_indptr, void* out_sub_indices,
+                             void* out_edge_ids, int64_t* nnz_host, void* stream) {
+  SHMT_REQUIRE(weights != nullptr || n == 0 || k == 0, "shmt_sample_hop_weighted: weights are null");
+  SHMT_REQUIRE(replace || k <= 32,
+               "shmt_sample_hop_weighted: without replacement the fan-out is limited to 32 (got %lld)",
+               (long long)k);
+  SHMT_REQUIRE(map == nullptr || gpu_weights != nullptr,
+               "shmt_sample_hop_weighted: a cached graph needs gpu_weights");
+  SHMT_REQUIRE(map == nullptr || out_edge_ids == nullptr || gpu_edge_base != nullptr,
+               "shmt_sample_hop_weighted: edge ids of a cached graph need gpu_edge_base");
+  return sample_hop_impl(ctx, indptr, indptr_dtype, indices, indices_dtype, gpu_indptr, gpu_indices, map,
+                         seeds, seeds_dtype, n, k, replace, rng_seed, rng_offset, out_sub_indptr,
+                         out_sub_indices, nnz_host, stream, out_edge_ids, gpu_edge_base, weights,
+                         gpu_weights);
 }
 
 int shmt_sample_hop_eids(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,

@@ -139,7 +139,10 @@ scan_kernel(T* __restrict__ data, int64_t n, int exclusive, int vec_ok, TileStat
 // registers, so load latency overlaps the rest.  (3) Four CTAs form a cluster, add their sums
 // up through distributed shared memory and look back once for a 256 KB super-tile: a quarter of
 // the descriptors per microsecond, so the nearest known prefix is one round trip away, not three.
-constexpr int kScanCluster = 4;
+#ifndef SHMT_SCAN_CLUSTER
+#define SHMT_SCAN_CLUSTER 4
+#endif
+constexpr int kScanCluster = SHMT_SCAN_CLUSTER;
 constexpr int64_t kScanSuperBytes = (int64_t)kScanCluster * kScanTileBytes;
 constexpr int64_t kScanClusterMinBytes = (int64_t)32 << 20;  // below this the ticketed kernel spreads better
 
