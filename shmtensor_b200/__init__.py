@@ -10,7 +10,7 @@ library before anything tries to open it.
 import importlib
 
 __all__ = ["capi", "ShmTensor", "DiskTensor", "GPUSamplingDataloader", "PartitionedFeatureCache",
-           "install_dropin"]
+           "GraphCache", "install_dropin"]
 
 _LAZY = {
     "capi": ("shmtensor_b200.capi", None),
@@ -18,6 +18,7 @@ _LAZY = {
     "DiskTensor": ("shmtensor_b200.host_tensors", "DiskTensor"),
     "GPUSamplingDataloader": ("shmtensor_b200.dataloader", "GPUSamplingDataloader"),
     "PartitionedFeatureCache": ("shmtensor_b200.partition", "PartitionedFeatureCache"),
+    "GraphCache": ("shmtensor_b200.graph_cache", "GraphCache"),
 }
 
 

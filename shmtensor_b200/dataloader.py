@@ -133,10 +133,12 @@ class GPUSamplingDataloader:
         return seeds, output_nodes, blocks
 
     # ------------------------------------------------------------------ cache management
-    def create_cache(self, cache_capacity, hotness):
+    def create_cache(self, cache_capacity, hotness, replaceable=False):
         """Keep the hottest rows' adjacency on the GPU within ``cache_capacity`` bytes
         (python/shmtensor/sampling.py:149-189; same size model: adjacency bytes + one indptr
-        entry + 1.25*2*4 bytes of map per row, map load factor 0.8, int32 keys/values)."""
+        entry + 1.25*2*4 bytes of map per row, map load factor 0.8, int32 keys/values).
+        ``replaceable=True`` (not in the reference) builds a ``GraphCache`` instead of a compact
+        sub-CSR, so that ``replace_cache`` can later swap rows without a rebuild."""
         if cache_capacity <= 0:
             return
         full_size = self.indptr.nbytes + self.indices.nbytes
@@ -160,15 +162,34 @@ class GPUSamplingDataloader:
         candidates = candidates[:n_rows].cuda()
         if candidates.numel() == 0:
             return
+        if replaceable:
+            from .graph_cache import GraphCache
+            self.graph_cache = GraphCache(self.indptr, self.indices, candidates)
+            self.gpu_indptr, self.gpu_indices = self.graph_cache.gpu_indptr, self.graph_cache.gpu_indices
+            self.hashmap = self.graph_cache.hashmap
+            self.has_cache = True
+            return
         self.gpu_indptr, self.gpu_indices = capi.create_subcsr(self.indptr, self.indices,
                                                                candidates)
         slots = torch.arange(candidates.numel(), device='cuda', dtype=torch.int32)
         self.hashmap = capi.CUCOStaticHashmap(candidates.int(), slots, 0.8)
         self.has_cache = True
 
+    def replace_cache(self, evict_nodes, admit_nodes):
+        """Swap cached rows in place (needs ``create_cache(..., replaceable=True)``): the rows of
+        ``evict_nodes`` leave the GPU, those of ``admit_nodes`` are copied into the freed space.
+        Returns how many nodes were admitted.  Call between mini-batches."""
+        gc = getattr(self, "graph_cache", None)
+        if gc is None or not self.has_cache:
+            raise RuntimeError("replace_cache: the cache was not created with replaceable=True")
+        n = gc.replace(evict_nodes, admit_nodes)
+        self.gpu_indptr, self.gpu_indices = gc.gpu_indptr, gc.gpu_indices
+        return n
+
     def clear_cache(self):
         self.has_cache = False
         self.gpu_indptr = self.gpu_indices = self.hashmap = None
+        self.graph_cache = None
 
     def presampling(self):
         """One uncached epoch that counts how often each node is a seed (sampling hotness)

@@ -117,4 +117,4 @@ def test_heavier_edges_win_more_often_on_long_rows(capi):
     x = x.cpu().numpy().reshape(reps, 10)
     assert (np.sort(x, 1)[:, 1:] != np.sort(x, 1)[:, :-1]).all()
     share = (x < 20).mean()
-    assert 0.30 < share < 0.50, share
+    assert 0.44 < share < 0.50, share   # sequential draws on the CPU give 0.471
