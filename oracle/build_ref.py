@@ -1,16 +1,21 @@
 """Compile the reference's own sources into ``oracle/_ref/ShmTensorLib.so``.
 
-TEST AND BENCH INFRASTRUCTURE.  The sources are compiled where they lie (the read-only reference
-checkout named by ``REFERENCE`` below, unmodified; nothing is copied into this repository) with nvcc for sm_100a, against this
+TEST AND BENCH INFRASTRUCTURE.  The sources are compiled where they lie (the reference checkout
+named by the environment variable ``SHMT_REFERENCE_DIR`` or the first command-line argument,
+unmodified; nothing is copied into this repository) with nvcc for sm_100a, against this
 image's torch headers and ``oracle/ref_shim`` — a stand-in for the one header the reference's
 build downloads (cuCollections, see ``oracle/ref_shim/cuco/static_map.cuh``).  The reference's
 own build system (CMake + CPM download) is not run.  Output goes only to ``oracle/_ref/``
 (git-ignored; it travels to the GPU box with the repository snapshot).
 
-    python oracle/build_ref.py        # about 5 minutes on 8 cores (torch headers)
+    SHMT_REFERENCE_DIR=<checkout of gpzlx1/ShmTensor> python oracle/build_ref.py
+    python oracle/build_ref.py <checkout> [--force]      # about 5 minutes on 8 cores (torch headers)
+
+Without a checkout an earlier build in ``oracle/_ref/`` is used as it is.
 """
 from __future__ import annotations
 
+import os
 import subprocess
 import sys
 import sysconfig
@@ -18,7 +23,18 @@ from concurrent.futures import ThreadPoolExecutor
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REFERENCE = Path("/root/reference")
+
+
+def reference_dir() -> Path | None:
+    """The reference checkout to compile from: SHMT_REFERENCE_DIR, else a sibling directory named
+    ``reference`` next to this repository; None if neither exists."""
+    named = os.environ.get("SHMT_REFERENCE_DIR")
+    for cand in ([Path(named)] if named else []) + [HERE.parent.parent / "reference"]:
+        if (cand / "src" / "pybind.cc").exists():
+            return cand
+    return None
+
+
 OUT_DIR = HERE / "_ref"
 OUT = OUT_DIR / "ShmTensorLib.so"
 SOURCES = ["src/pybind.cc", "src/cuco_hashmap.cu", "src/cache_feature_fetch.cu",
@@ -26,8 +42,9 @@ SOURCES = ["src/pybind.cc", "src/cuco_hashmap.cu", "src/cache_feature_fetch.cu",
            "src/thrust_scan.cu", "src/mmap_tensor.cc", "src/cnpy.cc"]
 
 
-def build_reference(force: bool = False) -> Path | None:
-    if not REFERENCE.exists():
+def build_reference(force: bool = False, reference: Path | None = None) -> Path | None:
+    REFERENCE = Path(reference) if reference else reference_dir()
+    if REFERENCE is None:
         return OUT if OUT.exists() else None
     if OUT.exists() and not force:
         return OUT
@@ -84,4 +101,5 @@ def load_reference():
 
 
 if __name__ == "__main__":
-    print(build_reference(force="--force" in sys.argv))
+    paths = [a for a in sys.argv[1:] if not a.startswith("--")]
+    print(build_reference(force="--force" in sys.argv, reference=Path(paths[0]) if paths else None))

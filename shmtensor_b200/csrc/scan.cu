@@ -259,7 +259,11 @@ scan_cluster_kernel(T* __restrict__ data, int64_t n_super, int exclusive, TileSt
       // this CTA's sum to every CTA of the cluster (its own copy included)
       if (lane < kScanCluster) st_cluster_u64(&s_sum[it & 1][rank], lane, (unsigned long long)total);
     }
+#ifdef SHMT_DBG_NO_CLUSTER_BARRIER
+    __syncthreads();
+#else
     cluster_sync_all();  // sums delivered; also the CTA-wide barrier behind `partial`
+#endif
     if (warp == 0) {
       unsigned long long before = 0, whole = 0;
 #pragma unroll
@@ -268,9 +272,13 @@ scan_cluster_kernel(T* __restrict__ data, int64_t n_super, int exclusive, TileSt
         whole += t;
         if ((unsigned)r < rank) before += t;
       }
+#ifdef SHMT_DBG_NO_LOOKBACK
+      const int64_t p = 0;
+#else
       const int64_t p = rank == 0
           ? lookback_exclusive_prefix_shared<true>(st, (int)super, (int64_t)whole, words + W_STATUS)
           : lookback_exclusive_prefix_shared<false>(st, (int)super, (int64_t)whole, words + W_STATUS);
+#endif
       if (lane == 0) s_prefix = p + (int64_t)before;
     }
     __syncthreads();
@@ -283,7 +291,11 @@ scan_cluster_kernel(T* __restrict__ data, int64_t n_super, int exclusive, TileSt
 #pragma unroll
       for (int j = 0; j < VEC; ++j)
         p.a[j] = ahead + (exclusive ? (j ? v[k][j - 1] : U(0)) : v[k][j]);
+#ifdef SHMT_DBG_NO_STORE
+      if (p.a[0] == (U)0x12345678) reinterpret_cast<uint4*>(out)[k * kScanThreads + tid] = p.q;
+#else
       reinterpret_cast<uint4*>(out)[k * kScanThreads + tid] = p.q;
+#endif
     }
   }
 }
