@@ -113,53 +113,61 @@ __device__ __forceinline__ int64_t lookback_exclusive_prefix(const TileStates& s
   return prefix;
 }
 
-// The same look-back for a tile computed by several CTAs at once (a thread-block cluster that
-// has already added its CTAs' sums up): every CTA of the cluster calls it with the cluster's
-// aggregate and gets the same prefix, but only the one with PUBLISH writes the descriptor.
-// A waiting lane also gives up as soon as another tile has recorded a timeout, so a kernel
+// Look-back for a tile whose aggregate has ALREADY been published (state 1, or state 2 for tile
+// 0) by an earlier step of the same kernel: returns the exclusive prefix and, if `publish`,
+// replaces the descriptor by the inclusive prefix.  Several CTAs that computed one tile together
+// (a thread-block cluster) may all call it and get the same prefix; one of them publishes.
+// WINDOWS * 32 predecessors are read per step, all loads in flight together: when the sums are
+// known to be out already, reading further back costs nothing in waiting and saves round trips
+// through L2.  A waiting lane gives up as soon as another tile has recorded a timeout, so a kernel
 // whose tile order was broken ends after one bounded wait instead of one per tile.
-template <bool PUBLISH>
-__device__ __forceinline__ int64_t lookback_exclusive_prefix_shared(const TileStates& st, int tile,
-                                                                    int64_t aggregate,
-                                                                    int64_t* status_word,
-                                                                    int spin_limit = kLookbackSpinLimit) {
+template <int WINDOWS>
+__device__ __forceinline__ int64_t lookback_published(const TileStates& st, int tile, int64_t aggregate,
+                                                      bool publish, int64_t* status_word,
+                                                      int spin_limit = kLookbackSpinLimit) {
   const unsigned lane = threadIdx.x & 31;
-  if (tile == 0) {
-    if (PUBLISH && lane == 0) st_desc(st.d, aggregate, kTileInclusive);
-    return 0;
-  }
-  if (PUBLISH && lane == 0) st_desc(st.d + tile, aggregate, kTileAggregate);
+  if (tile == 0) return 0;
   int64_t prefix = 0;
   int base = tile - 1;
-  while (true) {
-    const int t = base - (int)lane;
-    unsigned long long f = kTileInclusive;
-    long long v = 0;
-    if (t >= 0) {
+  bool done = false;
+  while (!done) {
+    unsigned long long f[WINDOWS];
+    long long v[WINDOWS];
+#pragma unroll
+    for (int j = 0; j < WINDOWS; ++j) {
+      const int t = base - 32 * j - (int)lane;
+      f[j] = kTileInclusive;  // before the first tile: a known prefix of zero
+      v[j] = 0;
+      if (t >= 0) ld_desc(st.d + t, &v[j], &f[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < WINDOWS; ++j) {
+      if (done) break;
+      const int t = base - 32 * j - (int)lane;
       int spins = 0;
-      ld_desc(st.d + t, &v, &f);
-      while (f == 0ULL && spins < spin_limit) {
+      while (f[j] == 0ULL && spins < spin_limit) {
         __nanosleep(20);
-        ld_desc(st.d + t, &v, &f);
+        ld_desc(st.d + t, &v[j], &f[j]);
         if ((++spins & 1023) == 0 && ld_relaxed64(status_word) != DEV_OK) spins = spin_limit;
       }
-      if (f == 0ULL) {
+      if (f[j] == 0ULL) {
         atomicMax(reinterpret_cast<unsigned long long*>(status_word),
                   (unsigned long long)DEV_TIMEOUT);
-        f = kTileInclusive;
-        v = 0;
+        f[j] = kTileInclusive;  // give up: treat as a known (zero) prefix so the chain ends here
+        v[j] = 0;
       }
-    }
-    const unsigned known = __ballot_sync(0xffffffffu, f == kTileInclusive);
-    const unsigned upto = known ? (unsigned)(__ffs(known) - 1) : 31u;
-    int64_t part = lane <= upto ? (int64_t)v : 0;
+      const unsigned known = __ballot_sync(0xffffffffu, f[j] == kTileInclusive);
+      // lanes at or before the nearest tile with a known inclusive prefix contribute
+      const unsigned upto = known ? (unsigned)(__ffs(known) - 1) : 31u;
+      int64_t part = lane <= upto ? (int64_t)v[j] : 0;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-    prefix += part;
-    if (known) break;
-    base -= 32;
+      for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      prefix += part;
+      done = known != 0;
+    }
+    base -= 32 * WINDOWS;
   }
-  if (PUBLISH && lane == 0) st_desc(st.d + tile, prefix + aggregate, kTileInclusive);
+  if (publish && lane == 0) st_desc(st.d + tile, prefix + aggregate, kTileInclusive);
   return prefix;
 }
 

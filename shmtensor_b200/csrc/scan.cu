@@ -130,20 +130,51 @@ scan_kernel(T* __restrict__ data, int64_t n, int exclusive, int vec_ok, TileStat
 
 // ---- large inputs: persistent clusters ------------------------------------------------------
 // What bounds the kernel above is not bytes but the time a tile sits in registers: ticket,
-// load latency, local sums, look-back (a prefix crosses 32 tiles per round trip through L2 and
-// ~100 tiles per microsecond are started), store.  This kernel takes the three longest waits off
-// that path.  (1) The grid is persistent (every cluster resident at once, super-tiles dealt
-// round-robin), so there is no ticket: a tile's predecessors belong to clusters that are
-// running and only ever wait for still earlier tiles.  (2) A CTA's next tile is brought into
-// shared memory by one bulk copy while the current one is summed, looked back and stored from
-// registers, so load latency overlaps the rest.  (3) Four CTAs form a cluster, add their sums
-// up through distributed shared memory and look back once for a 256 KB super-tile: a quarter of
-// the descriptors per microsecond, so the nearest known prefix is one round trip away, not three.
+// load latency, local sums, look-back, store.  A tile cannot leave before EVERY earlier tile has
+// published its sum, so each tile waits for the slowest load among the hundreds in flight;
+// timed on B200, that wait was 4.0 us of a 7.0 us iteration.  This kernel takes the waits off
+// that path:
+// (1) The grid is persistent (every cluster resident at once, super-tiles dealt round-robin), so
+//     there is no ticket: a tile's predecessors belong to clusters that are running and only
+//     ever wait for still earlier tiles.
+// (2) A CTA keeps two landing buffers: the tiles of its next two iterations are brought into
+//     shared memory by bulk copies while the current one is scanned and stored from registers.
+// (3) The sum of the NEXT tile is taken from its landing buffer and published one iteration
+//     early, by the warps that would otherwise idle while warp 0 looks back for the current
+//     tile.  When a tile's own look-back starts, the sums of everything in flight before it have
+//     been out for a whole iteration: the look-back reads them, it does not wait for them.
+// (4) The four CTAs of a cluster add their sums up through distributed shared memory and publish
+//     one descriptor per 128 KB super-tile.  The sums travel as asynchronous remote stores that
+//     complete a transaction on the receiver's mbarrier, so no cluster-wide barrier (and no
+//     memory fence behind the previous tile's global stores) sits in the loop.
 #ifndef SHMT_SCAN_CLUSTER
 #define SHMT_SCAN_CLUSTER 4
 #endif
+#ifndef SHMT_SCAN_CL_THREADS
+#define SHMT_SCAN_CL_THREADS 256
+#endif
+#ifndef SHMT_SCAN_CL_CTAS
+#define SHMT_SCAN_CL_CTAS 3  // per SM: two 32 KB landing buffers each
+#endif
+#ifndef SHMT_SCAN_CL_WINDOWS
+#define SHMT_SCAN_CL_WINDOWS 1
+#endif
+#ifndef SHMT_SCAN_CL_VECS
+#define SHMT_SCAN_CL_VECS 8
+#endif
 constexpr int kScanCluster = SHMT_SCAN_CLUSTER;
-constexpr int64_t kScanSuperBytes = (int64_t)kScanCluster * kScanTileBytes;
+constexpr int kClThreads = SHMT_SCAN_CL_THREADS;
+constexpr int kClWarps = kClThreads / 32;
+constexpr int kClVecs = SHMT_SCAN_CL_VECS;
+constexpr int kClTileBytes = kClThreads * kClVecs * 16;
+constexpr int kClTileVecs = kClThreads * kClVecs;
+constexpr int kClPartials = kClVecs * kClWarps;
+constexpr int kClCtasPerSm = SHMT_SCAN_CL_CTAS;
+constexpr int kClWindows = SHMT_SCAN_CL_WINDOWS;  // x 32 predecessors read per look-back step
+constexpr int kClSmemBytes = 2 * kClTileBytes;
+static_assert(kClPartials % 32 == 0, "warp 0 scans the per-warp partials, the same number per lane");
+static_assert(kClWarps >= 2 && kClWarps <= 32, "warp 0 looks back, the others sum the next tile");
+constexpr int64_t kScanSuperBytes = (int64_t)kScanCluster * kClTileBytes;
 constexpr int64_t kScanClusterMinBytes = (int64_t)32 << 20;  // below this the ticketed kernel spreads better
 
 __device__ __forceinline__ unsigned cluster_ctarank() {
@@ -164,79 +195,147 @@ __device__ __forceinline__ unsigned cluster_count_x() {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// 8-byte store into the shared memory of CTA `rank` of this cluster, at the address `local`
-// has in the calling CTA (same kernel, same layout).
-__device__ __forceinline__ void st_cluster_u64(void* local, unsigned rank, unsigned long long v) {
-  uint32_t remote;
+// barrier among the warps 1 .. kClWarps-1 of a CTA (warp 0 is looking back meanwhile)
+__device__ __forceinline__ void helpers_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kClThreads - 32) : "memory");
+}
+// 8 bytes into the shared memory of CTA `rank` of this cluster, at the address `local` has in the
+// calling CTA (same kernel, same layout), counted as 8 bytes of transaction on the receiver's
+// mbarrier `local_bar`: whoever waits on that barrier sees the data.
+__device__ __forceinline__ void st_async_cluster_u64(void* local, void* local_bar, unsigned rank,
+                                                     unsigned long long v) {
+  uint32_t remote, remote_bar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(local)), "r"(rank));
-  asm volatile("st.shared::cluster.u64 [%0], %1;" ::"r"(remote), "l"(v) : "memory");
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote_bar) : "r"(smem_addr(local_bar)), "r"(rank));
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.u64 [%0], %1, [%2];" ::"r"(remote),
+               "l"(v), "r"(remote_bar)
+               : "memory");
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads, 2)
+__global__ void __launch_bounds__(kClThreads, kClCtasPerSm)
 scan_cluster_kernel(T* __restrict__ data, int64_t n_super, int exclusive, TileStates st, int64_t* words) {
   using U = typename ScanWord<T>::type;
   constexpr int VEC = 16 / (int)sizeof(T);
-  constexpr int PER_LANE = kScanPartials / 32;
-  extern __shared__ __align__(128) unsigned char landing[];  // one tile, filled by the bulk copy
-  __shared__ U partial[kScanPartials];
-  __shared__ unsigned long long s_sum[2][kScanCluster];  // CTA sums of the cluster, by iteration parity
+  constexpr int PER_LANE = kClPartials / 32;
+  extern __shared__ __align__(128) unsigned char landing[];  // two tiles, filled by bulk copies
+  __shared__ U partial[kClPartials];
+  __shared__ U s_help[32];                                            // per-warp sums of the next tile
+  __shared__ __align__(8) unsigned long long s_sum[2][kScanCluster];  // CTA sums of the cluster, by tile parity
+  __shared__ __align__(8) uint64_t s_sumbar[2];                       // their arrival, by tile parity
+  __shared__ unsigned long long s_whole[2], s_before[2];              // cluster sum / sum of lower ranks, by tile parity
   __shared__ int64_t s_prefix;
-  __shared__ __align__(8) uint64_t s_bar;
+  __shared__ __align__(8) uint64_t s_bar[2];                          // landing buffers, by tile parity
   const unsigned full = 0xffffffffu;
   const unsigned tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned rank = cluster_ctarank();
   const int64_t n_clusters = cluster_count_x();
+  int64_t* status = words + W_STATUS;
   char* bytes = reinterpret_cast<char*>(data);
   union Pack {
     uint4 q;
     U a[VEC];
   };
+  auto flag_timeout = [&]() {
+    atomicMax(reinterpret_cast<unsigned long long*>(status), (unsigned long long)DEV_TIMEOUT);
+  };
+  // bulk copy of this CTA's part of super-tile `sup` into landing buffer j & 1 (one thread)
+  auto issue_load = [&](int64_t sup, int j) {
+    mbar_arrive_expect_tx(&s_bar[j & 1], kClTileBytes);
+    bulk_load(landing + (size_t)(j & 1) * kClTileBytes, bytes + (sup * kScanCluster + rank) * kClTileBytes,
+              kClTileBytes, &s_bar[j & 1]);
+  };
+  // The sum of tile j (of super-tile `sup`), taken from its landing buffer by the calling
+  // threads -- `n_threads` of them, numbered `t`, whole warps, synchronised by `sync` -- and
+  // handed round the cluster; the first warp of them waits for the cluster's sums, leaves the
+  // totals for the look-back in s_whole / s_before and, on rank 0, publishes the aggregate.
+  auto publish_sum = [&](int64_t sup, int j, unsigned t, unsigned n_threads, unsigned first_warp, auto sync) {
+    const int b = j & 1;
+    if (!mbar_wait_bounded(&s_bar[b], (uint32_t)(j >> 1) & 1u)) flag_timeout();
+    const uint4* src = reinterpret_cast<const uint4*>(landing + (size_t)b * kClTileBytes);
+    U acc = 0;
+    for (unsigned q = t; q < (unsigned)kClTileVecs; q += n_threads) {
+      Pack p;
+      p.q = src[q];
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc += p.a[e];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(full, acc, o);
+    if (lane == 0) s_help[warp] = acc;
+    sync();
+    if (warp == first_warp) {
+      U total = 0;
+      for (unsigned w = first_warp; w < first_warp + n_threads / 32; ++w) total += s_help[w];
+      if (lane == 0) mbar_arrive_expect_tx(&s_sumbar[b], 8 * kScanCluster);
+      if (lane < kScanCluster) st_async_cluster_u64(&s_sum[b][rank], &s_sumbar[b], lane, (unsigned long long)total);
+      if (!mbar_wait_bounded(&s_sumbar[b], (uint32_t)(j >> 1) & 1u)) flag_timeout();
+      unsigned long long before = 0, whole = 0;
+#pragma unroll
+      for (int r = 0; r < kScanCluster; ++r) {
+        const unsigned long long x = s_sum[b][r];
+        whole += x;
+        if ((unsigned)r < rank) before += x;
+      }
+      if (lane == 0) {
+        s_whole[b] = whole;
+        s_before[b] = before;
+        if (rank == 0) st_desc(st.d + sup, (long long)whole, sup == 0 ? kTileInclusive : kTileAggregate);
+      }
+    }
+  };
 
-  if (tid == 0) mbar_init(&s_bar, 1);
+  if (tid == 0) {
+    mbar_init(&s_bar[0], 1);
+    mbar_init(&s_bar[1], 1);
+    mbar_init(&s_sumbar[0], 1);
+    mbar_init(&s_sumbar[1], 1);
+  }
   mbar_init_fence();
   __syncthreads();
-  cluster_sync_all();  // every CTA of the cluster is running before anyone writes into its memory
+  cluster_sync_all();  // every CTA of the cluster runs and has its barriers before anyone sends to it
 
   int64_t super = cluster_id_x();
-  if (tid == 0 && super < n_super) {
-    mbar_arrive_expect_tx(&s_bar, kScanTileBytes);
-    bulk_load(landing, bytes + (super * kScanCluster + rank) * kScanTileBytes, kScanTileBytes, &s_bar);
+  if (tid == 0) {
+    if (super < n_super) issue_load(super, 0);
+    if (super + n_clusters < n_super) issue_load(super + n_clusters, 1);
   }
-  uint32_t phase = 0;
+  if (super < n_super) publish_sum(super, 0, tid, kClThreads, 0, [] { __syncthreads(); });
+  __syncthreads();
+
   for (int it = 0; super < n_super; super += n_clusters, ++it) {
-    if (!mbar_wait_bounded(&s_bar, phase))
-      atomicMax(reinterpret_cast<unsigned long long*>(words + W_STATUS), (unsigned long long)DEV_TIMEOUT);
-    phase ^= 1u;
-    U v[kScanVecs][VEC], vsum[kScanVecs], inc[kScanVecs];
+    const int b = it & 1;
+    // ---- the tile into registers, sums inside vectors and warps.  It landed before its sum was
+    // taken an iteration ago, so this wait returns at once; it is what entitles every thread (not
+    // only those that summed) to read what the bulk copy wrote.
+    if (!mbar_wait_bounded(&s_bar[b], (uint32_t)(it >> 1) & 1u)) flag_timeout();
+    U v[kClVecs][VEC], inc[kClVecs];  // a vector's own sum stays in its last element
+    const uint4* src = reinterpret_cast<const uint4*>(landing + (size_t)b * kClTileBytes);
 #pragma unroll
-    for (int k = 0; k < kScanVecs; ++k) {
+    for (int k = 0; k < kClVecs; ++k) {
       Pack p;
-      p.q = reinterpret_cast<const uint4*>(landing)[k * kScanThreads + tid];
+      p.q = src[k * kClThreads + tid];
 #pragma unroll
       for (int j = 0; j < VEC; ++j) v[k][j] = p.a[j];
     }
-    __syncthreads();  // the tile is in registers: the landing buffer is free, `partial` too
-    const int64_t next = super + n_clusters;
-    if (tid == 0 && next < n_super) {
-      mbar_arrive_expect_tx(&s_bar, kScanTileBytes);
-      bulk_load(landing, bytes + (next * kScanCluster + rank) * kScanTileBytes, kScanTileBytes, &s_bar);
-    }
 #pragma unroll
-    for (int k = 0; k < kScanVecs; ++k) {
+    for (int k = 0; k < kClVecs; ++k) {
 #pragma unroll
       for (int j = 1; j < VEC; ++j) v[k][j] += v[k][j - 1];
-      vsum[k] = v[k][VEC - 1];
-      inc[k] = vsum[k];
+      inc[k] = v[k][VEC - 1];
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const U up = __shfl_up_sync(full, inc[k], o);
         if (lane >= (unsigned)o) inc[k] += up;
       }
-      if (lane == 31) partial[k * kScanWarps + warp] = inc[k];
+      if (lane == 31) partial[k * kClWarps + warp] = inc[k];
     }
-    __syncthreads();
+    __syncthreads();  // the tile is in registers: its landing buffer is free
+    const int64_t next = super + n_clusters, after_next = next + n_clusters;
+    if (tid == 0 && after_next < n_super) issue_load(after_next, it + 2);
     if (warp == 0) {
+      // ---- warp 0: offsets of the (row, warp) partials, then the look-back (every sum it needs
+      // was published an iteration ago)
       U a[PER_LANE], lsum = 0;
 #pragma unroll
       for (int q = 0; q < PER_LANE; ++q) {
@@ -255,49 +354,27 @@ scan_cluster_kernel(T* __restrict__ data, int64_t n_super, int exclusive, TileSt
         partial[lane * PER_LANE + q] = run;
         run += a[q];
       }
-      const U total = __shfl_sync(full, linc, 31);
-      // this CTA's sum to every CTA of the cluster (its own copy included)
-      if (lane < kScanCluster) st_cluster_u64(&s_sum[it & 1][rank], lane, (unsigned long long)total);
-    }
-#ifdef SHMT_DBG_NO_CLUSTER_BARRIER
-    __syncthreads();
-#else
-    cluster_sync_all();  // sums delivered; also the CTA-wide barrier behind `partial`
-#endif
-    if (warp == 0) {
-      unsigned long long before = 0, whole = 0;
-#pragma unroll
-      for (int r = 0; r < kScanCluster; ++r) {
-        const unsigned long long t = s_sum[it & 1][r];
-        whole += t;
-        if ((unsigned)r < rank) before += t;
-      }
-#ifdef SHMT_DBG_NO_LOOKBACK
-      const int64_t p = 0;
-#else
-      const int64_t p = rank == 0
-          ? lookback_exclusive_prefix_shared<true>(st, (int)super, (int64_t)whole, words + W_STATUS)
-          : lookback_exclusive_prefix_shared<false>(st, (int)super, (int64_t)whole, words + W_STATUS);
-#endif
-      if (lane == 0) s_prefix = p + (int64_t)before;
+      const int64_t p = lookback_published<kClWindows>(st, (int)super, (int64_t)s_whole[b], rank == 0, status);
+      if (lane == 0) s_prefix = p + (int64_t)s_before[b];
+    } else if (next < n_super) {
+      // ---- the other warps: the next tile's sum, out to the cluster and (rank 0) to its descriptor
+      publish_sum(next, it + 1, tid - 32, kClThreads - 32, 1, [] { helpers_sync(); });
     }
     __syncthreads();
     const U prefix = (U)(uint64_t)s_prefix;
-    T* out = data + (super * kScanCluster + rank) * (kScanTileBytes / (int64_t)sizeof(T));
+    T* out = data + (super * kScanCluster + rank) * (kClTileBytes / (int64_t)sizeof(T));
 #pragma unroll
-    for (int k = 0; k < kScanVecs; ++k) {
-      const U ahead = prefix + partial[k * kScanWarps + warp] + (inc[k] - vsum[k]);
+    for (int k = 0; k < kClVecs; ++k) {
+      const U ahead = prefix + partial[k * kClWarps + warp] + (inc[k] - v[k][VEC - 1]);
       Pack p;
 #pragma unroll
       for (int j = 0; j < VEC; ++j)
         p.a[j] = ahead + (exclusive ? (j ? v[k][j - 1] : U(0)) : v[k][j]);
-#ifdef SHMT_DBG_NO_STORE
-      if (p.a[0] == (U)0x12345678) reinterpret_cast<uint4*>(out)[k * kScanThreads + tid] = p.q;
-#else
-      reinterpret_cast<uint4*>(out)[k * kScanThreads + tid] = p.q;
-#endif
+      reinterpret_cast<uint4*>(out)[k * kClThreads + tid] = p.q;
     }
   }
+  // nobody leaves while a CTA of the cluster may still be sending to it or reading its barriers
+  cluster_sync_all();
 }
 
 // Clusters of the persistent grid: as many as are resident at once (asked of the runtime once
@@ -310,11 +387,11 @@ static int scan_cluster_grid(int64_t n_super, unsigned* grid) {
   SHMT_REQUIRE(dev >= 0 && dev < 64, "scan: device index %d not supported", dev);
   if (resident[dev] == 0) {
     SHMT_CUDA_TRY(cudaFuncSetAttribute(scan_cluster_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       kScanTileBytes));
+                                       kClSmemBytes));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(kScanCluster * 64);
-    cfg.blockDim = dim3(kScanThreads);
-    cfg.dynamicSmemBytes = kScanTileBytes;
+    cfg.blockDim = dim3(kClThreads);
+    cfg.dynamicSmemBytes = kClSmemBytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = kScanCluster;
@@ -339,8 +416,8 @@ static int run_scan_clusters(void* data, int64_t n_super, int exclusive, TileSta
   if (int rc = scan_cluster_grid<T>(n_super, &grid)) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kScanThreads);
-  cfg.dynamicSmemBytes = kScanTileBytes;
+  cfg.blockDim = dim3(kClThreads);
+  cfg.dynamicSmemBytes = kClSmemBytes;
   cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -399,9 +476,14 @@ int launch_scan(shmt_ctx* ctx, void* data, int dtype, int64_t n, int exclusive,
   const int64_t n_tiles = (n + kScanTile - 1) / kScanTile;
   SHMT_REQUIRE(n_tiles < (int64_t)1 << 30, "scan: %lld items is too many", (long long)n);
   TileStates st = carve_tile_states(ctx->region() + scratch_off, n_tiles);
-  // status / result / ticket words and the tile descriptors start at zero
-  SHMT_CUDA_TRY(cudaMemsetAsync(ctx->d_words(), 0, 256, stream));
-  SHMT_CUDA_TRY(cudaMemsetAsync(st.d, 0, tile_state_bytes(n_tiles), stream));
+  // status / result / ticket words and the tile descriptors start at zero (one memset when the
+  // descriptors sit right behind the words, as they do for a plain scan)
+  if (scratch_off == 0) {
+    SHMT_CUDA_TRY(cudaMemsetAsync(ctx->scratch, 0, 256 + tile_state_bytes(n_tiles), stream));
+  } else {
+    SHMT_CUDA_TRY(cudaMemsetAsync(ctx->d_words(), 0, 256, stream));
+    SHMT_CUDA_TRY(cudaMemsetAsync(st.d, 0, tile_state_bytes(n_tiles), stream));
+  }
   static const bool no_clusters = getenv("SHMT_SCAN_NO_CLUSTERS") != nullptr;
   if (!no_clusters && ((uintptr_t)data & 15) == 0 && n * int_itemsize(dtype) >= kScanClusterMinBytes) {
     // the ticketed kernel's descriptor block is larger than what both kernels need here

@@ -98,9 +98,14 @@ def test_dataloader_with_a_replaceable_cache():
     hotness = torch.from_numpy(deg.astype(np.float32))
     dl.create_cache(int(indices.nbytes * 0.3), hotness, replaceable=True)
     assert dl.has_cache and dl.graph_cache.rows() > 0
-    cached = torch.sort(hotness, descending=True).indices[:dl.graph_cache.rows()]
-    others = torch.from_numpy(np.setdiff1d(np.arange(8000), cached.numpy())[:200])
-    assert dl.replace_cache(cached[-200:].cuda(), others.cuda()) == 200
+    is_cached = dl.hashmap.query(torch.arange(8000, device="cuda")) >= 0
+    cached = is_cached.nonzero(as_tuple=True)[0]
+    assert cached.numel() == dl.graph_cache.rows() >= 8      # the hottest rows are the longest: few fit
+    n_swap = cached.numel() // 2
+    # rows without neighbours or with few of them always fit into what the evicted rows free
+    small = ((~is_cached) & torch.from_numpy(deg <= 8).cuda()).nonzero(as_tuple=True)[0][:n_swap]
+    assert dl.replace_cache(cached[-n_swap:], small) == n_swap
+    assert bool((dl.hashmap.query(small) >= 0).all()) and bool((dl.hashmap.query(cached[-n_swap:]) == -1).all())
     for frontier, output_nodes, blocks in dl:
         cur = output_nodes.cpu().numpy()
         for (sub_indptr, relabel_indices, n_src, n_dst) in reversed(blocks):
