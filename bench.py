@@ -1,10 +1,10 @@
 #!/usr/bin/env python
-"""Benchmark of the cached feature fetch (the hot path's headline metric).
+"""Benchmark of the GPU-cache hot path: fetched feature GB/s and sampled edges/s.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload ...]
 
-Workload (one step = one batch through the fused probe+gather kernel): a pinned host table of
-2,400,000 x 100 float32 rows, N(0,1); the top 20 % of rows by a seeded power-law score are
+Headline workload (one step = one batch through the fused probe+gather kernel): a pinned host table
+of 2,400,000 x 100 float32 rows, N(0,1); the top 20 % of rows by a seeded power-law score are
 cached in HBM behind a static hashmap (int64 keys -> int32 slots, load factor 0.5); each
 batch is 500,000 int64 ids, rank-Zipf(1.1) over the score ranking mixed with uniform rows so
 that about 80 % hit the cache; misses are read from the host table through UVA.  With N > 1
@@ -13,9 +13,14 @@ over NVLink by the same kernel; every rank runs its own batches (weak scaling).
 
 Prints one JSON line (rank 0).  ``value`` times the kernel with ids already on the GPU;
 ``e2e`` times the public call with the ids starting in pinned host memory and a read-back of
-the last fetched row.  ``--impl reference`` times the reference's CPU path for the same
-fetch (``data[q]`` = torch.index_select on the host table, example/test_cache_fetch.py:138)
-on the host cores.  Data is synthetic and seeded.
+the last fetched row; ``e2e_host_result`` copies the whole result to pinned host memory as well.
+The same line carries, as objects with their own rooflines and baselines, the rest of the
+metric: ``sampling`` (cached 3-hop neighbour sampling + relabel, sampled edges/s) and ``update``
+(fused insert/overwrite + lookups) at N = 1, and ``minibatch_c4`` (sampling + feature fetch over
+the partitioned cache on the 111,000,000-node graph) at every N.  ``--workload`` runs one of them
+alone.  ``--impl reference`` times the reference's CPU path for the same fetch (``data[q]`` =
+torch.index_select on the host table, example/test_cache_fetch.py:138) on the host cores.
+Data is synthetic and seeded.
 """
 from __future__ import annotations
 
@@ -467,6 +472,7 @@ def run_ours(args) -> None:
     else:
         pcache = PartitionedFeatureCache(table, cached_ids, load_factor=LOAD_FACTOR,
                                          replicate=replicated_rows(n_cached, world))
+        pcache.warm()
         fetch = pcache.fetch
         query = pcache.directory.query
     hit_counts = [int((query(b) >= 0).sum().item()) for b in batches]
@@ -1318,6 +1324,7 @@ def minibatch_object(steps: int, rank: int, local_rank: int, world: int) -> dict
     del indices_dev, indptr_dev
     gmap = capi.CUCOStaticHashmap(hot.int(), torch.arange(n_cached, dtype=torch.int32, device=dev), 0.8)
     fcache = PartitionedFeatureCache(feats, hot, replicate=0)   # neighbours are uniform over the nodes: no hot head
+    fcache.warm()
     del hot
     torch.cuda.empty_cache()
     t_cached = time.perf_counter()
@@ -1420,8 +1427,10 @@ def minibatch_object(steps: int, rank: int, local_rank: int, world: int) -> dict
                     "build_caches": round(t_cached - t_filled, 1)},
         "host_pages_per_node": {"feats": pages_per_node(feats.data_ptr()), "indices": pages_per_node(indices.data_ptr())},
     })
-    # CPU beside it, on rank 0, bounded: the threaded C++ sampler + relabel, then index_select on the table
-    if rank == 0:
+    # CPU beside it: one GPU only (with more ranks the other processes' threads share the cores), bounded:
+    # the threaded C++ sampler + relabel, then index_select on the table
+    obj["cpu_baseline"] = None
+    if world == 1:
         from oracle import build_oracle
         use_all_host_threads()
         cpu = build_oracle.load_cpu()
@@ -1436,12 +1445,8 @@ def minibatch_object(steps: int, rank: int, local_rank: int, world: int) -> dict
         cpu_dt = (time.perf_counter() - t0) / n_cpu
         obj["cpu_baseline"] = {"value": round(1 / cpu_dt, 2), "unit": "mini-batches/s", "cores": cpu.oracle_num_threads(),
                                "kind": "port", "ms_per_step": round(cpu_dt * 1e3, 2),
-                               "sample": f"{n_cpu} full mini-batches of one rank: threaded C++ sampler + serial relabel + "
+                               "sample": f"{n_cpu} full mini-batches: threaded C++ sampler + serial relabel + "
                                          "torch.index_select on the shared feature table"}
-    if world > 1:
-        box = [obj.get("cpu_baseline")]
-        dist.broadcast_object_list(box, src=0)
-        obj["cpu_baseline"] = box[0]
     torch.cuda.synchronize()
     fcache.close()
     del fcache, gp, gi, gmap, indptr, indices, feats, indptr_n, indices_n, rows, frontier

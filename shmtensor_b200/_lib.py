@@ -93,6 +93,7 @@ SIGNATURES = {
     "shmt_npy_close": (_i, [_i64, _i64, _i64, _i]),
     "shmt_host_register": (_i, [_vp, _i64]),
     "shmt_host_unregister": (_i, [_vp]),
+    "shmt_host_prefault": (_i, [_vp, _i64, _i]),
     "shmt_host_numa_nodes": (_i, []),
     "shmt_host_numa_place": (_i, [_vp, _i64, _i, _i]),
     "shmt_dev_alloc": (_i, [_i64, _pvp]),

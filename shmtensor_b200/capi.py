@@ -148,6 +148,14 @@ def unlink_shared_mem(name: str) -> None:
 NUMA_INTERLEAVE, NUMA_BIND = 1, 2
 
 
+def prefault(ptr: int, nbytes: int, n_threads: int = 0) -> None:
+    """Extension: make the pages of a fresh (all-zero) host mapping present from several threads
+    (default: one per core this process may run on, at most 32), before it is registered."""
+    import os
+    n = n_threads or min(32, len(os.sched_getaffinity(0)))
+    check(lib.shmt_host_prefault(ptr, nbytes, n))
+
+
 def numa_nodes() -> int:
     """Extension: number of memory nodes of this machine."""
     return lib.shmt_host_numa_nodes()

@@ -345,6 +345,32 @@ int shmt_host_register(void* ptr, int64_t nbytes) {
   return register_host(ptr, (size_t)nbytes, cudaHostRegisterPortable, "shmt_host_register");
 }
 
+int shmt_host_prefault(void* ptr, int64_t nbytes, int n_threads) {
+  if (!ptr || nbytes <= 0) {
+    set_error("shmt_host_prefault: bad argument");
+    return SHMT_ERR_INVALID;
+  }
+  if (n_threads < 1) n_threads = 1;
+  if (n_threads > 64) n_threads = 64;
+  char* base = static_cast<char*>(ptr);
+  const size_t total = (size_t)nbytes;
+  // slices of whole 2 MB pieces, one thread each: a fresh shared mapping has no pages yet, and
+  // one thread asking the kernel for them page by page manages only a few GB/s
+  const size_t piece = (size_t)2 << 20;
+  const size_t n_pieces = (total + piece - 1) / piece;
+  std::vector<std::thread> workers;
+  for (int t = 0; t < n_threads; ++t) {
+    workers.emplace_back([=] {
+      for (size_t p = (size_t)t; p < n_pieces; p += (size_t)n_threads) {
+        const size_t lo = p * piece, hi = lo + piece < total ? lo + piece : total;
+        for (size_t q = lo; q < hi; q += 4096) *reinterpret_cast<volatile char*>(base + q) = 0;
+      }
+    });
+  }
+  for (auto& w : workers) w.join();
+  return SHMT_OK;
+}
+
 int shmt_host_numa_nodes(void) { return (int)memory_nodes().size(); }
 
 int shmt_host_numa_place(void* ptr, int64_t nbytes, int policy, int node) {

@@ -65,14 +65,18 @@ class ShmTensor(_HostTensorView):
                         capi.numa_place(self.ptr_, nbytes, capi.NUMA_INTERLEAVE)
                     else:
                         capi.numa_place(self.ptr_, nbytes, capi.NUMA_BIND, int(numa))
-                if pin_memory:
-                    capi._register_range(self.ptr_, nbytes)
+                if pin_memory and nbytes >= (1 << 28):
+                    capi.prefault(self.ptr_, nbytes)  # pages present before anyone pins them
             except Exception as exc:  # noqa: BLE001  told to every rank below
                 error = "File name is already exist" if "already exists" in str(exc) else str(exc)
         error = self._agree(error, local_group)
         if error is not None:
             raise Exception(error)
-        if not creator:
+        # every rank pins its own mapping, all at the same time
+        if creator:
+            if pin_memory:
+                capi._register_range(self.ptr_, nbytes)
+        else:
             self.ptr_, self.fd_ = capi.open_shared_mem(name, nbytes, pin_memory)
 
         # arguments only, no reference to self, or the object would never be collected

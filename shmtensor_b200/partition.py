@@ -176,6 +176,19 @@ class PartitionedFeatureCache:
                                                 values.to(self.device), load_factor)
         self.counts = counts
 
+    def warm(self) -> None:
+        """One streaming pass over every peer's shard from this GPU, so that the first timed fetch
+        does not pay for setting up the translations of memory it has never touched."""
+        if self.world <= 1:
+            return
+        sink = torch.zeros(1, dtype=torch.int64, device=self.device)
+        sizes = [c + self.replicated for c in self.counts]
+        for r, (ptr, rows) in enumerate(zip(self._peer_ptrs, sizes)):
+            nbytes = rows * self.row_bytes // 16 * 16
+            if r != self.rank and nbytes >= 16:
+                check(lib.shmt_stream_read(ptr, nbytes, sink.data_ptr(), capi._stream(self.device)))
+        torch.cuda.synchronize()
+
     def fetch(self, ids: torch.Tensor) -> torch.Tensor:
         capi._check_cuda(ids, "ids")
         ids = ids.contiguous()
