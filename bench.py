@@ -47,7 +47,7 @@ ROW_BYTES = DIM * 4
 N_BATCHES = 8
 METRIC, UNIT = "fetched feature GB/s", "GB/s"
 PG_TIMEOUT = datetime.timedelta(minutes=6)  # a rank that failed ends the others' next collective
-NCU_DRAM_BYTES_PER_LAUNCH = 210_300_000  # 63.8 MB read + 146.5 MB written (ncu, headline batch)
+NCU_DRAM_BYTES_PER_LAUNCH = 203_000_000  # 63.8 MB read + 139.2 MB written (ncu, headline batch)
 WORKLOAD = ("1-GPU cached feature fetch: pinned 2,400,000x100 f32 host table, top 20% rows cached "
             "behind int64->int32 map (load 0.5), 500,000 int64 ids/batch Zipf(1.1), ~80% hits, misses via UVA")
 
@@ -729,7 +729,7 @@ def run_ours(args) -> None:
             # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
             # workload, from the ncu capture summarised in profiles/row_gather_bulk_mixed.md
             "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "algorithmic_bytes": int(alg),
-            "traffic_source": "profiles/row_gather_bulk_mixed.md (ncu --set full, 2 launches; bytes per launch)",
+            "traffic_source": "profiles/row_gather_bulk_mixed.md (ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the headline batch)",
             "kernel_ms": round(kernel_ms, 5),
             "note": "the 80%-hit batch is bound by the host link, not HBM: see roofline_link and "
                     "frac_of_bound (time at the binding ceiling / measured time)",
