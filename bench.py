@@ -1863,6 +1863,17 @@ def run_scan_relabel(args) -> None:
     while cap < 2 * SR_IDS:
         cap <<= 1
     b_rel = SR_IDS * (8 + 8 + 8 * 3) + uniq.numel() * 8
+    # what bounds relabel is the rate of random 16-byte slot accesses in a table beyond L2 (three per id:
+    # claim + first index, read first index + write new id, read new id + empty the slot)
+    from shmtensor_b200._lib import check, lib as shm_lib
+    sink = torch.zeros(1, dtype=torch.int64, device=dev)
+    tbl = torch.empty(cap * 16, dtype=torch.uint8, device=dev)
+    n_probe = 1 << 26
+    probe = lambda c=[0]: (check(shm_lib.shmt_random_read(tbl.data_ptr(), tbl.numel(), n_probe, 16, c[0], sink.data_ptr(),
+                                                          stream.cuda_stream)), c.__setitem__(0, c[0] + 1))
+    probe()
+    slot_rate = n_probe / (min(time_launches(probe, 1, stream) for _ in range(5)) * 1e-3)
+    del tbl
     line.update({
         "value": round((SR_SCAN_N + SR_IDS) / ((t32 + t_rel) * 1e-3), 1), "ms_per_step": round(t32 + t_rel, 4),
         "scan_int32": {"ms": round(t32, 4), "elements_per_s": round(SR_SCAN_N / (t32 * 1e-3), 1),
@@ -1873,15 +1884,18 @@ def run_scan_relabel(args) -> None:
                                     "frac": round(b64 / (t64 * 1e6) / peak, 4)}},
         "relabel": {"ms": round(t_rel, 4), "ids_per_s": round(SR_IDS / (t_rel * 1e-3), 1), "unique": uniq.numel(),
                     "table_slots": cap,
-                    "roofline": {"bound": "hbm", "achieved": round(b_rel / (t_rel * 1e6), 1), "peak": peak, "unit": "GB/s",
-                                 "frac": round(b_rel / (t_rel * 1e6) / peak, 4),
-                                 "note": "streamed bytes only; the random 12-byte table accesses (one sector each) "
-                                         "are what bounds it"}},
+                    "roofline": {"bound": "hbm, rate of random 16-byte slot accesses (3 per id)",
+                                 "kernel": "relabel_insert / relabel_compact / relabel_remap",
+                                 "achieved": round(3 * SR_IDS / (t_rel * 1e-3) / 1e9, 3), "peak": round(slot_rate / 1e9, 3),
+                                 "unit": "G accesses/s", "frac": round(3 * SR_IDS / (t_rel * 1e-3) / slot_rate, 4),
+                                 "peak_source": "shmt_random_read, 16-byte reads over a buffer of the table's size "
+                                                "(1 GiB), measured in this run",
+                                 "streamed_bytes_frac_of_hbm": round(b_rel / (t_rel * 1e6) / peak, 4)}},
         "cub_scan": {"int32_ms": round(cub32, 4), "int64_ms": round(cub64, 4),
                      "int32_gbs": round(b32 / (cub32 * 1e6), 1), "int64_gbs": round(b64 / (cub64 * 1e6), 1),
                      "what": "torch.cumsum (cub::DeviceScan::InclusiveSum, out of place) on the same inputs: the "
                              "library scan the reference's hot path calls"},
-        "roofline": {"bound": "hbm", "kernel": "scan_kernel (decoupled look-back, one pass)",
+        "roofline": {"bound": "hbm", "kernel": "scan_cluster_kernel<int> (persistent clusters, decoupled look-back, one pass)",
                      "achieved": round(b32 / (t32 * 1e6), 1), "peak": peak, "unit": "GB/s",
                      "frac": round(b32 / (t32 * 1e6) / peak, 4), "peak_source": peak_src, "traffic": None},
         "e2e": {"value": round((SR_SCAN_N + SR_IDS) / ((t32 + t_rel) * 1e-3), 1), "unit": "elements/s",
