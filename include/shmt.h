@@ -290,6 +290,19 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
                           void* const* out_relabel, void* const* out_frontier,
                           int64_t* sizes_host, void* stream);
 
+/* The same mini-batch that also reports the edge id of every sampled neighbour, per hop, in
+ * out_edge_ids[h] (c_h * fanouts[h] entries of indptr dtype, parallel to out_sub_indices[h]);
+ * see shmt_sample_hop_eids.  No counterpart in the reference.                              */
+int shmt_sample_minibatch_eids(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
+                               const void* indices, int indices_dtype,
+                               const void* gpu_indptr, const void* gpu_indices,
+                               const void* gpu_edge_base, const shmt_map* map,
+                               const void* seeds, int64_t n_seeds, const int64_t* fanouts,
+                               int n_hops, int replace, uint64_t rng_seed, uint64_t rng_offset,
+                               void* const* out_sub_indptr, void* const* out_sub_indices,
+                               void* const* out_edge_ids, void* const* out_relabel,
+                               void* const* out_frontier, int64_t* sizes_host, void* stream);
+
 /* Compact CSR of the selected rows, in the given order: CreateCacheCSR
  * (src/cache_graph_sampling.cu:455-492).  _count writes the n+1 offsets and
  * (synchronising) the total; _fill copies the adjacency lists.               */

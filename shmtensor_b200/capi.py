@@ -681,7 +681,8 @@ def csr_weighted_sampling(indptr, indices, weights, seeds, num_picks: int, repla
 
 def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.Tensor,
                      fanouts: Sequence[int], replace: bool = False, gpu_indptr=None,
-                     gpu_indices=None, hashmap: "CUCOStaticHashmap | None" = None):
+                     gpu_indices=None, hashmap: "CUCOStaticHashmap | None" = None,
+                     gpu_edge_base=None, return_eids: bool = False):
     """Extension: all hops of a mini-batch in one native call (``shmt_sample_minibatch``).
 
     Equivalent to, for each ``k`` in ``fanouts`` in the given order::
@@ -691,7 +692,9 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
 
     but nothing is read back between hops; the host waits once.  Returns
     ``(frontier, hops)`` where ``hops[h] = (sub_indptr, sub_indices, relabel_indices,
-    frontier_after_hop)``.  Seeds are converted to the dtype of ``indices``.
+    frontier_after_hop)``.  Seeds are converted to the dtype of ``indices``.  With ``return_eids``
+    every hop's tuple ends with the edge ids of its sampled neighbours (positions in ``indices``,
+    dtype of ``indptr``); a cached graph then needs ``gpu_edge_base`` (``subcsr_edge_base``).
     """
     _check_cuda(seeds, "seeds")
     dev = seeds.device
@@ -705,7 +708,9 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
         caps.append(caps[-1] * (1 + int(k)))
     # two allocations (one per dtype); the per-hop outputs are 16-byte aligned pieces of them,
     # handed to the library as raw addresses and turned into views only once sizes are known
-    key = (seeds.numel(), tuple(int(k) for k in fanouts), indptr.dtype, indices.dtype)
+    if return_eids and hashmap is not None and gpu_edge_base is None:
+        raise RuntimeError("sample_minibatch: edge ids of a cached graph need gpu_edge_base")
+    key = (seeds.numel(), tuple(int(k) for k in fanouts), indptr.dtype, indices.dtype, bool(return_eids))
     layout = _minibatch_layouts.get(key)
     if layout is None:
         def plan(dtype, counts):
@@ -716,7 +721,8 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
                 offs.append(lo)
                 lo += -(-c // step) * step
             return offs + [lo], item
-        p_off, p_item = plan(indptr.dtype, [caps[h] + 1 for h in range(n_hops)])
+        p_off, p_item = plan(indptr.dtype, [caps[h] + 1 for h in range(n_hops)]
+                             + ([caps[h] * int(fanouts[h]) for h in range(n_hops)] if return_eids else []))
         i_off, i_item = plan(indices.dtype, [caps[h] * int(fanouts[h]) for h in range(n_hops)]
                              + [caps[h + 1] for h in range(n_hops)] * 2)
         fan = (C.c_int64 * n_hops)(*[int(k) for k in fanouts])
@@ -729,14 +735,22 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
     sizes = (C.c_int64 * (3 * n_hops))()
     offset = _rng["calls"] + 1
     _rng["calls"] += n_hops
-    check(lib.shmt_sample_minibatch(
-        _ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr), _ptr(gpu_indices),
-        hashmap._handle if hashmap is not None else None, _ptr(seeds), seeds.numel(), fan, n_hops,
-        int(bool(replace)), _rng["seed"], offset,
-        VP(*[p_base + p_off[h] * p_item for h in range(n_hops)]),
-        VP(*[i_base + i_off[h] * i_item for h in range(n_hops)]),
-        VP(*[i_base + i_off[n_hops + h] * i_item for h in range(n_hops)]),
-        VP(*[i_base + i_off[2 * n_hops + h] * i_item for h in range(n_hops)]), sizes, _stream(dev)))
+    out_ptr = VP(*[p_base + p_off[h] * p_item for h in range(n_hops)])
+    out_idx = VP(*[i_base + i_off[h] * i_item for h in range(n_hops)])
+    out_rel = VP(*[i_base + i_off[n_hops + h] * i_item for h in range(n_hops)])
+    out_front = VP(*[i_base + i_off[2 * n_hops + h] * i_item for h in range(n_hops)])
+    map_handle = hashmap._handle if hashmap is not None else None
+    if return_eids:
+        out_eid = VP(*[p_base + p_off[n_hops + h] * p_item for h in range(n_hops)])
+        check(lib.shmt_sample_minibatch_eids(
+            _ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr), _ptr(gpu_indices),
+            _ptr(gpu_edge_base), map_handle, _ptr(seeds), seeds.numel(), fan, n_hops, int(bool(replace)),
+            _rng["seed"], offset, out_ptr, out_idx, out_eid, out_rel, out_front, sizes, _stream(dev)))
+    else:
+        check(lib.shmt_sample_minibatch(
+            _ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr), _ptr(gpu_indices),
+            map_handle, _ptr(seeds), seeds.numel(), fan, n_hops, int(bool(replace)), _rng["seed"], offset,
+            out_ptr, out_idx, out_rel, out_front, sizes, _stream(dev)))
     # one split per pool gives every exact-size view: per piece (skip, take, rest)
     cuts_p, cuts_i = [], [0] * (9 * n_hops)
     for h in range(n_hops):
@@ -746,9 +760,14 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
         for piece, skip, take in ((h, 0, nnz), (n_hops + h, n_in, nnz), (2 * n_hops + h, 0, n_out)):
             room = i_off[piece + 1] - i_off[piece]
             cuts_i[3 * piece:3 * piece + 3] = [skip, take, room - skip - take]
+    if return_eids:
+        for h in range(n_hops):
+            nnz = sizes[3 * h + 1]
+            cuts_p += [nnz, p_off[n_hops + h + 1] - p_off[n_hops + h] - nnz]
     pv = p_pool.split_with_sizes(cuts_p)
     iv = i_pool.split_with_sizes(cuts_i)
     hops = [(pv[2 * h], iv[3 * h + 1], iv[3 * (n_hops + h) + 1], iv[3 * (2 * n_hops + h) + 1])
+            + ((pv[2 * (n_hops + h)],) if return_eids else ())
             for h in range(n_hops)]
     return hops[-1][3], hops
 

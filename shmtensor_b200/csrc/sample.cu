@@ -764,13 +764,14 @@ int shmt_sample_hop_eids(shmt_ctx* ctx, const void* indptr, int indptr_dtype, co
 // to back; each reads the size of its input from the device word the previous stage
 // wrote, with grids sized for the largest frontier the fan-outs allow.  The host waits
 // once, at the end, for all the sizes.
-int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
-                          int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
-                          const shmt_map* map, const void* seeds, int64_t n_seeds,
-                          const int64_t* fanouts, int n_hops, int replace, uint64_t rng_seed,
-                          uint64_t rng_offset, void* const* out_sub_indptr,
-                          void* const* out_sub_indices, void* const* out_relabel,
-                          void* const* out_frontier, int64_t* sizes_host, void* stream) {
+static int sample_minibatch_impl(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                                 int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
+                                 const shmt_map* map, const void* seeds, int64_t n_seeds,
+                                 const int64_t* fanouts, int n_hops, int replace, uint64_t rng_seed,
+                                 uint64_t rng_offset, void* const* out_sub_indptr,
+                                 void* const* out_sub_indices, void* const* out_relabel,
+                                 void* const* out_frontier, int64_t* sizes_host, void* stream,
+                                 const void* gpu_edge_base, void* const* out_edge_ids) {
   SHMT_REQUIRE(ctx != nullptr, "shmt_sample_minibatch: ctx is null");
   SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(indices_dtype),
                "shmt_sample_minibatch: ID can only be int32 or int64");
@@ -828,6 +829,8 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     job.sub_indptr = out_sub_indptr[h];
     job.sub_indices = out_sub_indices[h];
     job.seeds_per_tile = spt[h];
+    job.out_eids = out_edge_ids ? out_edge_ids[h] : nullptr;
+    job.gpu_edge_base = gpu_edge_base;
     job.st = carve_tile_states(base + off_hop[h], hop_tiles[h]);
     job.ticket = w + 0;
     job.status = status;
@@ -878,6 +881,37 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, c
     n_in = sizes_host[3 * h + 2];
   }
   return SHMT_OK;
+}
+
+int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                          int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
+                          const shmt_map* map, const void* seeds, int64_t n_seeds,
+                          const int64_t* fanouts, int n_hops, int replace, uint64_t rng_seed,
+                          uint64_t rng_offset, void* const* out_sub_indptr,
+                          void* const* out_sub_indices, void* const* out_relabel,
+                          void* const* out_frontier, int64_t* sizes_host, void* stream) {
+  return sample_minibatch_impl(ctx, indptr, indptr_dtype, indices, indices_dtype, gpu_indptr, gpu_indices, map,
+                               seeds, n_seeds, fanouts, n_hops, replace, rng_seed, rng_offset, out_sub_indptr,
+                               out_sub_indices, out_relabel, out_frontier, sizes_host, stream, nullptr, nullptr);
+}
+
+int shmt_sample_minibatch_eids(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                               int indices_dtype, const void* gpu_indptr, const void* gpu_indices,
+                               const void* gpu_edge_base, const shmt_map* map, const void* seeds,
+                               int64_t n_seeds, const int64_t* fanouts, int n_hops, int replace,
+                               uint64_t rng_seed, uint64_t rng_offset, void* const* out_sub_indptr,
+                               void* const* out_sub_indices, void* const* out_edge_ids,
+                               void* const* out_relabel, void* const* out_frontier,
+                               int64_t* sizes_host, void* stream) {
+  SHMT_REQUIRE(out_edge_ids != nullptr, "shmt_sample_minibatch_eids: out_edge_ids is null");
+  SHMT_REQUIRE(map == nullptr || gpu_edge_base != nullptr,
+               "shmt_sample_minibatch_eids: a cached graph needs gpu_edge_base (shmt_subcsr_edge_base)");
+  for (int h = 0; h < n_hops && h < 8; ++h)
+    SHMT_REQUIRE(out_edge_ids[h] != nullptr, "shmt_sample_minibatch_eids: edge-id buffer of hop %d is null", h);
+  return sample_minibatch_impl(ctx, indptr, indptr_dtype, indices, indices_dtype, gpu_indptr, gpu_indices, map,
+                               seeds, n_seeds, fanouts, n_hops, replace, rng_seed, rng_offset, out_sub_indptr,
+                               out_sub_indices, out_relabel, out_frontier, sizes_host, stream, gpu_edge_base,
+                               out_edge_ids);
 }
 
 int shmt_subcsr_count(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* seeds,

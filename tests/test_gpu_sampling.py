@@ -289,6 +289,36 @@ def test_edge_ids_name_the_sampled_edges(capi, ptr_dt, idx_dt):
         capi.csr_sampling_with_eids(indptr, indices, seeds, 4, False, gpu_indptr=gp, gpu_indices=gi, hashmap=hmap)
 
 
+def test_edge_ids_through_the_fused_minibatch(capi):
+    rng = np.random.default_rng(23)
+    deg = np.minimum((rng.pareto(1.2, size=5000) * 6).astype(np.int64), 700)
+    indptr_n = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices_n = np.concatenate([rng.choice(5000, size=d, replace=False) for d in deg]).astype(np.int32)
+    indptr, indices = torch.from_numpy(indptr_n).cuda(), torch.from_numpy(indices_n).cuda()
+    hot = torch.from_numpy(np.argsort(-deg)[:1200].copy()).cuda()
+    gp, gi = capi.create_subcsr(indptr, indices, hot)
+    base = capi.subcsr_edge_base(indptr, hot)
+    hmap = capi.CUCOStaticHashmap(hot, torch.arange(1200, device="cuda"), 0.5)
+    seeds = torch.from_numpy(rng.integers(0, 5000, size=777).astype(np.int32)).cuda()
+    for cached in (True, False):
+        extra = (gp, gi, hmap, base) if cached else (None, None, None, None)
+        capi.set_sampling_seed(41)
+        _, plain = capi.sample_minibatch(indptr, indices, seeds, [4, 40, 9], False, *extra[:3])
+        capi.set_sampling_seed(41)
+        front, hops = capi.sample_minibatch(indptr, indices, seeds, [4, 40, 9], False, *extra, return_eids=True)
+        cur = seeds
+        for (sp, sx, rel, nxt, eid), (sp0, sx0, rel0, nxt0) in zip(hops, plain):
+            assert torch.equal(sp, sp0) and torch.equal(sx, sx0) and torch.equal(rel, rel0) and torch.equal(nxt, nxt0)
+            assert eid.dtype == indptr.dtype and eid.numel() == sx.numel()
+            assert torch.equal(indices[eid], sx)
+            owner = torch.repeat_interleave(cur.long(), (sp[1:] - sp[:-1]))
+            assert bool(((eid >= indptr[owner]) & (eid < indptr[owner + 1])).all())
+            cur = nxt
+        assert torch.equal(front, hops[-1][3])
+    with pytest.raises(RuntimeError, match="need gpu_edge_base"):
+        capi.sample_minibatch(indptr, indices, seeds, [4], False, gp, gi, hmap, return_eids=True)
+
+
 def test_sampling_errors(capi):
     indptr = torch.tensor([0, 2], device="cuda")
     indices = torch.tensor([0, 1], device="cuda")
