@@ -186,6 +186,23 @@ def test_numa_placement_of_a_fresh_segment():
     capi.unlink_shared_mem(name)
 
 
+def test_prefault_makes_a_fresh_segment_resident():
+    from shmtensor_b200 import capi
+    name = f"shmt_test_{uuid.uuid4().hex[:8]}"
+    nbytes = 64 << 20
+    ptr, fd = capi.create_shared_mem(name, nbytes, exclusive=True)
+    try:
+        capi.prefault(ptr, nbytes, 4)
+        t = capi.open_shared_tensor(ptr, torch.uint8, (nbytes,))
+        assert int(t.sum()) == 0                       # still all zeros, now present
+        t[::4096] = 1
+        assert int(t.sum()) == nbytes // 4096
+    finally:
+        capi.release_shared_mem(name, nbytes, ptr, fd)
+    from shmtensor_b200._lib import ERR_INVALID, lib
+    assert lib.shmt_host_prefault(None, 10, 1) == ERR_INVALID
+
+
 def test_disk_tensor_read_only_and_bfloat16(tmp_path):
     from shmtensor_b200 import DiskTensor
     arr = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
