@@ -497,7 +497,7 @@ def run_ours(args) -> None:
         out = fetch(batches[i % N_BATCHES])  # held like in the timed loop: two output blocks get cached
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     region = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-    sampler = ClockSampler(local_rank, period_s=0.1)
+    sampler = ClockSampler(local_rank, period_s=0.005)
     sampler.start()  # its first NVML queries are slow and can stall a launch: let them pass now
     for i in range(3):
         out = fetch(batches[i % N_BATCHES])

@@ -149,3 +149,33 @@ def test_cpu_baseline_library_matches_oracle():
         nnz = lib.oracle_sample_hop(indptr.ctypes.data, indices.ctypes.data, 0, seeds.ctypes.data,
                                     64, 7, replace, 99, sp.ctypes.data, so.ctypes.data)
         oracle.check_sample(indptr, indices, seeds, 7, bool(replace), sp, so[:nnz], positional=True)
+
+
+def test_bulk_sample_checker_agrees_with_the_per_seed_checker():
+    """`check_sample_bulk` (whole-array form used at full size) accepts what `check_sample` accepts
+    and rejects the same corruptions."""
+    rng = np.random.default_rng(12)
+    deg = rng.integers(0, 40, size=400)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = np.concatenate([rng.permutation(3000)[:d] for d in deg]).astype(np.int32)
+    seeds = rng.integers(0, 400, size=500)
+    for k, replace in ((5, False), (64, False), (7, True)):
+        p, x = oracle.csr_sampling(indptr, indices, seeds, k, replace, np.random.default_rng(k))
+        oracle.check_sample(indptr, indices, seeds, k, replace, p, x, positional=True)
+        oracle.check_sample_bulk(indptr, indices, seeds, k, replace, p, x, distinct_rows=True)
+        picked = np.flatnonzero(np.diff(p) > 0)
+        big = [i for i in picked if deg[seeds[i]] > k] or list(picked)
+        i = int(big[0])
+        outside = x.copy()
+        outside[p[i]] = 2999 if 2999 not in indices[indptr[seeds[i]]:indptr[seeds[i] + 1]] else 2998
+        with pytest.raises(AssertionError):
+            oracle.check_sample_bulk(indptr, indices, seeds, k, replace, p, outside, distinct_rows=True)
+        if not replace and deg[seeds[i]] > k:
+            twice = x.copy()
+            twice[p[i] + 1] = twice[p[i]]
+            with pytest.raises(AssertionError, match="twice"):
+                oracle.check_sample_bulk(indptr, indices, seeds, k, replace, p, twice, distinct_rows=True)
+        wrong_ptr = p.copy()
+        wrong_ptr[-1] += 1
+        with pytest.raises(AssertionError, match="sub_indptr"):
+            oracle.check_sample_bulk(indptr, indices, seeds, k, replace, wrong_ptr, x)
