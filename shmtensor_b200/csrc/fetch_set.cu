@@ -43,11 +43,6 @@ struct RowJob {
   int64_t row_bytes;
   char* flat;             // fetch: output; set: update rows (request order)
   int rows_per_tile;      // R, 1..32
-  // insert-or-overwrite (row_scatter_bulk_kernel<STAGES, true>): idx holds the keys, `slots` the
-  // value a new key gets, `meta` the map's status / key-count words
-  const void* slots;
-  int slots64;
-  int64_t* meta;
 };
 
 template <int VEC> struct VecT;
@@ -193,10 +188,7 @@ row_gather_bulk_kernel(const RowJob job) {
 // The mirror image for set: the tile's update rows are contiguous, so ONE bulk load brings
 // them into the stage buffer; each lane then stores its row to where the probe sent it (the
 // cached copy on a hit, the host table on a miss) with its own bulk store.
-// INSERT: the row address comes from probe-or-claim (warp_insert) instead of a lookup: a key
-// that is not in the map yet takes slots[i], a known key keeps its slot, and the row goes there
-// -- the fused insert/overwrite on the same bulk-copy path as the overwrite.
-template <int STAGES, bool INSERT>
+template <int STAGES>
 __global__ void __launch_bounds__(kRowThreads)
 row_scatter_bulk_kernel(const RowJob job) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -217,22 +209,11 @@ row_scatter_bulk_kernel(const RowJob job) {
 
   char* dst_row[STAGES];  // where this lane's row of the stage goes (nullptr: nowhere)
   uint32_t parity = 0;
-  int64_t total_new = 0;
 
   auto issue = [&](int64_t tile, int s) {
     const int64_t first = tile * R;
     const int rows = (int)min((int64_t)R, job.n - first);
-    if (INSERT) {
-      const bool valid = (int)lane < rows;
-      const int64_t key = load_id(job, first, rows, lane);
-      const int64_t want = valid ? load_int(job.slots, job.slots64, first + lane) : -1;
-      int n_new = 0;
-      const int64_t got = warp_insert(job.map, key, want, valid, /*assign=*/false, job.meta, &n_new);
-      total_new += n_new;
-      dst_row[s] = (valid && got >= 0) ? job.bases[0] + got * job.row_bytes : nullptr;
-    } else {
-      dst_row[s] = resolve_row(job, first, rows, lane, slot_mask, load_id(job, first, rows, lane));
-    }
+    dst_row[s] = resolve_row(job, first, rows, lane, slot_mask, load_id(job, first, rows, lane));
     if (lane == 0) {
       mbar_arrive_expect_tx(&s_bar[warp][s], (uint32_t)rows * rb);
       bulk_load(wbase + (size_t)s * stage_bytes, job.flat + first * job.row_bytes, (uint32_t)rows * rb,
@@ -272,8 +253,6 @@ row_scatter_bulk_kernel(const RowJob job) {
     }
   }
   bulk_wait_read<0>();
-  if (INSERT && lane == 0 && total_new)
-    atomicAdd(reinterpret_cast<unsigned long long*>(job.meta + 1), (unsigned long long)total_new);
 }
 
 // SET == false: table row -> flat (fetch).  SET == true: flat -> table row.
@@ -459,11 +438,9 @@ static int bulk_rows_per_stage(int64_t row_bytes, int vec, int R_small) {
   return (int)r;
 }
 
-template <int MODE>  // 0 gather, 1 scatter, 2 insert + scatter
+template <bool SET>
 static int launch_bulk(RowJob job, int R, cudaStream_t s) {
-  auto kernel = MODE == 2 ? row_scatter_bulk_kernel<kBulkStages, true>
-                          : (MODE == 1 ? row_scatter_bulk_kernel<kBulkStages, false>
-                                       : row_gather_bulk_kernel<kBulkStages>);
+  auto kernel = SET ? row_scatter_bulk_kernel<kBulkStages> : row_gather_bulk_kernel<kBulkStages>;
   static bool configured[64] = {false};
   int dev = 0;
   SHMT_CUDA_TRY(cudaGetDevice(&dev));
@@ -485,7 +462,7 @@ static int launch_row_copy(const RowJob& job, int vec, cudaStream_t s) {
   {
     static const bool no_bulk = getenv("SHMT_NO_BULK") != nullptr;
     const int R = no_bulk ? 0 : bulk_rows_per_stage(job.row_bytes, vec, job.rows_per_tile);
-    if (R >= 1) return launch_bulk<SET ? 1 : 0>(job, R, s);
+    if (R >= 1) return launch_bulk<SET>(job, R, s);
   }
   switch (vec) {
     case 16: return launch_lsu<16, SET>(job, s);
@@ -638,25 +615,6 @@ int shmt_insert_set(shmt_map* map, void* gpu_base, const void* keys, int key_dty
   const int k64 = key_dtype == SHMT_I64, s64 = slots_dtype == SHMT_I64;
   // the status word reports on this call only (see shmt_map_insert)
   SHMT_CUDA_TRY(cudaMemsetAsync(map->d_meta, 0, sizeof(int64_t), s));
-  static const bool no_bulk = getenv("SHMT_NO_BULK") != nullptr;
-  const int bulk_rows = no_bulk ? 0 : bulk_rows_per_stage(row_bytes, vec, R);
-  if (bulk_rows >= 1) {
-    // rows that are 16-byte units: probe-or-claim, then the rows through the bulk-copy ring
-    RowJob job{};
-    job.map = map->view;
-    job.mode = MODE_MAP;
-    job.bases[0] = g;
-    job.owner_shift = 62;
-    job.idx = keys;
-    job.idx64 = k64;
-    job.n = n;
-    job.row_bytes = row_bytes;
-    job.flat = const_cast<char*>(u);
-    job.slots = slots;
-    job.slots64 = s64;
-    job.meta = map->d_meta;
-    if (int rc = launch_bulk<2>(job, bulk_rows, s)) return rc;
-  } else
   switch (vec) {
     case 16: insert_set_kernel<16, 8><<<grid, kRowThreads, 0, s>>>(map->view, g, keys, k64, slots, s64, n, row_bytes, u, R, map->d_meta); break;
     case 8: insert_set_kernel<8, 8><<<grid, kRowThreads, 0, s>>>(map->view, g, keys, k64, slots, s64, n, row_bytes, u, R, map->d_meta); break;
