@@ -1304,8 +1304,8 @@ def minibatch_workload(n_nodes, n_edges, divisor) -> str:
     return ("end-to-end mini-batch over a partitioned cache (config 4" + ("" if divisor == 1 else f", scaled 1:{divisor}")
             + f"): power-law CSR {n_nodes:,} nodes / {n_edges:,} edges (degree tail Zipf(2.0), int64 indptr, int32 "
             f"indices), {C4_DIM}-d float32 features ({n_nodes * C4_DIM * 4 / 1e9:.1f} GB), graph and features in POSIX shared "
-            "memory mapped and pinned by every rank; the top 40% of nodes by degree have their adjacency cached on "
-            "every GPU and their features hash-partitioned over the GPUs; per GPU and step 1,024 seeds, fan-out "
+            f"memory mapped and pinned by every rank; every GPU holds the row offsets ({n_nodes * 8 / 1e9:.1f} GB) and the adjacency of the "
+            "top 40% of nodes by degree, whose features are hash-partitioned over the GPUs; per GPU and step 1,024 seeds, fan-out "
             "[15,10,5], then the features of every sampled node are fetched (remote hits over NVLink, misses over UVA)")
 
 
@@ -1367,7 +1367,7 @@ def minibatch_object(steps: int, rank: int, local_rank: int, world: int) -> dict
     del deg
     indices_dev = indices.to(dev, non_blocking=True)
     gp, gi = capi.create_subcsr(indptr_dev, indices_dev, hot)
-    del indices_dev, indptr_dev
+    del indices_dev   # the row offsets (0.9 GB) stay on the GPU: see `step`
     gmap = capi.CUCOStaticHashmap(hot.int(), torch.arange(n_cached, dtype=torch.int32, device=dev), 0.8)
     fcache = PartitionedFeatureCache(feats, hot, replicate=0)   # neighbours are uniform over the nodes: no hot head
     fcache.warm()
@@ -1383,9 +1383,12 @@ def minibatch_object(steps: int, rank: int, local_rank: int, world: int) -> dict
     capi.set_sampling_seed(7777 + rank)
     fan = list(reversed(FANOUT))
 
+    # The sampler reads row offsets from the GPU copy (what GPUSamplingDataloader.create_cache does when
+    # they fit in a quarter of its budget: a row whose adjacency is in host memory then costs one trip over
+    # the host link instead of two) and the adjacency of rows that are not cached from the shared host array.
     def step(i):
         seeds_buf.copy_(seeds_host[i % 32], non_blocking=True)
-        frontier, hops = capi.sample_minibatch(indptr, indices, seeds_buf, fan, False, gp, gi, gmap)
+        frontier, hops = capi.sample_minibatch(indptr_dev, indices, seeds_buf, fan, False, gp, gi, gmap)
         rows = fcache.fetch(frontier)
         return sum(h[1].numel() for h in hops), frontier, rows, hops
 
@@ -1418,7 +1421,7 @@ def minibatch_object(steps: int, rank: int, local_rank: int, world: int) -> dict
     edges = n_rows = 0
     for i in range(steps):
         seeds_buf.copy_(seeds_host[i % 32], non_blocking=True)
-        frontier, hops = capi.sample_minibatch(indptr, indices, seeds_buf, fan, False, gp, gi, gmap)
+        frontier, hops = capi.sample_minibatch(indptr_dev, indices, seeds_buf, fan, False, gp, gi, gmap)
         mid[2 * i].record(stream)
         rows = fcache.fetch(frontier)
         mid[2 * i + 1].record(stream)
@@ -1495,7 +1498,7 @@ def minibatch_object(steps: int, rank: int, local_rank: int, world: int) -> dict
                                          "torch.index_select on the shared feature table"}
     torch.cuda.synchronize()
     fcache.close()
-    del fcache, gp, gi, gmap, indptr, indices, feats, indptr_n, indices_n, rows, frontier
+    del fcache, gp, gi, gmap, indptr, indices, feats, indptr_n, indices_n, rows, frontier, indptr_dev
     shm_ptr = shm_idx = shm_feat = None
     torch.cuda.empty_cache()
     return obj
