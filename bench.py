@@ -556,7 +556,50 @@ def run_ours(args) -> None:
             ms = t_.item()
         return ms, wall
 
-    e2e_ms, e2e_wall_ms = e2e_loop(lambda res: tail.copy_(res[-1], non_blocking=True), args.steps)
+    e2e_serial_ms, _ = e2e_loop(lambda res: tail.copy_(res[-1], non_blocking=True), args.steps)
+
+    # the same with the next step's ids prefetched: they cross to the GPU on a second stream while
+    # the current step's fetch runs (two id buffers), as a loader that knows its next batch does;
+    # the host still waits for every step's read-back before it issues the next step
+    pre_stream = torch.cuda.Stream()
+    ids_two = [torch.empty(BATCH, dtype=torch.int64, device=dev) for _ in range(2)]
+    ids_ready = [torch.cuda.Event() for _ in range(2)]
+    ids_free = [torch.cuda.Event() for _ in range(2)]
+
+    def e2e_prefetched(steps):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        def prefetch(j):
+            pre_stream.wait_event(ids_free[j % 2])     # the fetch that last read this buffer is done
+            with torch.cuda.stream(pre_stream):
+                ids_two[j % 2].copy_(batches_host[j % N_BATCHES], non_blocking=True)
+                ids_ready[j % 2].record(pre_stream)
+        for e in ids_free:
+            e.record(stream)
+        t0 = time.perf_counter()
+        region[0].record(stream)
+        prefetch(0)
+        for i in range(steps):
+            if i + 1 < steps:
+                prefetch(i + 1)
+            stream.wait_event(ids_ready[i % 2])
+            res = fetch(ids_two[i % 2])
+            ids_free[i % 2].record(stream)
+            tail.copy_(res[-1], non_blocking=True)
+            stream.synchronize()
+        region[1].record(stream)
+        torch.cuda.synchronize()
+        ms = region[0].elapsed_time(region[1]) / steps
+        wall = (time.perf_counter() - t0) * 1e3 / steps
+        if world > 1:
+            t_ = torch.tensor([ms], device=dev)
+            dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+            ms = t_.item()
+        return ms, wall
+
+    e2e_prefetched(3)
+    e2e_ms, e2e_wall_ms = e2e_prefetched(args.steps)
     e2e_value = world * BATCH * ROW_BYTES / (e2e_ms * 1e6)
     # ... and with the whole 200 MB result copied out to pinned host memory, which is where the
     # CPU arm's result lies: one step after the other, and pipelined (the copy of step i runs on a
@@ -614,7 +657,11 @@ def run_ours(args) -> None:
         "e2e": {"value": round(e2e_value, 2), "unit": UNIT, "h2d_bytes_per_step": BATCH * 8,
                 "d2h_bytes_per_step": DIM * 4, "ms_per_step": round(e2e_ms, 5),
                 "wall_ms_per_step": round(e2e_wall_ms, 5),
-                "result_in": "GPU memory (as the reference's cache_fetch returns it); one row read back"},
+                "result_in": "GPU memory (as the reference's cache_fetch returns it); one row read back",
+                "how": "every step: 4 MB of ids from pinned host memory (copied on a second stream while the step "
+                       "before runs), the public call, one fetched row read back, the host waits for it",
+                "ids_copied_in_line": {"value": round(world * BATCH * ROW_BYTES / (e2e_serial_ms * 1e6), 2),
+                                       "ms_per_step": round(e2e_serial_ms, 5)}},
         "e2e_host_result": {"value": round(world * BATCH * ROW_BYTES / (e2e_pipe_ms * 1e6), 2), "unit": UNIT,
                             "h2d_bytes_per_step": BATCH * 8, "d2h_bytes_per_step": BATCH * ROW_BYTES,
                             "ms_per_step": round(e2e_pipe_ms, 5), "steps": host_steps,
