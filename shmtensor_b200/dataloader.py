@@ -18,25 +18,28 @@ import torch.distributed as dist
 from . import capi
 
 
-def _dgl_block(sub_indptr, relabel_indices, num_src, num_dst):
-    """CSC block as python/shmtensor/sampling.py:9-20 builds it (needs dgl)."""
+def _dgl_block(sub_indptr, relabel_indices, num_src, num_dst, edge_ids=None):
+    """CSC block as python/shmtensor/sampling.py:9-20 builds it (needs dgl).  The reference hands
+    an empty edge-id tensor over; with ``with_edge_ids`` the block carries the real ones."""
     import dgl  # noqa: deferred so that the package works without dgl
     from dgl.heterograph import DGLBlock
     hgidx = dgl.heterograph_index.create_unitgraph_from_csr(
-        2, num_src, num_dst, sub_indptr, relabel_indices, torch.Tensor(),
-        formats=['coo', 'csr', 'csc'], transpose=True)
+        2, num_src, num_dst, sub_indptr, relabel_indices,
+        torch.Tensor() if edge_ids is None else edge_ids, formats=['coo', 'csr', 'csc'], transpose=True)
     return DGLBlock(hgidx, (['_N'], ['_N']), ['_E'])
 
 
-def _plain_block(sub_indptr, relabel_indices, num_src, num_dst):
-    return sub_indptr, relabel_indices, num_src, num_dst
+def _plain_block(sub_indptr, relabel_indices, num_src, num_dst, edge_ids=None):
+    if edge_ids is None:
+        return sub_indptr, relabel_indices, num_src, num_dst
+    return sub_indptr, relabel_indices, num_src, num_dst, edge_ids
 
 
 class GPUSamplingDataloader:
 
     def __init__(self, indptr, indices, seeds, batchsize, num_picks, replace=False,
                  use_ddp=False, shuffle=True, drop_last=False,
-                 block_fn: Optional[Callable] = None, fused: bool = True):
+                 block_fn: Optional[Callable] = None, fused: bool = True, with_edge_ids: bool = False):
         self.indptr, self.indices = indptr, indices
         self.batchsize, self.num_picks, self.replace = batchsize, num_picks, replace
         self.use_ddp, self.shuffle, self.drop_last = use_ddp, shuffle, drop_last
@@ -44,8 +47,11 @@ class GPUSamplingDataloader:
 
         # fused: one native call per mini-batch; False keeps the reference's call-per-hop loop
         self.fused = fused
+        # with_edge_ids (not in the reference): every block also gets the edge ids of its sampled
+        # neighbours (positions in `indices`), passed to block_fn as a fifth argument
+        self.with_edge_ids = with_edge_ids
         self.has_cache = False
-        self.gpu_indptr = self.gpu_indices = self.hashmap = None
+        self.gpu_indptr = self.gpu_indices = self.hashmap = self.gpu_edge_base = None
 
         # host-resident CSR arrays are registered so kernels can read them in place
         for t in (self.indptr, self.indices):
@@ -118,17 +124,29 @@ class GPUSamplingDataloader:
                                             list(reversed(self.num_picks)), self.replace,
                                             self.gpu_indptr if self.has_cache else None,
                                             self.gpu_indices if self.has_cache else None,
-                                            self.hashmap if self.has_cache else None)
+                                            self.hashmap if self.has_cache else None,
+                                            self.gpu_edge_base if self.has_cache else None,
+                                            return_eids=self.with_edge_ids)
             n_dst = seeds.numel()
-            for sub_indptr, _, relabel_indices, frontier in hops:
-                blocks.insert(0, self.block_fn(sub_indptr, relabel_indices, frontier.numel(), n_dst))
+            for hop in hops:
+                sub_indptr, relabel_indices, frontier = hop[0], hop[2], hop[3]
+                extra = (hop[4],) if self.with_edge_ids else ()
+                blocks.insert(0, self.block_fn(sub_indptr, relabel_indices, frontier.numel(), n_dst, *extra))
                 n_dst = frontier.numel()
             return hops[-1][3].to(seeds.dtype), output_nodes, blocks
         for num_pick in reversed(self.num_picks):
-            sub_indptr, sub_indices = self._hop(seeds, num_pick)
+            if self.with_edge_ids:
+                cached = dict(gpu_indptr=self.gpu_indptr, gpu_indices=self.gpu_indices,
+                              gpu_edge_base=self.gpu_edge_base, hashmap=self.hashmap) if self.has_cache else {}
+                sub_indptr, sub_indices, eids = capi.csr_sampling_with_eids(self.indptr, self.indices, seeds,
+                                                                           num_pick, self.replace, **cached)
+                extra = (eids,)
+            else:
+                sub_indptr, sub_indices = self._hop(seeds, num_pick)
+                extra = ()
             frontier, (_, relabel_indices) = capi.tensor_relabel([seeds, sub_indices])
             blocks.insert(0, self.block_fn(sub_indptr, relabel_indices, frontier.numel(),
-                                           seeds.numel()))
+                                           seeds.numel(), *extra))
             seeds = frontier
         return seeds, output_nodes, blocks
 
@@ -162,6 +180,10 @@ class GPUSamplingDataloader:
         candidates = candidates[:n_rows].cuda()
         if candidates.numel() == 0:
             return
+        if self.with_edge_ids and replaceable:
+            raise RuntimeError("create_cache: edge ids are kept for a compact cache only (replaceable=False)")
+        if self.with_edge_ids:
+            self.gpu_edge_base = capi.subcsr_edge_base(self.indptr, candidates)
         if replaceable:
             from .graph_cache import GraphCache
             self.graph_cache = GraphCache(self.indptr, self.indices, candidates)
@@ -188,7 +210,7 @@ class GPUSamplingDataloader:
 
     def clear_cache(self):
         self.has_cache = False
-        self.gpu_indptr = self.gpu_indices = self.hashmap = None
+        self.gpu_indptr = self.gpu_indices = self.hashmap = self.gpu_edge_base = None
         self.graph_cache = None
 
     def presampling(self):

@@ -121,3 +121,32 @@ def test_fused_minibatch_equals_hop_by_hop(cached, idx_dtype):
     finally:
         capi.unpin_memory(indptr)
         capi.unpin_memory(indices)
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_blocks_with_edge_ids(fused):
+    """`with_edge_ids`: every block carries, for each sampled neighbour, its position in `indices`,
+    with and without a cache (the reference passes an empty edge-id tensor to its block builder)."""
+    from shmtensor_b200 import GPUSamplingDataloader
+    rng = np.random.default_rng(6)
+    deg = np.minimum((rng.pareto(1.3, size=3000) * 5).astype(np.int64), 300)
+    indptr_n = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices_n = rng.integers(0, 3000, size=int(indptr_n[-1])).astype(np.int64)
+    indptr, indices = torch.from_numpy(indptr_n), torch.from_numpy(indices_n)
+    dl = GPUSamplingDataloader(indptr, indices, torch.arange(0, 1024), 256, [6, 3], shuffle=False, fused=fused,
+                               with_edge_ids=True)
+    dl.create_cache(int(indices.nbytes * 0.4), torch.from_numpy(deg.astype(np.float32)))
+    assert dl.has_cache and dl.gpu_edge_base is not None
+    flat = torch.from_numpy(indices_n).cuda()
+    n = 0
+    for frontier, output_nodes, blocks in dl:
+        # blocks[0] is the outermost hop; walk from the seeds outwards
+        src = frontier
+        for sub_indptr, relabel_indices, n_src, n_dst, eids in blocks:
+            assert eids.numel() == relabel_indices.numel() == int(sub_indptr[-1])
+            # an edge id names the neighbour the relabelled index stands for
+            assert torch.equal(flat[eids], src[relabel_indices.long()].long())
+            src = src[:n_dst]
+        n += 1
+    assert n == 4
+    del dl
