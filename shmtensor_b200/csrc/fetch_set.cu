@@ -373,82 +373,6 @@ insert_set_kernel(MapView map, char* gpu_base, const void* keys, int keys64, con
     atomicAdd(reinterpret_cast<unsigned long long*>(meta + 1), (unsigned long long)total_new);
 }
 
-// The same through the bulk-copy ring, for rows that are 16-byte units.  A warp inserts 32 keys
-// at once (the cooperative insert works on 32 keys per call, whatever the row size), then moves
-// the tile's 32 update rows -- contiguous in `update` -- through a ring of STAGES shared-memory
-// buffers of C rows each: one bulk load per chunk, then the C lanes that own its rows store them
-// with one bulk store each to the slots the insert returned.  Chunk 0 of a tile is already in
-// flight while its keys are inserted.
-template <int STAGES>
-__global__ void __launch_bounds__(kRowThreads)
-insert_set_bulk_kernel(MapView map, char* gpu_base, const void* keys, int keys64, const void* slots,
-                       int slots64, int64_t n, uint32_t rb, const char* update, int C, int64_t* meta) {
-  extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ __align__(8) uint64_t s_bar[kRowWarps][STAGES];
-  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t stage_bytes = (uint32_t)C * rb;
-  unsigned char* wbase = smem_raw + (size_t)warp * STAGES * stage_bytes;
-  const int64_t n_tiles = (n + 31) / 32;
-  if (lane == 0)
-    for (int s = 0; s < STAGES; ++s) mbar_init(&s_bar[warp][s], 1);
-  mbar_init_fence();
-  __syncwarp();
-  uint32_t parity = 0;  // bit s: phase of stage s to wait for next
-  uint32_t g = 0;       // chunks this warp has issued so far: chunk number g uses stage g % STAGES
-  int64_t total_new = 0;
-  bool ok = true;
-  for (int64_t tile = (int64_t)blockIdx.x * kRowWarps + warp; tile < n_tiles && ok;
-       tile += (int64_t)gridDim.x * kRowWarps) {
-    const int64_t first = tile * 32;
-    const int rows = (int)min((int64_t)32, n - first);
-    const int n_chunks = (rows + C - 1) / C;
-    auto issue = [&](int c) {  // chunk c of this tile into the next stage of the ring
-      const int s = (int)((g + (uint32_t)c) % STAGES);
-      const uint32_t bytes = (uint32_t)min(C, rows - c * C) * rb;
-      if (lane == 0) {
-        mbar_arrive_expect_tx(&s_bar[warp][s], bytes);
-        bulk_load(wbase + (size_t)s * stage_bytes, update + (first + (int64_t)c * C) * rb, bytes, &s_bar[warp][s]);
-      }
-    };
-    bulk_wait_read<0>();  // every lane's stores out of the ring have read it
-    __syncwarp();
-    for (int c = 0; c < STAGES - 1 && c < n_chunks; ++c) issue(c);
-    const bool valid = (int)lane < rows;
-    const int64_t k = valid ? load_int(keys, keys64, first + lane) : kEmptyKey;
-    const int64_t want = valid ? load_int(slots, slots64, first + lane) : -1;
-    int n_new = 0;
-    const int64_t got = warp_insert(map, k, want, valid, /*assign=*/false, meta, &n_new);
-    total_new += n_new;
-    char* dst = (valid && got >= 0) ? gpu_base + got * (int64_t)rb : nullptr;
-    for (int c = 0; c < n_chunks && ok; ++c) {
-      const int ahead = c + STAGES - 1;
-      if (ahead < n_chunks) {
-        bulk_wait_read<0>();
-        __syncwarp();
-        issue(ahead);
-      }
-      const int s = (int)((g + (uint32_t)c) % STAGES);
-      if (!mbar_wait_bounded(&s_bar[warp][s], (parity >> s) & 1u)) {
-        atomicExch(&g_device_fault, 1);
-        ok = false;
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      parity ^= 1u << s;
-      if (ok) {
-        async_proxy_fence();
-        const int mine = (int)lane - c * C;
-        if (dst && mine >= 0 && mine < C)
-          bulk_store(dst, wbase + (size_t)s * stage_bytes + (size_t)mine * rb, rb);
-        bulk_commit();
-      }
-    }
-    g += (uint32_t)n_chunks;
-  }
-  bulk_wait_read<0>();
-  if (lane == 0 && total_new)
-    atomicAdd(reinterpret_cast<unsigned long long*>(meta + 1), (unsigned long long)total_new);
-}
-
 // ---- host side ---------------------------------------------------------------
 
 static int pick_vec(int64_t row_bytes, std::initializer_list<const void*> ptrs) {
@@ -691,25 +615,6 @@ int shmt_insert_set(shmt_map* map, void* gpu_base, const void* keys, int key_dty
   const int k64 = key_dtype == SHMT_I64, s64 = slots_dtype == SHMT_I64;
   // the status word reports on this call only (see shmt_map_insert)
   SHMT_CUDA_TRY(cudaMemsetAsync(map->d_meta, 0, sizeof(int64_t), s));
-  static const int ring_mode = [] {  // SHMT_INSERT_RING=0 keeps the copy on the LSU path
-    const char* e = getenv("SHMT_INSERT_RING");
-    return e ? atoi(e) : 1;
-  }();
-  const int chunk_rows = (ring_mode && R == 32) ? bulk_rows_per_stage(row_bytes, vec, 32) : 0;
-  if (chunk_rows >= 1) {
-    auto kernel = insert_set_bulk_kernel<kBulkStages>;
-    static bool configured[64] = {false};
-    int dev = 0;
-    SHMT_CUDA_TRY(cudaGetDevice(&dev));
-    if (dev < 64 && !configured[dev]) {
-      SHMT_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBulkSmemMax));
-      configured[dev] = true;
-    }
-    const size_t smem = (size_t)kRowWarps * kBulkStages * chunk_rows * row_bytes;
-    const unsigned blocks = grid_for_tiles(kernel, n, 32, smem);
-    kernel<<<blocks, kRowThreads, smem, s>>>(map->view, g, keys, k64, slots, s64, n, (uint32_t)row_bytes, u,
-                                             chunk_rows, map->d_meta);
-  } else
   switch (vec) {
     case 16: insert_set_kernel<16, 8><<<grid, kRowThreads, 0, s>>>(map->view, g, keys, k64, slots, s64, n, row_bytes, u, R, map->d_meta); break;
     case 8: insert_set_kernel<8, 8><<<grid, kRowThreads, 0, s>>>(map->view, g, keys, k64, slots, s64, n, row_bytes, u, R, map->d_meta); break;
