@@ -1,4 +1,5 @@
-// In-place prefix sum: one kernel, decoupled look-back between 64 KB tiles.
+// In-place prefix sum in one pass with decoupled look-back: a ticketed kernel over 64 KB tiles
+// for small inputs, a persistent thread-block-cluster kernel with early sums for large ones.
 // Semantics follow cub_exclusiveSum (reference src/cache_graph_sampling.cu:30-45)
 // and the intended meaning of thrust_scan (reference src/thrust_scan.cu:9-18,
 // whose own lambda races); integer arithmetic wraps.
