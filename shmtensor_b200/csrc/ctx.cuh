@@ -25,7 +25,7 @@ struct shmt_ctx {
 namespace shmt {
 
 constexpr int kCtxWords = 128;
-enum : int { W_STATUS = 0, W_RESULT = 1, W_TICKET = 2, W_DONE = 3 };
+enum : int { W_STATUS = 0, W_RESULT = 1, W_TICKET = 2, W_DONE = 3, W_RANGE = 4 };
 
 // Make sure ctx->region() holds at least `bytes` (256-byte aligned base).
 int ctx_reserve(shmt_ctx* ctx, size_t bytes);

@@ -42,7 +42,10 @@ map_erase_kernel(MapView m, const void* __restrict__ keys, int keys64, int64_t n
     atomicAdd(reinterpret_cast<unsigned long long*>(meta + 1), 0ULL - (unsigned long long)removed);
 }
 
-__global__ void __launch_bounds__(kMapThreads)
+#ifndef SHMT_QUERY_CTAS
+#define SHMT_QUERY_CTAS 4
+#endif
+__global__ void __launch_bounds__(kMapThreads, SHMT_QUERY_CTAS)
 map_query_kernel(MapView m, const void* __restrict__ req, int req64, int64_t n,
                  void* __restrict__ out, int out64) {
   const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;

@@ -16,6 +16,8 @@
 
 namespace shmt {
 
+constexpr uint64_t kRelDirectMinTableBytes = 32ull << 20;
+
 __device__ __forceinline__ void resolve_sizes(Parts& ps, int64_t* numel) {
   if (ps.dev_n1) {  // |part 0| from the device if given there, else the host's start[1]
     const int64_t a = ps.dev_n0 ? *ps.dev_n0 : ps.start[1], b = *ps.dev_n1;
@@ -34,8 +36,29 @@ __device__ __forceinline__ int64_t part_elem(const Parts& ps, int64_t i) {
   return load_int(ps.ptr[p], ps.is64, i - ps.start[p]);
 }
 
+// Largest id of the input, read as an unsigned number (so that a negative id counts as huge).
 __global__ void __launch_bounds__(kRelThreads)
-relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* status) {
+relabel_range_kernel(Parts ps, unsigned long long* range) {
+  pdl_prologue();
+  int64_t numel;
+  resolve_sizes(ps, &numel);
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  unsigned long long m = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += 4 * stride) {
+    long long v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = i + u * stride < numel ? part_elem(ps, i + u * stride) : 0;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) m = max(m, (unsigned long long)v[u]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m) atomicMax(range, m);
+}
+
+__global__ void __launch_bounds__(kRelThreads)
+relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* status,
+                      const unsigned long long* __restrict__ range) {
   pdl_prologue();
   int64_t numel;
   resolve_sizes(ps, &numel);
@@ -43,10 +66,15 @@ relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* sta
   // much of it as this input needs (load <= 0.5), so a small input stays in a small,
   // cache-resident part.  Only the inserting code hashes; the rest follows recorded slots.
   const uint32_t mask = relabel_mask_for(numel, t.mask);
+  // ids that all fit the table are their own slots: a frontier of densely numbered nodes then
+  // touches a compact, cache-resident part of the table instead of one line per distinct id
+  const bool direct = range != nullptr && *range <= (unsigned long long)mask;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
-    const uint32_t pos = relabel_insert_one(t.slots, mask, part_elem(ps, i), (unsigned)i, status);
-    store_int(out, ps.is64, i, (int64_t)pos);
+    bool maybe_first;
+    const uint32_t pos = relabel_insert_one(t.slots, mask, part_elem(ps, i), (unsigned)i, status, &maybe_first,
+                                            direct);
+    store_int(out, ps.is64, i, relabel_pack(pos, maybe_first, ps.is64, t.mask));
   }
 }
 
@@ -79,8 +107,10 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
     const int64_t i = base + j;
     is_first[j] = false;
     if (i < numel) {
-      pos[j] = (uint32_t)load_int(slot_of, ps.is64, i);
-      is_first[j] = __ldcg(&t.slots[pos[j]].first) == (unsigned)i;
+      // only an element the inserting pass did not rule out has to look at its slot
+      bool maybe_first;
+      pos[j] = relabel_unpack(slot_of, ps.is64, i, t.mask, &maybe_first);
+      is_first[j] = maybe_first && __ldcg(&t.slots[pos[j]].first) == (unsigned)i;
     }
     cnt += is_first[j];
   }
@@ -112,13 +142,14 @@ relabel_remap_kernel(Parts ps, RelTable t, void* out) {
   resolve_sizes(ps, &numel);
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < numel; i += stride) {
-    const int64_t pos = ps.is64 ? reinterpret_cast<const long long*>(out)[i]
-                                : (int64_t) reinterpret_cast<const int*>(out)[i];
-    store_int(out, ps.is64, i, (int64_t)__ldcg(&t.slots[pos].newid));
-    // leave the slot empty for the next call (every duplicate writes the same values); the new id
-    // stays, because another element of the same id may not have read it yet
-    t.slots[pos].key = kEmptyKey;
-    t.slots[pos].first = 0xFFFFFFFFu;
+    bool maybe_first;
+    const uint32_t pos = relabel_unpack(out, ps.is64, i, t.mask, &maybe_first);
+    const uint4 slot = __ldcg(reinterpret_cast<const uint4*>(t.slots + pos));  // key lo, key hi, first, newid
+    store_int(out, ps.is64, i, (int64_t)slot.w);
+    // leave the slot empty for the next call: the id's first occurrence does it, once (the new id
+    // stays, because another element of the same id may not have read it yet)
+    if (maybe_first && slot.z == (unsigned)i)
+      *reinterpret_cast<uint4*>(t.slots + pos) = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, slot.w);
   }
 }
 
@@ -141,15 +172,19 @@ int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t 
 
 int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
                    int64_t* status, int64_t* result, cudaStream_t s, bool inserted, bool pdl,
-                   const HostPost* post) {
+                   const HostPost* post, int64_t* range) {
   RelTable t;
   if (int rc = relabel_table(ctx, numel_bound, &t, s)) return rc;
   const int64_t n_tiles = (numel_bound + kRelTile - 1) / kRelTile;
   int64_t blocks = (numel_bound + kRelThreads - 1) / kRelThreads;
   const int64_t cap_blocks = (int64_t)sm_count() * 16;
   const unsigned grid = (unsigned)(blocks < cap_blocks ? blocks : cap_blocks);
-  if (!inserted)
-    SHMT_CUDA_TRY(launch_kernel(pdl, relabel_insert_kernel, grid, kRelThreads, 0, s, ps, t, out_relabel, status));
+  if (!inserted) {
+    unsigned long long* r = reinterpret_cast<unsigned long long*>(range);
+    if (r) SHMT_CUDA_TRY(launch_kernel(pdl, relabel_range_kernel, grid, kRelThreads, 0, s, ps, r));
+    SHMT_CUDA_TRY(launch_kernel(pdl, relabel_insert_kernel, grid, kRelThreads, 0, s, ps, t, out_relabel, status,
+                                (const unsigned long long*)r));
+  }
   SHMT_CUDA_TRY(launch_kernel(pdl, relabel_compact_kernel, (unsigned)n_tiles, kRelThreads, 0, s, ps, t,
                               (const void*)out_relabel, out_unique, st, ticket, status, result,
                               post ? *post : HostPost{}));
@@ -201,9 +236,11 @@ extern "C" int shmt_relabel(shmt_ctx* ctx, const void* const* parts, const int64
   // kernel runs; the next user of the context waits for that kernel first
   HostPost post{};
   if (n_unique_host) post = ctx_begin_post(ctx, w, 4, w + W_DONE);
+  // a table that fits the L2 cache gains nothing from compact slots; a larger one may
+  int64_t* range = relabel_capacity(numel) * sizeof(RelSlot) > kRelDirectMinTableBytes ? w + W_RANGE : nullptr;
   if (int rc = launch_relabel(ctx, ps, numel, out_unique, out_relabel, st, w + W_TICKET,
                               w + W_STATUS, w + W_RESULT, s, false, false,
-                              n_unique_host ? &post : nullptr))
+                              n_unique_host ? &post : nullptr, range))
     return rc;
   if (n_unique_host) {
     if (int rc = ctx_mark_tail(ctx, s)) return rc;

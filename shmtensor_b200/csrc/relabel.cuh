@@ -44,17 +44,56 @@ __device__ __forceinline__ uint32_t relabel_mask_for(int64_t numel, uint32_t tab
   return want < table_mask ? want : table_mask;
 }
 
+// What the inserting pass leaves per element in the output array: the element's slot, plus a mark
+// on the elements that are certainly NOT the first occurrence of their id (they met a smaller index
+// in the slot), so that the later passes need not look at the slot to know.  64-bit arrays always
+// have room for the mark; 32-bit ones as long as the table has fewer than 2^31 slots.
+constexpr unsigned long long kRelNotFirst64 = 1ull << 40;
+constexpr uint32_t kRelNotFirst32 = 0x80000000u;
+
+__device__ __forceinline__ int64_t relabel_pack(uint32_t pos, bool maybe_first, bool is64, uint32_t table_mask) {
+  if (is64) return (int64_t)((unsigned long long)pos | (maybe_first ? 0ull : kRelNotFirst64));
+  if (table_mask < kRelNotFirst32 && !maybe_first) pos |= kRelNotFirst32;
+  return (int64_t)(int32_t)pos;
+}
+
+__device__ __forceinline__ uint32_t relabel_unpack(const void* slot_of, bool is64, int64_t i, uint32_t table_mask,
+                                                   bool* maybe_first) {
+  if (is64) {
+    const unsigned long long raw = reinterpret_cast<const unsigned long long*>(slot_of)[i];
+    *maybe_first = !(raw & kRelNotFirst64);
+    return (uint32_t)raw;
+  }
+  const uint32_t raw = reinterpret_cast<const uint32_t*>(slot_of)[i];
+  if (table_mask < kRelNotFirst32) {
+    *maybe_first = !(raw & kRelNotFirst32);
+    return raw & ~kRelNotFirst32;
+  }
+  *maybe_first = true;
+  return raw;
+}
+
 // Claim (or find) the slot of `key`, record `i` as a candidate first occurrence, and return
-// the slot.  Linear probing from mix64(key) & mask; bounded by the table size.
+// the slot.  Linear probing from mix64(key) & mask; bounded by the table size.  *maybe_first is
+// false when the slot was seen to hold a smaller index (then `i` cannot be the first occurrence).
+// `direct`: every id of the input is known to lie in [0, mask], so the id itself is its slot:
+// neighbouring ids share cache lines and nothing collides.
 __device__ __forceinline__ uint32_t relabel_insert_one(RelSlot* slots, uint32_t mask, long long key,
-                                                       unsigned i, int64_t* status) {
-  uint32_t pos = (uint32_t)mix64((uint64_t)key) & mask;
+                                                       unsigned i, int64_t* status, bool* maybe_first,
+                                                       bool direct = false) {
+  uint32_t pos = direct ? (uint32_t)key : (uint32_t)mix64((uint64_t)key) & mask;
   uint32_t steps = 0;
+  unsigned seen_first;
   while (true) {
-    long long cur = __ldcg(&slots[pos].key);
-    if (cur == kEmptyKey)
+    // key and first index come with one 16-byte load
+    const uint4 s = __ldcg(reinterpret_cast<const uint4*>(slots + pos));
+    long long cur = (long long)(((unsigned long long)s.y << 32) | s.x);
+    seen_first = s.z;
+    if (cur == kEmptyKey) {
       cur = (long long)atomicCAS(reinterpret_cast<unsigned long long*>(&slots[pos].key),
                                  (unsigned long long)kEmptyKey, (unsigned long long)key);
+      seen_first = 0xFFFFFFFFu;  // claimed just now, by this element or by another one of the same id
+    }
     if (cur == kEmptyKey || cur == key) break;
     pos = (pos + 1) & mask;
     if (++steps > mask) {  // cannot happen at load <= 0.5; bounded all the same
@@ -62,7 +101,12 @@ __device__ __forceinline__ uint32_t relabel_insert_one(RelSlot* slots, uint32_t 
       break;
     }
   }
-  atomicMin(&slots[pos].first, i);
+  // `first` only ever goes down: when the index seen there is already smaller than this one the
+  // atomic would change nothing, and most elements of a frontier are such repeats.  Nothing waits
+  // for the atomic's result: an element that lowers the index, or loses to a still smaller one, is
+  // simply left among the candidates.
+  *maybe_first = seen_first > i;
+  if (*maybe_first) atomicMin(&slots[pos].first, i);
   return pos;
 }
 #endif
@@ -77,9 +121,11 @@ uint64_t relabel_capacity(int64_t numel_bound);
 // of the ids (the fused sampling kernel), so only the compact and remap kernels run.
 // `post`: the compact kernel hands the result words to the host as soon as the unique count is
 // final, i.e. while the remap kernel is still to run (it produces neither sizes nor errors).
+// `range`: a zeroed device word; when given, a first kernel stores the largest id there and the
+// insert kernel uses ids as slots if they all fit the table (see relabel_insert_one).
 int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, void* out_unique, void* out_relabel, TileStates st, int64_t* ticket,
                    int64_t* status, int64_t* result, cudaStream_t s, bool inserted = false,
-                   bool pdl = false, const HostPost* post = nullptr);
+                   bool pdl = false, const HostPost* post = nullptr, int64_t* range = nullptr);
 
 // The context's table for `numel_bound` ids (reserving it).
 int relabel_table(shmt_ctx* ctx, int64_t numel_bound, RelTable* t, cudaStream_t s);

@@ -250,10 +250,11 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
     store_int(job.sub_indptr, job.indptr64, first + j, prefix + s_off[j]);
     if (relabel) {
       const int64_t i = first + j;
+      bool maybe_first;
       const uint32_t pos = relabel_insert_one(job.rel_slots, rel_mask,
                                               load_int(job.seeds, job.seeds64, i), (unsigned)i,
-                                              job.status);
-      store_int(job.rel_out, sizeof(IxT) == 8, i, (int64_t)pos);
+                                              job.status, &maybe_first);
+      store_int(job.rel_out, sizeof(IxT) == 8, i, relabel_pack(pos, maybe_first, sizeof(IxT) == 8, job.rel_mask));
     }
   }
   if (tile == n_tiles - 1 && tid == 0) {
@@ -277,9 +278,11 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
           store_int(job.out_eids, job.indptr64, o,
                     (src[u] - static_cast<const IxT*>(s_hit[j] ? job.gpu_indices : job.indices)) + s_eshift[j]);
         if (relabel) {
-          const uint32_t pos = relabel_insert_one(job.rel_slots, rel_mask,
-                                                  (long long)v[u], (unsigned)(n + o), job.status);
-          store_int(job.rel_out, sizeof(IxT) == 8, n + o, (int64_t)pos);
+          bool maybe_first;
+          const uint32_t pos = relabel_insert_one(job.rel_slots, rel_mask, (long long)v[u],
+                                                  (unsigned)(n + o), job.status, &maybe_first);
+          store_int(job.rel_out, sizeof(IxT) == 8, n + o,
+                    relabel_pack(pos, maybe_first, sizeof(IxT) == 8, job.rel_mask));
         }
       }
     }
@@ -307,9 +310,11 @@ __global__ void __launch_bounds__(kHopThreads) sample_hop_kernel(const HopJob jo
       out_all[o] = val;
       if (job.out_eids) store_int(job.out_eids, job.indptr64, o, s_begin[j] + pos + s_eshift[j]);
       if (relabel) {
+        bool maybe_first;
         const uint32_t slot = relabel_insert_one(job.rel_slots, rel_mask, (long long)val,
-                                                 (unsigned)(n + o), job.status);
-        store_int(job.rel_out, sizeof(IxT) == 8, n + o, (int64_t)slot);
+                                                 (unsigned)(n + o), job.status, &maybe_first);
+        store_int(job.rel_out, sizeof(IxT) == 8, n + o,
+                  relabel_pack(slot, maybe_first, sizeof(IxT) == 8, job.rel_mask));
       }
     };
     if (job.weights && deg > 0 && (job.replace || deg > k)) {

@@ -115,6 +115,32 @@ def test_relabel_random_matches_oracle(capi, sizes, hi, dtype):
         assert np.array_equal(a.cpu().numpy(), b)
 
 
+def test_relabel_ids_as_slots_and_hashed_ids_share_one_table(capi):
+    """Inputs whose table is larger than the cache use the ids themselves as slots when they all fit
+    the table, and hash them when one does not (a larger or a negative id); calls of both kinds,
+    one after the other on one context, all match the oracle."""
+    n, top = 1_500_000, (1 << 22) - 1  # 2^22 slots serve 1,500,000 ids
+    rng = np.random.default_rng(9)
+    dense = rng.integers(0, 300_000, size=n).astype(np.int64)
+    cases = []
+    for extra in (top, top + 1, -5, None, 1 << 40, top):
+        x = dense.copy()
+        rng.shuffle(x)
+        if extra is not None:
+            x[rng.integers(0, n)] = extra
+        cases.append(x)
+    for x in cases:
+        uniq, (rel,) = capi.tensor_relabel([torch.from_numpy(x).cuda()])
+        wu, (wr,) = oracle.tensor_relabel([x])
+        assert np.array_equal(uniq.cpu().numpy(), wu) and np.array_equal(rel.cpu().numpy(), wr)
+    x32 = cases[0].astype(np.int32)
+    uniq, rel = capi.tensor_relabel([torch.from_numpy(x32[:700_000]).cuda(), torch.from_numpy(x32[700_000:]).cuda()])
+    wu, wr = oracle.tensor_relabel([x32[:700_000], x32[700_000:]])
+    assert np.array_equal(uniq.cpu().numpy(), wu)
+    assert all(np.array_equal(a.cpu().numpy(), b) for a, b in zip(rel, wr))
+    capi.check_async()
+
+
 def test_relabel_is_repeatable_and_idempotent(capi):
     g = torch.Generator(device="cuda").manual_seed(1)
     x = torch.randint(0, 100_000, (500_000,), generator=g, device="cuda")
