@@ -9,6 +9,7 @@ yields the tuple ``(sub_indptr, relabel_indices, num_src, num_dst)``.
 """
 from __future__ import annotations
 
+import contextlib
 import weakref
 from typing import Callable, Optional
 
@@ -39,7 +40,8 @@ class GPUSamplingDataloader:
 
     def __init__(self, indptr, indices, seeds, batchsize, num_picks, replace=False,
                  use_ddp=False, shuffle=True, drop_last=False,
-                 block_fn: Optional[Callable] = None, fused: bool = True, with_edge_ids: bool = False):
+                 block_fn: Optional[Callable] = None, fused: bool = True, with_edge_ids: bool = False,
+                 own_stream: bool = False):
         self.indptr, self.indices = indptr, indices
         self.batchsize, self.num_picks, self.replace = batchsize, num_picks, replace
         self.use_ddp, self.shuffle, self.drop_last = use_ddp, shuffle, drop_last
@@ -52,6 +54,14 @@ class GPUSamplingDataloader:
         self.with_edge_ids = with_edge_ids
         self.has_cache = False
         self.gpu_indptr = self.gpu_indices = self.hashmap = self.gpu_edge_base = None
+        # own_stream (not in the reference): sample on a stream of the loader's own.  The caller's
+        # stream waits for each batch it is handed, but the sampling of a batch does not wait for
+        # what the caller queued for the batch before it, so a consumer that queues its work and
+        # comes back for the next batch (a feature fetch, a training step) has that work run on the
+        # GPU beside the sampling of the next batch.
+        self._side = None
+        self._own_stream = own_stream
+        self._raw = []
 
         # host-resident CSR arrays are registered so kernels can read them in place
         for t in (self.indptr, self.indices):
@@ -65,10 +75,14 @@ class GPUSamplingDataloader:
         self.seeds = self.seeds.cuda()
         self._set_len()
         self.curr = 0
+        if own_stream:
+            self._side = torch.cuda.Stream(device=self.seeds.device)
         if self.fused and len(self.num_picks) <= 8:
-            # scratch for the largest mini-batch this loader can issue, before the first one
-            capi.reserve_minibatch(max(1, min(self.batchsize, max(1, self.seeds.numel()))),
-                                   list(reversed(self.num_picks)), self.seeds.device)
+            # scratch for the largest mini-batch this loader can issue, before the first one (the
+            # scratch belongs to the stream the sampling runs on)
+            with torch.cuda.stream(self._side) if self._side is not None else contextlib.nullcontext():
+                capi.reserve_minibatch(max(1, min(self.batchsize, max(1, self.seeds.numel()))),
+                                       list(reversed(self.num_picks)), self.seeds.device)
 
     # ------------------------------------------------------------------ seed bookkeeping
     def _local_share(self, seeds):
@@ -93,6 +107,9 @@ class GPUSamplingDataloader:
         if self.shuffle:
             self._reshuffle()
         self.curr = 0
+        if self._side is not None:
+            # the loader's stream sees the seeds, caches and arrays as the caller's stream left them
+            self._side.wait_stream(torch.cuda.current_stream(self.seeds.device))
         return self
 
     def update_params(self, **kwargs):
@@ -113,6 +130,20 @@ class GPUSamplingDataloader:
     def __next__(self):
         if self.curr >= self.len:
             raise StopIteration
+        if self._side is None:
+            return self._next_batch()
+        caller = torch.cuda.current_stream(self.seeds.device)
+        with torch.cuda.stream(self._side):
+            batch = self._next_batch()
+            done = torch.cuda.Event()
+            done.record(self._side)
+        caller.wait_event(done)
+        for t in self._raw:  # allocated on the loader's stream, used from here on by the caller's
+            t.record_stream(caller)
+        self._raw = []
+        return batch
+
+    def _next_batch(self):
         lo = self.curr * self.batchsize
         seeds = self.seeds[lo:lo + self.batchsize]
         self.curr += 1
@@ -131,9 +162,12 @@ class GPUSamplingDataloader:
             for hop in hops:
                 sub_indptr, relabel_indices, frontier = hop[0], hop[2], hop[3]
                 extra = (hop[4],) if self.with_edge_ids else ()
+                self._raw += [sub_indptr, relabel_indices, frontier, *extra]
                 blocks.insert(0, self.block_fn(sub_indptr, relabel_indices, frontier.numel(), n_dst, *extra))
                 n_dst = frontier.numel()
-            return hops[-1][3].to(seeds.dtype), output_nodes, blocks
+            input_nodes = hops[-1][3].to(seeds.dtype)
+            self._raw.append(input_nodes)
+            return input_nodes, output_nodes, blocks
         for num_pick in reversed(self.num_picks):
             if self.with_edge_ids:
                 cached = dict(gpu_indptr=self.gpu_indptr, gpu_indices=self.gpu_indices,
@@ -145,6 +179,7 @@ class GPUSamplingDataloader:
                 sub_indptr, sub_indices = self._hop(seeds, num_pick)
                 extra = ()
             frontier, (_, relabel_indices) = capi.tensor_relabel([seeds, sub_indices])
+            self._raw += [sub_indptr, relabel_indices, frontier, *extra]
             blocks.insert(0, self.block_fn(sub_indptr, relabel_indices, frontier.numel(),
                                            seeds.numel(), *extra))
             seeds = frontier

@@ -150,3 +150,38 @@ def test_blocks_with_edge_ids(fused):
         n += 1
     assert n == 4
     del dl
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_loader_on_its_own_stream_yields_the_same_batches(fused):
+    """own_stream=True: sampling runs on the loader's stream while the caller's stream works on the
+    batch before; every batch equals the one the plain loader yields, and what the caller computes
+    from a batch on its own stream sees finished tensors."""
+    from shmtensor_b200 import GPUSamplingDataloader, capi
+    indptr_n, indices_n = _graph(seed=5)
+    hotness = torch.from_numpy(np.diff(indptr_n).astype(np.float32))
+    feats = torch.randn(20_000, 64, device="cuda")
+    runs = []
+    for own in (False, True):
+        # a loader registers its host arrays for the GPU: each gets arrays of its own
+        indptr, indices = torch.from_numpy(indptr_n.copy()), torch.from_numpy(indices_n.copy())
+        dl = GPUSamplingDataloader(indptr, indices, torch.arange(0, 8192), 1024, [15, 10, 5], shuffle=False,
+                                   fused=fused, own_stream=own)
+        dl.create_cache(int((indptr.nbytes + indices.nbytes) * 0.5), hotness)
+        capi.set_sampling_seed(99)
+        out = []
+        for _ in range(2):  # two epochs: the second re-enters __iter__ with work still queued
+            for input_nodes, output_nodes, blocks in dl:
+                # consumer work queued on the caller's stream, not waited for before the next batch
+                pooled = feats[input_nodes.long()].sum(0)
+                for _ in range(20):
+                    pooled = pooled + feats[input_nodes.long()].sum(0)
+                out.append((input_nodes, [b[0] for b in blocks], [b[1] for b in blocks], pooled))
+        torch.cuda.synchronize()
+        runs.append(out)
+    assert len(runs[0]) == len(runs[1]) == 16
+    for a, b in zip(*runs):
+        assert torch.equal(a[0], b[0]) and torch.equal(a[3], b[3])
+        assert all(torch.equal(x, y) for x, y in zip(a[1], b[1]))
+        assert all(torch.equal(x, y) for x, y in zip(a[2], b[2]))
+    capi.check_async()
