@@ -78,6 +78,7 @@ relabel_insert_kernel(Parts ps, RelTable t, void* __restrict__ out, int64_t* sta
   }
 }
 
+template <int ITEMS>
 __global__ void __launch_bounds__(kRelThreads)
 relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
                        void* __restrict__ unique, TileStates st, int64_t* ticket, int64_t* status,
@@ -89,7 +90,8 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
   pdl_prologue();
   int64_t numel;
   resolve_sizes(ps, &numel);
-  const int64_t n_tiles = (numel + kRelTile - 1) / kRelTile;
+  constexpr int kTile = kRelThreads * ITEMS;
+  const int64_t n_tiles = (numel + kTile - 1) / kTile;
   const int tile = take_tile(ticket, &s_tile);
   if (tile >= n_tiles) {  // the grid is sized for the largest input the caller allows
     if (numel == 0 && tile == 0 && threadIdx.x == 0) {
@@ -98,22 +100,52 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
     }
     return;
   }
-  const int64_t base = (int64_t)tile * kRelTile + (int64_t)threadIdx.x * kRelItems;
-  uint32_t pos[kRelItems];
-  bool is_first[kRelItems];
-  int64_t cnt = 0;
+  const int64_t base = (int64_t)tile * kTile + (int64_t)threadIdx.x * ITEMS;
+  uint32_t pos[ITEMS];
+  unsigned maybe = 0, is_first = 0;  // one bit per element of this thread
+  // the thread's ITEMS slot numbers: 16-byte loads when the whole run lies inside the input
+  // and the array is aligned, else one by one
+  if (base + ITEMS <= numel && (reinterpret_cast<uintptr_t>(slot_of) & 15) == 0) {
+    if (ps.is64) {
+      const ulonglong2* src = reinterpret_cast<const ulonglong2*>(slot_of) + base / 2;
 #pragma unroll
-  for (int j = 0; j < kRelItems; ++j) {
-    const int64_t i = base + j;
-    is_first[j] = false;
-    if (i < numel) {
-      // only an element the inserting pass did not rule out has to look at its slot
-      bool maybe_first;
-      pos[j] = relabel_unpack(slot_of, ps.is64, i, t.mask, &maybe_first);
-      is_first[j] = maybe_first && __ldcg(&t.slots[pos[j]].first) == (unsigned)i;
+      for (int q = 0; q < ITEMS / 2; ++q) {
+        const ulonglong2 v = __ldg(src + q);
+        bool m0, m1;
+        pos[2 * q] = relabel_unpack64(v.x, &m0);
+        pos[2 * q + 1] = relabel_unpack64(v.y, &m1);
+        maybe |= ((unsigned)m0 << (2 * q)) | ((unsigned)m1 << (2 * q + 1));
+      }
+    } else {
+      const uint4* src = reinterpret_cast<const uint4*>(slot_of) + base / 4;
+#pragma unroll
+      for (int q = 0; q < ITEMS / 4; ++q) {
+        const uint4 v = __ldg(src + q);
+        const uint32_t raw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          bool m;
+          pos[4 * q + e] = relabel_unpack32(raw[e], t.mask, &m);
+          maybe |= (unsigned)m << (4 * q + e);
+        }
+      }
     }
-    cnt += is_first[j];
+  } else {
+#pragma unroll
+    for (int j = 0; j < ITEMS; ++j) {
+      pos[j] = 0;
+      if (base + j < numel) {
+        bool m;
+        pos[j] = relabel_unpack(slot_of, ps.is64, base + j, t.mask, &m);
+        maybe |= (unsigned)m << j;
+      }
+    }
   }
+  // only an element the inserting pass did not rule out has to look at its slot
+#pragma unroll
+  for (int j = 0; j < ITEMS; ++j)
+    if ((maybe >> j & 1u) && __ldcg(&t.slots[pos[j]].first) == (unsigned)(base + j)) is_first |= 1u << j;
+  const int64_t cnt = __popc(is_first);
   const int64_t local = block_exclusive_scan(cnt, warp_sums, &s_total);
   if (threadIdx.x < 32) {
     const int64_t p = lookback_exclusive_prefix(st, tile, s_total, status);
@@ -126,8 +158,8 @@ relabel_compact_kernel(Parts ps, RelTable t, const void* __restrict__ slot_of,
   if (threadIdx.x == 0) post_when_last(post, n_tiles);
   int64_t uid = s_prefix + local;
 #pragma unroll
-  for (int j = 0; j < kRelItems; ++j) {
-    if (is_first[j]) {
+  for (int j = 0; j < ITEMS; ++j) {
+    if (is_first >> j & 1u) {
       store_int(unique, ps.is64, uid, part_elem(ps, base + j));
       t.slots[pos[j]].newid = (unsigned)uid;
       ++uid;
@@ -185,9 +217,16 @@ int launch_relabel(shmt_ctx* ctx, const Parts& ps, int64_t numel_bound, void* ou
     SHMT_CUDA_TRY(launch_kernel(pdl, relabel_insert_kernel, grid, kRelThreads, 0, s, ps, t, out_relabel, status,
                                 (const unsigned long long*)r));
   }
-  SHMT_CUDA_TRY(launch_kernel(pdl, relabel_compact_kernel, (unsigned)n_tiles, kRelThreads, 0, s, ps, t,
-                              (const void*)out_relabel, out_unique, st, ticket, status, result,
-                              post ? *post : HostPost{}));
+  if (numel_bound >= kRelLargeInput) {
+    const int64_t big_tiles = (numel_bound + kRelThreads * kRelItemsLarge - 1) / (kRelThreads * kRelItemsLarge);
+    SHMT_CUDA_TRY(launch_kernel(pdl, relabel_compact_kernel<kRelItemsLarge>, (unsigned)big_tiles, kRelThreads, 0, s,
+                                ps, t, (const void*)out_relabel, out_unique, st, ticket, status, result,
+                                post ? *post : HostPost{}));
+  } else {
+    SHMT_CUDA_TRY(launch_kernel(pdl, relabel_compact_kernel<kRelItems>, (unsigned)n_tiles, kRelThreads, 0, s, ps, t,
+                                (const void*)out_relabel, out_unique, st, ticket, status, result,
+                                post ? *post : HostPost{}));
+  }
   SHMT_CUDA_TRY(launch_kernel(pdl, relabel_remap_kernel, grid, kRelThreads, 0, s, ps, t, out_relabel));
   SHMT_CUDA_TRY(cudaGetLastError());
   return SHMT_OK;

@@ -8,7 +8,14 @@
 namespace shmt {
 
 constexpr int kRelThreads = 256;
+// Elements per thread of the compact kernel, and so per tile.  Its tiles hand their counts on
+// through a look-back that advances 32 tiles per round trip: for a large input the length of that
+// chain, not memory, is what small tiles cost, so inputs of kRelLargeInput elements and more use
+// kRelItemsLarge per thread; a small input is a few dependent reads long and wants many CTAs.
+// Look-back state is always sized for the small tile.
 constexpr int kRelItems = 4;
+constexpr int kRelItemsLarge = 16;
+constexpr int64_t kRelLargeInput = 4 << 20;
 constexpr int kRelTile = kRelThreads * kRelItems;
 constexpr int kMaxParts = 8;
 
@@ -57,20 +64,24 @@ __device__ __forceinline__ int64_t relabel_pack(uint32_t pos, bool maybe_first, 
   return (int64_t)(int32_t)pos;
 }
 
-__device__ __forceinline__ uint32_t relabel_unpack(const void* slot_of, bool is64, int64_t i, uint32_t table_mask,
-                                                   bool* maybe_first) {
-  if (is64) {
-    const unsigned long long raw = reinterpret_cast<const unsigned long long*>(slot_of)[i];
-    *maybe_first = !(raw & kRelNotFirst64);
-    return (uint32_t)raw;
-  }
-  const uint32_t raw = reinterpret_cast<const uint32_t*>(slot_of)[i];
+__device__ __forceinline__ uint32_t relabel_unpack64(unsigned long long raw, bool* maybe_first) {
+  *maybe_first = !(raw & kRelNotFirst64);
+  return (uint32_t)raw;
+}
+
+__device__ __forceinline__ uint32_t relabel_unpack32(uint32_t raw, uint32_t table_mask, bool* maybe_first) {
   if (table_mask < kRelNotFirst32) {
     *maybe_first = !(raw & kRelNotFirst32);
     return raw & ~kRelNotFirst32;
   }
   *maybe_first = true;
   return raw;
+}
+
+__device__ __forceinline__ uint32_t relabel_unpack(const void* slot_of, bool is64, int64_t i, uint32_t table_mask,
+                                                   bool* maybe_first) {
+  if (is64) return relabel_unpack64(reinterpret_cast<const unsigned long long*>(slot_of)[i], maybe_first);
+  return relabel_unpack32(reinterpret_cast<const uint32_t*>(slot_of)[i], table_mask, maybe_first);
 }
 
 // Claim (or find) the slot of `key`, record `i` as a candidate first occurrence, and return
