@@ -130,8 +130,11 @@ class GPUSamplingDataloader:
     def __next__(self):
         if self.curr >= self.len:
             raise StopIteration
+        self._raw = []
         if self._side is None:
-            return self._next_batch()
+            batch = self._next_batch()
+            self._raw = []
+            return batch
         caller = torch.cuda.current_stream(self.seeds.device)
         with torch.cuda.stream(self._side):
             batch = self._next_batch()
