@@ -96,7 +96,9 @@ def test_fused_minibatch_equals_hop_by_hop(cached, idx_dtype):
             hot = torch.from_numpy(np.argsort(-np.diff(indptr_n))[:6000].copy()).cuda()
             gp, gi = capi.create_subcsr(indptr, indices, hot)
             hmap = capi.CUCOStaticHashmap(hot.int(), torch.arange(6000, dtype=torch.int32, device="cuda"), 0.8)
-        for n_seeds, fanouts in ((1024, [5, 10, 15]), (1, [3]), (333, [40, 2])):
+        # the last case's third relabel is sized for 8192 * 11 * 11 * 6 = 5.9 M ids: the fused path then
+        # takes the large-tile compact kernel where the per-hop calls (sized by the real counts) do not
+        for n_seeds, fanouts in ((1024, [5, 10, 15]), (1, [3]), (333, [40, 2]), (8192, [10, 10, 5])):
             seeds = torch.randperm(30_000, device="cuda")[:n_seeds].to(idx_dtype)
             capi.set_sampling_seed(4242)
             want, cur = [], seeds

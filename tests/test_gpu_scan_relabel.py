@@ -138,6 +138,14 @@ def test_relabel_ids_as_slots_and_hashed_ids_share_one_table(capi):
     wu, wr = oracle.tensor_relabel([x32[:700_000], x32[700_000:]])
     assert np.array_equal(uniq.cpu().numpy(), wu)
     assert all(np.array_equal(a.cpu().numpy(), b) for a, b in zip(rel, wr))
+    # one int32 array of odd length (16-byte loads of the largest-id pass, then a tail), dense and not
+    for extra in (None, -7):
+        y = np.concatenate([x32, x32[:3]])
+        if extra is not None:
+            y[-2] = extra
+        uniq, (rel,) = capi.tensor_relabel([torch.from_numpy(y).cuda()])
+        wu, (wr,) = oracle.tensor_relabel([y])
+        assert np.array_equal(uniq.cpu().numpy(), wu) and np.array_equal(rel.cpu().numpy(), wr)
     capi.check_async()
 
 
