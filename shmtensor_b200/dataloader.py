@@ -242,8 +242,15 @@ class GPUSamplingDataloader:
         gc = getattr(self, "graph_cache", None)
         if gc is None or not self.has_cache:
             raise RuntimeError("replace_cache: the cache was not created with replaceable=True")
+        if self._side is not None:
+            # batches already sampled on the loader's stream finish before the cache changes, and
+            # the next one sees the change
+            cur = torch.cuda.current_stream(self.seeds.device)
+            cur.wait_stream(self._side)
         n = gc.replace(evict_nodes, admit_nodes)
         self.gpu_indptr, self.gpu_indices = gc.gpu_indptr, gc.gpu_indices
+        if self._side is not None:
+            self._side.wait_stream(cur)
         return n
 
     def clear_cache(self):

@@ -149,6 +149,24 @@ def test_relabel_ids_as_slots_and_hashed_ids_share_one_table(capi):
     capi.check_async()
 
 
+@pytest.mark.parametrize("spread", [1, 1_000_003])
+def test_relabel_five_million_ids(capi, spread):
+    """Inputs of 4 M ids and more take the compact kernel with 4,096-element tiles (and, like every
+    input whose table exceeds the cache, the largest-id pass): dense ids (ids as slots) and ids
+    spread beyond the table (hashed), with a ragged last tile."""
+    rng = np.random.default_rng(77)
+    x = rng.integers(0, 2_000_000, size=5_000_123).astype(np.int64) * spread
+    uniq, (rel,) = capi.tensor_relabel([torch.from_numpy(x).cuda()])
+    wu, (wr,) = oracle.tensor_relabel([x])
+    assert np.array_equal(uniq.cpu().numpy(), wu) and np.array_equal(rel.cpu().numpy(), wr)
+    # the table is clean afterwards: a small input right behind it
+    y = x[:1000]
+    uniq, (rel,) = capi.tensor_relabel([torch.from_numpy(y).cuda()])
+    wu, (wr,) = oracle.tensor_relabel([y])
+    assert np.array_equal(uniq.cpu().numpy(), wu) and np.array_equal(rel.cpu().numpy(), wr)
+    capi.check_async()
+
+
 def test_relabel_is_repeatable_and_idempotent(capi):
     g = torch.Generator(device="cuda").manual_seed(1)
     x = torch.randint(0, 100_000, (500_000,), generator=g, device="cuda")
