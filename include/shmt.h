@@ -378,7 +378,9 @@ int shmt_host_numa_nodes(void); /* memory nodes of this machine (>= 1) */
 int shmt_host_numa_place(void* ptr, int64_t nbytes, int policy, int node);
 
 /* ---- device buffers shared between ranks (partitioned cache) ---------------
- * cudaMalloc'ed so that a CUDA IPC handle maps the buffer itself.  No
+ * cudaMalloc'ed so that a CUDA IPC handle maps the buffer itself; the size is
+ * rounded up to whole 2 MB pages, without which a peer maps it with small pages
+ * and random reads from a buffer of several GB slow down 10-20x.  No
  * counterpart in the reference.                                              */
 int shmt_dev_alloc(int64_t bytes, void** out);
 int shmt_dev_free(void* ptr);

@@ -66,7 +66,13 @@ extern "C" {
 
 int shmt_dev_alloc(int64_t bytes, void** out) {
   SHMT_REQUIRE(out != nullptr && bytes > 0, "shmt_dev_alloc: bad argument");
-  SHMT_CUDA_TRY(cudaMalloc(out, (size_t)bytes));
+  // Whole 2 MB pages: a peer that opens the buffer through CUDA IPC maps an allocation whose
+  // size is not a multiple of 2 MB with small pages, and random row reads from it then miss the
+  // TLB on every row once the buffer outgrows its reach (measured on B200: 63,000 rows of 512
+  // bytes from an 11.4 GB peer buffer in 1.04 ms, against 0.058 ms when the size is rounded up).
+  const size_t page = (size_t)2 << 20;
+  const size_t padded = ((size_t)bytes + page - 1) & ~(page - 1);
+  SHMT_CUDA_TRY(cudaMalloc(out, padded));
   return SHMT_OK;
 }
 
