@@ -107,7 +107,10 @@ class _DeviceBuffer:
 
 
 def share_device_buffer(buf: "_DeviceBuffer", group=None):
-    """Map every rank's buffer into every other rank (CUDA IPC).  Returns ``(ptrs, opened)``:
+    """Map every rank's buffer into every other rank (CUDA IPC).  The allocation behind ``buf``
+    should be whole 2 MB pages (``shmt_dev_alloc`` sees to it): a peer maps any other size with
+    small pages, and random row reads from a buffer of several GB then run 10-20x slower.
+    Returns ``(ptrs, opened)``:
     ``ptrs[r]`` is rank r's buffer as seen from this process, ``opened`` the mappings to close
     with ``shmt_ipc_close_handle`` (on every rank, with nothing in flight, before any free)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
