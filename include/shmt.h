@@ -290,6 +290,20 @@ int shmt_sample_minibatch(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
                           void* const* out_relabel, void* const* out_frontier,
                           int64_t* sizes_host, void* stream);
 
+/* The same mini-batch with every hop picking in proportion to per-edge weights, as
+ * shmt_sample_hop_weighted does (same draws as successive calls of it with rng_offset,
+ * rng_offset + 1, ...; without replacement every fan-out is at most 32).  No counterpart in the
+ * reference.                                                                                    */
+int shmt_sample_minibatch_weighted(shmt_ctx* ctx, const void* indptr, int indptr_dtype,
+                                   const void* indices, int indices_dtype, const float* weights,
+                                   const void* gpu_indptr, const void* gpu_indices,
+                                   const float* gpu_weights, const shmt_map* map,
+                                   const void* seeds, int64_t n_seeds, const int64_t* fanouts,
+                                   int n_hops, int replace, uint64_t rng_seed, uint64_t rng_offset,
+                                   void* const* out_sub_indptr, void* const* out_sub_indices,
+                                   void* const* out_relabel, void* const* out_frontier,
+                                   int64_t* sizes_host, void* stream);
+
 /* The same mini-batch that also reports the edge id of every sampled neighbour, per hop, in
  * out_edge_ids[h] (c_h * fanouts[h] entries of indptr dtype, parallel to out_sub_indices[h]);
  * see shmt_sample_hop_eids.  No counterpart in the reference.                              */

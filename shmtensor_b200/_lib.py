@@ -81,6 +81,8 @@ SIGNATURES = {
     "shmt_subcsr_edge_base": (_i, [_vp, _i, _vp, _i, _i64, _vp, _vp]),
     "shmt_sample_minibatch": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _i64, _pi64, _i, _i, _u64,
                                    _u64, _pvp, _pvp, _pvp, _pvp, _pi64, _vp]),
+    "shmt_sample_minibatch_weighted": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _pi64, _i, _i,
+                                            _u64, _u64, _pvp, _pvp, _pvp, _pvp, _pi64, _vp]),
     "shmt_sample_minibatch_eids": (_i, [_vp, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i64, _pi64, _i, _i, _u64,
                                         _u64, _pvp, _pvp, _pvp, _pvp, _pvp, _pi64, _vp]),
     "shmt_subcsr_count": (_i, [_vp, _vp, _i, _vp, _i, _i64, _vp, _pi64, _vp]),

@@ -682,7 +682,7 @@ def csr_weighted_sampling(indptr, indices, weights, seeds, num_picks: int, repla
 def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.Tensor,
                      fanouts: Sequence[int], replace: bool = False, gpu_indptr=None,
                      gpu_indices=None, hashmap: "CUCOStaticHashmap | None" = None,
-                     gpu_edge_base=None, return_eids: bool = False):
+                     gpu_edge_base=None, return_eids: bool = False, weights=None, gpu_weights=None):
     """Extension: all hops of a mini-batch in one native call (``shmt_sample_minibatch``).
 
     Equivalent to, for each ``k`` in ``fanouts`` in the given order::
@@ -695,6 +695,8 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
     frontier_after_hop)``.  Seeds are converted to the dtype of ``indices``.  With ``return_eids``
     every hop's tuple ends with the edge ids of its sampled neighbours (positions in ``indices``,
     dtype of ``indptr``); a cached graph then needs ``gpu_edge_base`` (``subcsr_edge_base``).
+    With ``weights`` (float32, one per edge; ``gpu_weights`` for the cached rows) every hop picks
+    in proportion to them, as ``csr_weighted_sampling`` does (not together with ``return_eids``).
     """
     _check_cuda(seeds, "seeds")
     dev = seeds.device
@@ -710,6 +712,18 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
     # handed to the library as raw addresses and turned into views only once sizes are known
     if return_eids and hashmap is not None and gpu_edge_base is None:
         raise RuntimeError("sample_minibatch: edge ids of a cached graph need gpu_edge_base")
+    if weights is not None:
+        if return_eids:
+            raise RuntimeError("sample_minibatch: weights and return_eids cannot be combined")
+        _check_contig(weights, "weights")
+        if weights.dtype != torch.float32 or weights.numel() != indices.numel():
+            raise RuntimeError("sample_minibatch: weights must be float32, one per edge")
+        if hashmap is not None:
+            if gpu_weights is None:
+                raise RuntimeError("sample_minibatch: a cached graph needs gpu_weights")
+            _check_cuda(gpu_weights, "gpu_weights")
+            if gpu_weights.dtype != torch.float32 or gpu_weights.numel() != gpu_indices.numel():
+                raise RuntimeError("sample_minibatch: gpu_weights must be float32, one per cached edge")
     key = (seeds.numel(), tuple(int(k) for k in fanouts), indptr.dtype, indices.dtype, bool(return_eids))
     layout = _minibatch_layouts.get(key)
     if layout is None:
@@ -746,6 +760,11 @@ def sample_minibatch(indptr: torch.Tensor, indices: torch.Tensor, seeds: torch.T
             _ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr), _ptr(gpu_indices),
             _ptr(gpu_edge_base), map_handle, _ptr(seeds), seeds.numel(), fan, n_hops, int(bool(replace)),
             _rng["seed"], offset, out_ptr, out_idx, out_eid, out_rel, out_front, sizes, _stream(dev)))
+    elif weights is not None:
+        check(lib.shmt_sample_minibatch_weighted(
+            _ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(weights), _ptr(gpu_indptr), _ptr(gpu_indices),
+            _ptr(gpu_weights), map_handle, _ptr(seeds), seeds.numel(), fan, n_hops, int(bool(replace)),
+            _rng["seed"], offset, out_ptr, out_idx, out_rel, out_front, sizes, _stream(dev)))
     else:
         check(lib.shmt_sample_minibatch(
             _ctx(dev), _ptr(indptr), pdt, _ptr(indices), xdt, _ptr(gpu_indptr), _ptr(gpu_indices),

@@ -608,7 +608,8 @@ struct MinibatchPlan {
   size_t scratch_bytes;
 };
 
-static int plan_minibatch(int64_t n_seeds, const int64_t* fanouts, int n_hops, MinibatchPlan* p) {
+static int plan_minibatch(int64_t n_seeds, const int64_t* fanouts, int n_hops, MinibatchPlan* p,
+                          bool weighted = false) {
   SHMT_REQUIRE(n_hops >= 1 && n_hops <= kMaxHops, "mini-batch: 1..%d hops", kMaxHops);
   SHMT_REQUIRE(n_seeds >= 1 && n_seeds < ((int64_t)1 << 31), "mini-batch: seed count out of range");
   SHMT_REQUIRE(fanouts != nullptr, "mini-batch: fanouts is null");
@@ -618,7 +619,7 @@ static int plan_minibatch(int64_t n_seeds, const int64_t* fanouts, int n_hops, M
     SHMT_REQUIRE(fanouts[h] >= 1 && fanouts[h] < ((int64_t)1 << 20), "mini-batch: fan-out out of range");
     p->cap[h + 1] = p->cap[h] * (1 + fanouts[h]);
     SHMT_REQUIRE(p->cap[h + 1] < ((int64_t)1 << 30), "mini-batch: worst-case frontier too large");
-    p->spt[h] = pick_seeds_per_tile(p->cap[h], fanouts[h]);
+    p->spt[h] = pick_seeds_per_tile(p->cap[h], weighted ? 33 : fanouts[h]);  // weighted: warp-per-seed layout
     p->hop_tiles[h] = (p->cap[h] + p->spt[h] - 1) / p->spt[h];
     p->rel_tiles[h] = (p->cap[h + 1] + kRelTile - 1) / kRelTile;
     p->off_hop[h] = cursor;
@@ -776,7 +777,8 @@ static int sample_minibatch_impl(shmt_ctx* ctx, const void* indptr, int indptr_d
                                  uint64_t rng_offset, void* const* out_sub_indptr,
                                  void* const* out_sub_indices, void* const* out_relabel,
                                  void* const* out_frontier, int64_t* sizes_host, void* stream,
-                                 const void* gpu_edge_base, void* const* out_edge_ids) {
+                                 const void* gpu_edge_base, void* const* out_edge_ids,
+                                 const float* weights = nullptr, const float* gpu_weights = nullptr) {
   SHMT_REQUIRE(ctx != nullptr, "shmt_sample_minibatch: ctx is null");
   SHMT_REQUIRE(valid_int_dtype(indptr_dtype) && valid_int_dtype(indices_dtype),
                "shmt_sample_minibatch: ID can only be int32 or int64");
@@ -792,7 +794,7 @@ static int sample_minibatch_impl(shmt_ctx* ctx, const void* indptr, int indptr_d
 
   // worst-case frontier sizes and the scratch plan: [words][per hop: sample tiles | relabel tiles]
   MinibatchPlan plan;
-  if (int rc = plan_minibatch(n_seeds, fanouts, n_hops, &plan)) return rc;
+  if (int rc = plan_minibatch(n_seeds, fanouts, n_hops, &plan, weights != nullptr)) return rc;
   for (int h = 0; h < n_hops; ++h)
     SHMT_REQUIRE(out_sub_indptr[h] && out_sub_indices[h] && out_relabel[h] && out_frontier[h],
                  "shmt_sample_minibatch: output buffer of hop %d is null", h);
@@ -836,6 +838,8 @@ static int sample_minibatch_impl(shmt_ctx* ctx, const void* indptr, int indptr_d
     job.seeds_per_tile = spt[h];
     job.out_eids = out_edge_ids ? out_edge_ids[h] : nullptr;
     job.gpu_edge_base = gpu_edge_base;
+    job.weights = weights;
+    job.gpu_weights = gpu_weights;
     job.st = carve_tile_states(base + off_hop[h], hop_tiles[h]);
     job.ticket = w + 0;
     job.status = status;
@@ -917,6 +921,27 @@ int shmt_sample_minibatch_eids(shmt_ctx* ctx, const void* indptr, int indptr_dty
                                seeds, n_seeds, fanouts, n_hops, replace, rng_seed, rng_offset, out_sub_indptr,
                                out_sub_indices, out_relabel, out_frontier, sizes_host, stream, gpu_edge_base,
                                out_edge_ids);
+}
+
+int shmt_sample_minibatch_weighted(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* indices,
+                                   int indices_dtype, const float* weights, const void* gpu_indptr,
+                                   const void* gpu_indices, const float* gpu_weights, const shmt_map* map,
+                                   const void* seeds, int64_t n_seeds, const int64_t* fanouts, int n_hops,
+                                   int replace, uint64_t rng_seed, uint64_t rng_offset,
+                                   void* const* out_sub_indptr, void* const* out_sub_indices,
+                                   void* const* out_relabel, void* const* out_frontier, int64_t* sizes_host,
+                                   void* stream) {
+  SHMT_REQUIRE(weights != nullptr, "shmt_sample_minibatch_weighted: weights are null");
+  SHMT_REQUIRE(map == nullptr || gpu_weights != nullptr,
+               "shmt_sample_minibatch_weighted: a cached graph needs gpu_weights");
+  for (int h = 0; fanouts && h < n_hops && h < 8; ++h)
+    SHMT_REQUIRE(replace || fanouts[h] <= 32,
+                 "shmt_sample_minibatch_weighted: without replacement the fan-out is at most 32 (hop %d has %lld)", h,
+                 (long long)fanouts[h]);
+  return sample_minibatch_impl(ctx, indptr, indptr_dtype, indices, indices_dtype, gpu_indptr, gpu_indices, map,
+                               seeds, n_seeds, fanouts, n_hops, replace, rng_seed, rng_offset, out_sub_indptr,
+                               out_sub_indices, out_relabel, out_frontier, sizes_host, stream, nullptr, nullptr,
+                               weights, gpu_weights);
 }
 
 int shmt_subcsr_count(shmt_ctx* ctx, const void* indptr, int indptr_dtype, const void* seeds,

@@ -118,3 +118,43 @@ def test_heavier_edges_win_more_often_on_long_rows(capi):
     assert (np.sort(x, 1)[:, 1:] != np.sort(x, 1)[:, :-1]).all()
     share = (x < 20).mean()
     assert 0.44 < share < 0.50, share   # sequential draws on the CPU give 0.471
+
+
+@pytest.mark.parametrize("cached", [False, True])
+def test_weighted_minibatch_equals_weighted_hops(capi, cached):
+    """shmt_sample_minibatch_weighted: all hops in one native call, the same draws as one
+    csr_weighted_sampling + tensor_relabel per hop."""
+    rng = np.random.default_rng(11)
+    n_nodes = 4000
+    deg = np.minimum((rng.pareto(1.2, size=n_nodes) * 6).astype(np.int64), 400)
+    indptr_n = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices_n = np.concatenate([rng.choice(n_nodes, size=d, replace=False) for d in deg]).astype(np.int32)
+    w_n = (rng.random(indices_n.size) + 0.01).astype(np.float32)
+    indptr, indices, weights = (torch.from_numpy(a).cuda() for a in (indptr_n, indices_n, w_n))
+    gp = gi = gw = hmap = None
+    if cached:
+        hot = torch.from_numpy(np.argsort(-deg)[:900].copy()).cuda()
+        gp, gi = capi.create_subcsr(indptr, indices, hot)
+        gw = capi.create_subcsr(indptr, weights.view(torch.int32), hot)[1].view(torch.float32)
+        hmap = capi.CUCOStaticHashmap(hot, torch.arange(900, device="cuda"), 0.5)
+    for n_seeds, fanouts, replace in ((512, [4, 8, 3], False), (100, [32, 2], False), (300, [6, 40], True)):
+        seeds = torch.from_numpy(rng.choice(n_nodes, size=n_seeds, replace=False)).int().cuda()
+        capi.set_sampling_seed(31)
+        want, cur = [], seeds
+        for k in fanouts:
+            p, x = capi.csr_weighted_sampling(indptr, indices, weights, cur, k, replace, gp, gi, gw, hmap)
+            nxt, (_, rx) = capi.tensor_relabel([cur, x])
+            want.append((p, x, rx, nxt))
+            cur = nxt
+        capi.set_sampling_seed(31)
+        frontier, hops = capi.sample_minibatch(indptr, indices, seeds, fanouts, replace, gp, gi, hmap,
+                                               weights=weights, gpu_weights=gw)
+        assert torch.equal(frontier, cur) and len(hops) == len(fanouts)
+        for (p, x, rx, nxt), (p2, x2, rx2, nxt2) in zip(want, hops):
+            assert torch.equal(p, p2) and torch.equal(x, x2) and torch.equal(rx, rx2) and torch.equal(nxt, nxt2)
+    from shmtensor_b200._lib import ShmtError
+    with pytest.raises(ShmtError, match="at most 32"):
+        capi.sample_minibatch(indptr, indices, seeds, [33], False, gp, gi, hmap, weights=weights, gpu_weights=gw)
+    with pytest.raises(RuntimeError, match="cannot be combined"):
+        capi.sample_minibatch(indptr, indices, seeds, [3], False, weights=weights, return_eids=True)
+    capi.check_async()
