@@ -41,7 +41,7 @@ class GPUSamplingDataloader:
     def __init__(self, indptr, indices, seeds, batchsize, num_picks, replace=False,
                  use_ddp=False, shuffle=True, drop_last=False,
                  block_fn: Optional[Callable] = None, fused: bool = True, with_edge_ids: bool = False,
-                 own_stream: bool = False):
+                 own_stream: bool = False, edge_weights: Optional[torch.Tensor] = None):
         self.indptr, self.indices = indptr, indices
         self.batchsize, self.num_picks, self.replace = batchsize, num_picks, replace
         self.use_ddp, self.shuffle, self.drop_last = use_ddp, shuffle, drop_last
@@ -54,6 +54,18 @@ class GPUSamplingDataloader:
         self.with_edge_ids = with_edge_ids
         self.has_cache = False
         self.gpu_indptr = self.gpu_indices = self.hashmap = self.gpu_edge_base = None
+        # edge_weights (not in the reference): float32, one per edge, parallel to `indices`; every hop
+        # then picks neighbours in proportion to them (without replacement: fan-outs of at most 32)
+        self.edge_weights = self.gpu_weights = None
+        if edge_weights is not None:
+            if edge_weights.dtype != torch.float32 or edge_weights.numel() != indices.numel():
+                raise RuntimeError("GPUSamplingDataloader: edge_weights must be float32, one per edge")
+            if with_edge_ids and fused:
+                raise RuntimeError("GPUSamplingDataloader: edge ids with edge_weights need fused=False")
+            self.edge_weights = edge_weights.contiguous()
+            if not self.edge_weights.is_cuda:
+                capi.pin_memory(self.edge_weights)
+                weakref.finalize(self, capi.unpin_memory, self.edge_weights)
         # own_stream (not in the reference): sample on a stream of the loader's own.  The caller's
         # stream waits for each batch it is handed, but the sampling of a batch does not wait for
         # what the caller queued for the batch before it, so a consumer that queues its work and
@@ -160,7 +172,8 @@ class GPUSamplingDataloader:
                                             self.gpu_indices if self.has_cache else None,
                                             self.hashmap if self.has_cache else None,
                                             self.gpu_edge_base if self.has_cache else None,
-                                            return_eids=self.with_edge_ids)
+                                            return_eids=self.with_edge_ids, weights=self.edge_weights,
+                                            gpu_weights=self.gpu_weights if self.has_cache else None)
             n_dst = seeds.numel()
             for hop in hops:
                 sub_indptr, relabel_indices, frontier = hop[0], hop[2], hop[3]
@@ -172,7 +185,13 @@ class GPUSamplingDataloader:
             self._raw.append(input_nodes)
             return input_nodes, output_nodes, blocks
         for num_pick in reversed(self.num_picks):
-            if self.with_edge_ids:
+            if self.edge_weights is not None:
+                cached = dict(gpu_indptr=self.gpu_indptr, gpu_indices=self.gpu_indices, gpu_weights=self.gpu_weights,
+                              gpu_edge_base=self.gpu_edge_base, hashmap=self.hashmap) if self.has_cache else {}
+                got = capi.csr_weighted_sampling(self.indptr, self.indices, self.edge_weights, seeds, num_pick,
+                                                 self.replace, return_eids=self.with_edge_ids, **cached)
+                sub_indptr, sub_indices, extra = got[0], got[1], tuple(got[2:])
+            elif self.with_edge_ids:
                 cached = dict(gpu_indptr=self.gpu_indptr, gpu_indices=self.gpu_indices,
                               gpu_edge_base=self.gpu_edge_base, hashmap=self.hashmap) if self.has_cache else {}
                 sub_indptr, sub_indices, eids = capi.csr_sampling_with_eids(self.indptr, self.indices, seeds,
@@ -201,6 +220,8 @@ class GPUSamplingDataloader:
         if full_size <= cache_capacity:  # everything fits: plain GPU CSR, no map
             self.has_cache = False
             self.indices, self.indptr = self.indices.cuda(), self.indptr.cuda()
+            if self.edge_weights is not None:
+                self.edge_weights = self.edge_weights.cuda()
             return
 
         degrees = (self.indptr[1:] - self.indptr[:-1]).cpu()
@@ -220,6 +241,8 @@ class GPUSamplingDataloader:
             return
         if self.with_edge_ids and replaceable:
             raise RuntimeError("create_cache: edge ids are kept for a compact cache only (replaceable=False)")
+        if self.edge_weights is not None and replaceable:
+            raise RuntimeError("create_cache: edge weights are kept for a compact cache only (replaceable=False)")
         if self.with_edge_ids:
             self.gpu_edge_base = capi.subcsr_edge_base(self.indptr, candidates)
         if replaceable:
@@ -231,6 +254,9 @@ class GPUSamplingDataloader:
             return
         self.gpu_indptr, self.gpu_indices = capi.create_subcsr(self.indptr, self.indices,
                                                                candidates)
+        if self.edge_weights is not None:  # the cached rows' weights, laid out like their neighbours
+            self.gpu_weights = capi.create_subcsr(self.indptr, self.edge_weights.view(torch.int32),
+                                                  candidates)[1].view(torch.float32)
         slots = torch.arange(candidates.numel(), device='cuda', dtype=torch.int32)
         self.hashmap = capi.CUCOStaticHashmap(candidates.int(), slots, 0.8)
         self.has_cache = True
@@ -255,7 +281,7 @@ class GPUSamplingDataloader:
 
     def clear_cache(self):
         self.has_cache = False
-        self.gpu_indptr = self.gpu_indices = self.hashmap = self.gpu_edge_base = None
+        self.gpu_indptr = self.gpu_indices = self.hashmap = self.gpu_edge_base = self.gpu_weights = None
         self.graph_cache = None
 
     def presampling(self):

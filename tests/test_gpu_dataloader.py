@@ -187,3 +187,45 @@ def test_loader_on_its_own_stream_yields_the_same_batches(fused):
         assert all(torch.equal(x, y) for x, y in zip(a[1], b[1]))
         assert all(torch.equal(x, y) for x, y in zip(a[2], b[2]))
     capi.check_async()
+
+
+@pytest.mark.parametrize("cached", [False, True])
+def test_loader_with_edge_weights(cached):
+    """edge_weights: every hop picks in proportion to the weights; the fused loader and the
+    call-per-hop loader yield the same batches, and an edge of weight ~0 next to heavy ones
+    is (almost) never taken from a long row."""
+    from shmtensor_b200 import GPUSamplingDataloader, capi
+    indptr_n, indices_n = _graph(seed=8)
+    rng = np.random.default_rng(8)
+    w_n = (rng.random(indices_n.size) + 0.5).astype(np.float32)
+    light = rng.random(indices_n.size) < 0.5
+    w_n[light] = 1e-12
+    hotness = torch.from_numpy(np.diff(indptr_n).astype(np.float32))
+    runs = []
+    for fused in (True, False):
+        indptr, indices = torch.from_numpy(indptr_n.copy()), torch.from_numpy(indices_n.copy())
+        dl = GPUSamplingDataloader(indptr, indices, torch.arange(0, 3072), 1024, [4, 6], shuffle=False, fused=fused,
+                                   edge_weights=torch.from_numpy(w_n.copy()))
+        if cached:
+            dl.create_cache(int((indptr.nbytes + indices.nbytes) * 0.5), hotness)
+            assert dl.has_cache and dl.gpu_weights is not None and dl.gpu_weights.numel() == dl.gpu_indices.numel()
+        capi.set_sampling_seed(55)
+        runs.append([(inp, [b[0] for b in blocks], [b[1] for b in blocks]) for inp, _, blocks in dl])
+    torch.cuda.synchronize()
+    assert len(runs[0]) == len(runs[1]) == 3
+    for a, b in zip(*runs):
+        assert torch.equal(a[0], b[0])
+        assert all(torch.equal(x, y) for x, y in zip(a[1], b[1])) and all(torch.equal(x, y) for x, y in zip(a[2], b[2]))
+    # first hop of one batch by hand: rows with at least 4 heavy edges among many yield heavy edges only
+    seeds = torch.arange(0, 1024, device="cuda")
+    p, x, e = capi.csr_weighted_sampling(torch.from_numpy(indptr_n).cuda(), torch.from_numpy(indices_n).cuda(),
+                                         torch.from_numpy(w_n).cuda(), seeds, 4, False, return_eids=True)
+    picked_light = light[e.cpu().numpy()]
+    row_of = np.repeat(np.arange(1024), np.diff(p.cpu().numpy()))
+    n_heavy = np.array([(~light[indptr_n[r]:indptr_n[r + 1]]).sum() for r in range(1024)])
+    deg = np.diff(indptr_n)[:1024]
+    strict = (n_heavy[row_of] >= 4) & (deg[row_of] > 4)
+    assert strict.sum() > 100 and picked_light[strict].sum() == 0
+    with pytest.raises(RuntimeError, match="fused=False"):
+        GPUSamplingDataloader(torch.from_numpy(indptr_n.copy()), torch.from_numpy(indices_n.copy()), torch.arange(8), 4,
+                              [2], with_edge_ids=True, edge_weights=torch.from_numpy(w_n.copy()))
